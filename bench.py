@@ -1,0 +1,375 @@
+"""Benchmark of the `bits` top-k selection hot path (and its CPU baseline).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--k 256] [--impl reference]
+
+Workload (the reference's selection sweep shape): a float32 distance matrix of q=1024 rows
+by n=2^20 columns (4 GiB) per GPU, Uniform[0,1) from a seeded device generator (synthetic:
+the reference itself only ever measures generated data), k=256 by default.  One step = one
+pass of the selection over the whole matrix.  With N GPUs the matrix is database-sharded:
+every rank holds its own q x n column block of a q x (N*n) matrix (weak scaling), selects
+its local top-k, the candidates are all-gathered over NCCL and merged on every rank.
+
+The JSON line carries: `value` (distances/s with the matrix resident in HBM), `e2e` (same
+metric through the C ABI with HOST buffers: pinned host -> device copy of the matrix, the
+selection, and the device -> host copy of the result, all inside the timed region),
+`roofline` (algorithmic bytes / CUDA-event kernel time against the measured HBM peak),
+`cpu_baseline` (the CPU port of the reference's OpenMP heap selection, timed on this host)
+and `sweep` (other k and the adversarial descending-row input, kernel time only).
+
+`--impl reference` times the reference's CPU selection alone (oracle/_ref when it was
+compiled, else the oracle port) and prints the same line shape with "impl": "reference".
+"""
+import argparse
+import json
+import os
+import pathlib
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = pathlib.Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+Q = 1024
+N_COLS = 1 << 20
+METRIC = "bits top-k selection throughput"
+UNIT = "distances/s"
+# the reference's published H100-PCIe numbers for this shape (q=1024, n=2^20), by k:
+# plots/kselection-hopper01-108424.csv lines 13, 45, 61, 106
+PUBLISHED_H100 = {32: 4.781e11, 128: 4.637e11, 256: 4.674e11, 2048: 3.599e11}
+
+
+def measured_peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        data = json.loads(path.read_text())
+        return float(data["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while a region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+        self.lines = []
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.thread.join(timeout=5)
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) != 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                smax.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[2:]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def cpu_selection_baseline(host_matrix, k, budget_s=20.0):
+    """Times the CPU port of the reference's OpenMP heap selection on a bounded row sample."""
+    import numpy as np
+    from oracle import oracle
+    oracle.build()
+    cores = oracle.num_threads()
+    rows = min(host_matrix.shape[0], max(cores, 64))
+    sample = np.ascontiguousarray(host_matrix[:rows])
+    oracle.select_heap(sample[:cores], k)  # warm the thread pool and the pages
+    times = []
+    spent = 0.0
+    while len(times) < 5 and spent < budget_s:
+        t0 = time.perf_counter()
+        oracle.select_heap(sample, k)
+        dt = time.perf_counter() - t0
+        times.append(dt)
+        spent += dt
+    best = statistics.median(times)
+    return {"value": rows * host_matrix.shape[1] / best, "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": f"first {rows} of {host_matrix.shape[0]} rows x {host_matrix.shape[1]} columns of the same "
+                      f"matrix, k={k}, OpenMP heap selection (port of parallel_knn::selection), "
+                      f"median of {len(times)} runs"}
+
+
+def run_reference_arm(args):
+    """The reference's own CPU implementation of the path, timed on the host cores."""
+    import numpy as np
+    from oracle import oracle
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    oracle.build()
+    cores = oracle.num_threads()
+    rows = max(cores, 64)
+    rng = np.random.default_rng(42)
+    sample = rng.random((rows, N_COLS), dtype=np.float32)
+    kind = "port"
+    select = lambda: oracle.select_heap(sample, args.k)
+    try:
+        from oracle import ref_select  # the reference's own parallel_knn::selection, if it was compiled
+        if ref_select.available():
+            kind = "reference"
+            select = lambda: ref_select.select_parallel(sample, args.k)
+    except Exception:
+        pass
+    for _ in range(max(args.warmup, 1)):
+        select()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        select()
+    dt = (time.perf_counter() - t0) / args.steps
+    value = rows * N_COLS / dt
+    sample_text = (f"each step = {rows} of {Q} rows x {N_COLS} columns, Uniform[0,1) seed 42, k={args.k}, "
+                   f"OpenMP heap selection on {cores} threads")
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"k-selection q={Q} n=2^20 uniform k={args.k} (bounded sample per step)",
+                       "q": Q, "n": N_COLS, "k": args.k},
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample_text},
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--k", type=int, default=256)
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--no-sweep", action="store_true", help="skip the k / input-order sweep")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--rows", type=int, default=Q, help="rows of the matrix (smaller = profiling case)")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "native" else args.warmup
+
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    import torch
+    import __graft_entry__ as entry
+    bk = entry.load_package()
+    bk.lib()  # fails loudly when the CUDA library is missing
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if args.gpus == 1 and world == 1:
+            pass
+        else:
+            raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist_pg = None
+    if world > 1:
+        import torch.distributed as dist_pg_mod
+        dist_pg_mod.init_process_group("nccl", device_id=dev)
+        dist_pg = dist_pg_mod
+
+    q, n, k = args.rows, N_COLS, args.k
+    gen = torch.Generator(device=dev).manual_seed(42 + rank)
+    matrix = torch.rand((q, n), generator=gen, device=dev, dtype=torch.float32)
+    offsets = torch.full((q,), rank * n, dtype=torch.int32, device=dev)  # global column index of the shard
+    out_d = torch.empty((q, k), dtype=torch.float32, device=dev)
+    out_i = torch.empty((q, k), dtype=torch.int32, device=dev)
+    if world > 1:
+        all_d = torch.empty((world, q, k), dtype=torch.float32, device=dev)
+        all_i = torch.empty((world, q, k), dtype=torch.int32, device=dev)
+        fin_d = torch.empty((q, k), dtype=torch.float32, device=dev)
+        fin_i = torch.empty((q, k), dtype=torch.int32, device=dev)
+
+    launches_per_step = 1 if world == 1 else 2
+
+    def step(src=matrix):
+        bk.select(src, k, label_offsets=offsets, out=(out_d, out_i))
+        if world > 1:
+            dist_pg.all_gather_into_tensor(all_d, out_d)
+            dist_pg.all_gather_into_tensor(all_i, out_i)
+            bk.merge(all_d, all_i, out=(fin_d, fin_i))
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist_pg.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist_pg.all_reduce(t, op=dist_pg.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- resident-input throughput (`value`) and the kernel time for the roofline ----------
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2 * args.steps + 2)]
+    barrier()
+    ev[-2].record()
+    for s in range(args.steps):
+        ev[2 * s].record()
+        bk.select(matrix, k, label_offsets=offsets, out=(out_d, out_i))
+        ev[2 * s + 1].record()
+        if world > 1:
+            dist_pg.all_gather_into_tensor(all_d, out_d)
+            dist_pg.all_gather_into_tensor(all_i, out_i)
+            bk.merge(all_d, all_i, out=(fin_d, fin_i))
+    ev[-1].record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    bk.device_status()
+    total_ms = max_over_ranks(ev[-2].elapsed_time(ev[-1]))
+    kernel_ms = statistics.mean(ev[2 * s].elapsed_time(ev[2 * s + 1]) for s in range(args.steps))
+    ms_per_step = total_ms / args.steps
+    value = q * n * world / (ms_per_step * 1e-3)
+
+    peak_gbs, peak_kind = measured_peaks()
+    algo_bytes = 4.0 * q * n + 8.0 * q * k
+    achieved = algo_bytes / (kernel_ms * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "kernel": "select_kernel", "achieved": achieved, "peak": peak_gbs, "unit": "GB/s",
+                "frac": achieved / peak_gbs, "peak_source": f"{peak_kind} (copy bandwidth, burst)",
+                "algorithmic_bytes_per_launch": algo_bytes, "kernel_ms": kernel_ms,
+                "traffic": None}
+    traffic_file = ROOT / "profiles" / "select_kernel_traffic.json"
+    if traffic_file.exists():
+        try:
+            t = json.loads(traffic_file.read_text())
+            # ncu capture of a smaller case of the same kernel, scaled by rows (traffic is per row)
+            roofline["traffic"] = t["dram_bytes_per_row"] * q
+            roofline["traffic_source"] = t.get("source")
+        except (KeyError, ValueError):
+            pass
+
+    # ---- sweep: other k, and the adversarial descending rows (kernel time only) -------------
+    sweep = None
+    if not args.no_sweep and world == 1:
+        sweep = {}
+        desc = None
+        for order in ("uniform", "descending"):
+            src = matrix
+            if order == "descending":
+                desc = torch.sort(matrix, dim=1, descending=True).values
+                src = desc
+            for kk in (16, 64, 256, 1024, 2048):
+                od = torch.empty((q, kk), dtype=torch.float32, device=dev)
+                oi = torch.empty((q, kk), dtype=torch.int32, device=dev)
+                reps = 5 if order == "uniform" else 2
+                for _ in range(2 if order == "uniform" else 1):
+                    bk.select(src, kk, out=(od, oi))
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(reps):
+                    bk.select(src, kk, out=(od, oi))
+                e1.record()
+                torch.cuda.synchronize()
+                ms = e0.elapsed_time(e1) / reps
+                sweep[f"{order}_k{kk}"] = {"ms": ms, "distances_per_s": q * n / (ms * 1e-3),
+                                           "frac_of_hbm_peak": (4.0 * q * n + 8.0 * q * kk) / (ms * 1e-3) / 1e9 / peak_gbs}
+            del src
+        del desc
+        torch.cuda.empty_cache()
+
+    # ---- end to end through the C ABI from host buffers (`e2e`) ----------------------------
+    e2e = None
+    host = None
+    if not args.no_e2e:
+        host = torch.empty((q, n), dtype=torch.float32).pin_memory()
+        host.copy_(matrix)
+        host_d = torch.empty((q, k), dtype=torch.float32).pin_memory()
+        host_i = torch.empty((q, k), dtype=torch.int32).pin_memory()
+        staging = torch.empty_like(matrix)
+        res_d, res_i = (out_d, out_i) if world == 1 else (fin_d, fin_i)
+
+        def e2e_step():
+            staging.copy_(host, non_blocking=True)
+            step(staging)
+            host_d.copy_(res_d, non_blocking=True)
+            host_i.copy_(res_i, non_blocking=True)
+
+        e2e_steps = max(3, min(args.steps, 10))
+        for _ in range(2):
+            e2e_step()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(e2e_steps):
+            e2e_step()
+        e1.record()
+        barrier()
+        e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / e2e_steps
+        e2e = {"value": q * n * world / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms, "steps": e2e_steps,
+               "h2d_bytes_per_step": 4 * q * n, "d2h_bytes_per_step": 8 * q * k}
+        del staging
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        host_np = (host if host is not None else matrix.cpu()).numpy()
+        cpu = cpu_selection_baseline(host_np, k)
+
+    if rank == 0:
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": (value / world / PUBLISHED_H100[k]) if (k in PUBLISHED_H100 and q == Q) else None,
+                "dtype": "f32", "data": "synthetic",
+                "config": {"workload": f"k-selection sweep shape: q={q} x n=2^20 float32 Uniform[0,1) per GPU, k={k}",
+                           "q": q, "n": n, "k": k, "sharding": "database columns" if world > 1 else "none",
+                           "l2_policy": "input (4 GiB per GPU) is larger than L2; no flush needed"},
+                "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
+                "gpu_launches": launches_per_step * args.steps, "clocks": clocks}
+        if sweep is not None:
+            line["sweep"] = sweep
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist_pg.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,161 @@
+// Error reporting, tuning registry and the device status word shared by every entry point.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+
+#include "common.cuh"
+
+namespace bitsknn
+{
+
+namespace
+{
+
+thread_local std::string g_last_error;
+
+__device__ int g_device_status = 0;
+
+struct tuning_entry
+{
+    const char* key;
+    int value;
+    int min;
+    int max;
+};
+
+std::mutex g_tuning_mutex;
+tuning_entry g_tuning[] = {
+    {"select.stage_bytes", 16384, 4096, 65536},
+    {"select.stages", 4, 2, 8},
+    {"select.merge_at", 100, 1, 100},
+    {"select.auto_split", 1, 0, 1},
+    {"fused.query_tile", 8, 8, 16},
+};
+
+} // namespace
+
+int fail(int code, const char* fmt, ...)
+{
+    char buffer[512];
+    va_list args;
+    va_start(args, fmt);
+    vsnprintf(buffer, sizeof(buffer), fmt, args);
+    va_end(args);
+    g_last_error = buffer;
+    return code;
+}
+
+int cuda_fail(cudaError_t err, const char* what, const char* file, int line)
+{
+    // same information the reference prints before throwing "CUDA error."
+    // (include/bits/cuch.hpp:11-19): file:line, error name and message, the failing call
+    return fail(BITSKNN_ERR_CUDA, "CUDA error. %s:%d %s: %s\n\t%s", file, line, cudaGetErrorName(err),
+                cudaGetErrorString(err), what);
+}
+
+int* device_status_word()
+{
+    int* ptr = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_device_status) != cudaSuccess)
+    {
+        return nullptr;
+    }
+    return ptr;
+}
+
+int tuning_value(const char* key, int fallback)
+{
+    std::lock_guard<std::mutex> lock{g_tuning_mutex};
+    for (const auto& entry : g_tuning)
+    {
+        if (std::strcmp(entry.key, key) == 0)
+        {
+            return entry.value;
+        }
+    }
+    return fallback;
+}
+
+int device_sm_count()
+{
+    int device = 0;
+    int sms = 0;
+    if (cudaGetDevice(&device) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0)
+    {
+        return 148;
+    }
+    return sms;
+}
+
+} // namespace bitsknn
+
+extern "C" int bitsknn_version(void) { return 100; }
+
+extern "C" const char* bitsknn_last_error_string(void) { return bitsknn::g_last_error.c_str(); }
+
+extern "C" int bitsknn_device_status(bitsknn_stream_t stream)
+{
+    using namespace bitsknn;
+    int* word = device_status_word();
+    if (word == nullptr)
+    {
+        return fail(BITSKNN_ERR_CUDA, "CUDA error. cannot resolve the device status word");
+    }
+    int value = 0;
+    auto s = static_cast<cudaStream_t>(stream);
+    BITSKNN_CUDA_TRY(cudaMemcpyAsync(&value, word, sizeof(int), cudaMemcpyDeviceToHost, s));
+    BITSKNN_CUDA_TRY(cudaStreamSynchronize(s));
+    if (value != 0)
+    {
+        BITSKNN_CUDA_TRY(cudaMemsetAsync(word, 0, sizeof(int), s));
+        BITSKNN_CUDA_TRY(cudaStreamSynchronize(s));
+        return fail(BITSKNN_ERR_DEVICE_TIMEOUT, "a kernel gave up a bounded wait (status word 0x%x)", value);
+    }
+    return BITSKNN_OK;
+}
+
+extern "C" int bitsknn_set_tuning(const char* key, int value)
+{
+    using namespace bitsknn;
+    if (key == nullptr)
+    {
+        return fail(BITSKNN_ERR_INVALID_ARGUMENT, "tuning key is null");
+    }
+    std::lock_guard<std::mutex> lock{g_tuning_mutex};
+    for (auto& entry : g_tuning)
+    {
+        if (std::strcmp(entry.key, key) == 0)
+        {
+            if (value < entry.min || value > entry.max)
+            {
+                return fail(BITSKNN_ERR_INVALID_ARGUMENT, "tuning value %d for '%s' outside [%d, %d]", value, key,
+                            entry.min, entry.max);
+            }
+            entry.value = value;
+            return BITSKNN_OK;
+        }
+    }
+    return fail(BITSKNN_ERR_INVALID_ARGUMENT, "unknown tuning key '%s'", key);
+}
+
+extern "C" int bitsknn_get_tuning(const char* key, int* value)
+{
+    using namespace bitsknn;
+    if (key == nullptr || value == nullptr)
+    {
+        return fail(BITSKNN_ERR_INVALID_ARGUMENT, "tuning key or output is null");
+    }
+    std::lock_guard<std::mutex> lock{g_tuning_mutex};
+    for (const auto& entry : g_tuning)
+    {
+        if (std::strcmp(entry.key, key) == 0)
+        {
+            *value = entry.value;
+            return BITSKNN_OK;
+        }
+    }
+    return fail(BITSKNN_ERR_INVALID_ARGUMENT, "unknown tuning key '%s'", key);
+}

@@ -1,0 +1,48 @@
+// Shared device/host helpers of the bitsknn kernels (sm_100a).
+#pragma once
+
+#include <cstdint>
+#include <cuda_runtime.h>
+
+#include "bitsknn.h"
+
+namespace bitsknn
+{
+
+// Label of a padding entry.  Padding pairs are (+inf, PAD_IDX): they sort after every real
+// pair, including real +inf distances (whose labels are smaller).
+constexpr int PAD_IDX = 0x7fffffff;
+constexpr unsigned FULL_MASK = 0xffffffffU;
+
+// The one total order of the engine: ascending distance, ties to the lowest index.
+// The reference's compare_and_swap (include/bits/topk/bitonic_sort_regs.cuh:53-60) looks at
+// the distance only; adding the index makes every network below deterministic.
+__device__ __forceinline__ bool pair_lt(float ad, int ai, float bd, int bi)
+{
+    return ad < bd || (ad == bd && ai < bi);
+}
+
+// Records a failure on the calling host thread and returns `code`.
+int fail(int code, const char* fmt, ...);
+// Checks a CUDA runtime status; on failure records file:line and returns BITSKNN_ERR_CUDA.
+int cuda_fail(cudaError_t err, const char* what, const char* file, int line);
+
+#define BITSKNN_CUDA_TRY(expr)                                                                     \
+    do                                                                                             \
+    {                                                                                              \
+        const cudaError_t bitsknn_err_ = (expr);                                                   \
+        if (bitsknn_err_ != cudaSuccess)                                                           \
+        {                                                                                          \
+            return ::bitsknn::cuda_fail(bitsknn_err_, #expr, __FILE__, __LINE__);                  \
+        }                                                                                          \
+    } while (0)
+
+// Device-side status word (0 = fine).  Kernels OR a bit into it when a bounded wait expires.
+int* device_status_word();
+constexpr int DEVICE_STATUS_TIMEOUT = 1;
+
+int tuning_value(const char* key, int fallback);
+
+int device_sm_count();
+
+} // namespace bitsknn

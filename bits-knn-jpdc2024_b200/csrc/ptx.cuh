@@ -1,0 +1,75 @@
+// Thin inline-PTX wrappers: mbarrier, 1-D bulk async copies (TMA without a tensor map).
+#pragma once
+
+#include <cstdint>
+#include <cuda_runtime.h>
+
+namespace bitsknn::ptx
+{
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p)
+{
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t arrivals)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(arrivals) : "memory");
+}
+
+// Makes freshly initialised barriers visible to the async proxy before any copy uses them.
+__device__ __forceinline__ void mbar_init_fence()
+{
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes)
+                 : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile("{\n"
+                 ".reg .pred p;\n"
+                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+                 "selp.u32 %0, 1, 0, p;\n"
+                 "}\n"
+                 : "=r"(ok)
+                 : "r"(smem_addr(bar)), "r"(parity)
+                 : "memory");
+    return ok != 0;
+}
+
+// Bounded wait: gives up after about `limit` polls (each poll may itself suspend for a
+// hardware-defined time).  Returns false on expiry; the caller reports it and leaves.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, uint32_t limit = (1U << 22))
+{
+    for (uint32_t i = 0; i < limit; ++i)
+    {
+        if (mbar_try_wait(bar, parity))
+        {
+            return true;
+        }
+        if (i > 64)
+        {
+            __nanosleep(64);
+        }
+    }
+    return false;
+}
+
+// 1-D bulk copy global -> shared, completion counted in bytes on `bar`.
+// dst, src 16-byte aligned; bytes a multiple of 16.  No multicast.
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_addr(dst)),
+                 "l"(src), "r"(bytes), "r"(smem_addr(bar))
+                 : "memory");
+}
+
+} // namespace bitsknn::ptx

@@ -1,0 +1,794 @@
+// `bits` top-k selection over a precomputed distance matrix, and the candidate-list merge.
+//
+// One thread block scans one row (or one slice of a row).  The row is streamed from HBM by
+// 1-D bulk asynchronous copies (TMA engine, no tensor map) into a ring of shared-memory
+// stages guarded by mbarriers; the threads read the stages with 128-bit loads, keep only the
+// values below the running k-th pair ("radius"), append the survivors to a shared-memory
+// candidate buffer by warp-aggregated slot allocation, and fold the buffer into a sorted,
+// register-resident list of L = 256 * IPT pairs with bitonic networks when it fills up.
+//
+// The algorithm is the reference's buffered partial bitonic sort
+// (include/bits/topk/singlepass/detail/bits_kernel.cuh:317-408: filter by radius :117-126,
+// buffer merge :145-199, overflow loop :383-391); the implementation differs where B200
+// wants it to:
+//   * bulk-copy ring instead of per-thread 4-byte loads + prefetch.global.L2 (:221-259);
+//   * an optimistic pass per stage with ONE barrier (survivors are rare once the radius has
+//     settled) that falls back to the reference's barrier-per-batch loop only when the
+//     buffer would overflow;
+//   * one ballot-free warp scan + one shared atomic per warp instead of one atomic per
+//     survivor;
+//   * every comparison is on the (distance, index) pair, so the output is the unique
+//     lowest-index answer whatever the arrival order of candidates.
+#include <algorithm>
+#include <cmath>
+#include <cstdint>
+#include <limits>
+
+#include "common.cuh"
+#include "ptx.cuh"
+#include "sortnet.cuh"
+
+namespace bitsknn
+{
+
+namespace
+{
+
+constexpr int SELECT_THREADS = 256;
+constexpr int MAX_STAGES = 8;
+
+struct select_params
+{
+    const float* dist;
+    int64_t ld;
+    const int32_t* labels;
+    int64_t ld_labels;
+    const int32_t* label_offsets;
+    int64_t n;
+    int k;
+    int splits;       // slices per row (1 = whole rows)
+    int64_t slice;    // elements per slice, a multiple of 4
+    float* out_dist;  // [rows * splits][k]
+    int32_t* out_idx; // [rows * splits][k]
+    int raw_pad;      // 1: leave padding as (+inf, PAD_IDX) (candidate lists for a later merge)
+    int stage_floats; // floats per stage, a multiple of 4 * SELECT_THREADS
+    int stages;
+    int merge_at;     // fold the buffer as soon as it holds this many candidates (<= L)
+    int* status;
+};
+
+struct select_ctrl
+{
+    int count;  // slow path: allocated slots (may exceed L)
+    int inc[3]; // fast path: slots allocated during stage c, in inc[c % 3]
+    float r_d;  // radius pair, written by the owner of list element k-1
+    int r_x;
+};
+
+template <int THREADS, int IPT>
+struct select_block
+{
+    static constexpr int L = THREADS * IPT;
+
+    float ld[IPT]; // the sorted list (ascending), blocked arrangement
+    int lx[IPT];
+    float r_d; // radius = k-th smallest pair seen so far
+    int r_x;
+    float* buf_d;
+    int* buf_x;
+    select_ctrl* ctrl;
+    const int32_t* labp; // explicit labels of this slice or nullptr
+    int lab0;            // implicit label of slice element 0
+    int k;
+
+    __device__ __forceinline__ int label_of(int e) const { return labp != nullptr ? labp[e] : lab0 + e; }
+
+    // Folds the first `valid` buffer entries into the list and refreshes the radius.
+    // Entered and left with all threads; `consumed` is taken off ctrl->count.
+    __device__ __forceinline__ void fold(int valid, int consumed)
+    {
+        const int tid = threadIdx.x;
+        float cd[IPT];
+        int cx[IPT];
+#pragma unroll
+        for (int r = 0; r < IPT; ++r)
+        {
+            const int s = r * THREADS + tid;
+            const bool in = s < valid;
+            cd[r] = in ? buf_d[s] : INFINITY;
+            cx[r] = in ? buf_x[s] : PAD_IDX;
+        }
+        __syncthreads(); // the buffer now doubles as exchange scratch of the networks
+        block_fold<THREADS, IPT>(ld, lx, cd, cx, buf_d, buf_x);
+#pragma unroll
+        for (int r = 0; r < IPT; ++r)
+        {
+            if (tid * IPT + r == k - 1)
+            {
+                ctrl->r_d = ld[r];
+                ctrl->r_x = lx[r];
+            }
+        }
+        if (tid == 0)
+        {
+            ctrl->count -= consumed;
+        }
+        __syncthreads();
+        r_d = ctrl->r_d;
+        r_x = ctrl->r_x;
+    }
+
+    // Evaluates the filter on one 4-vector; returns the number of survivors of this lane.
+    __device__ __forceinline__ int filter4(const float4& val, bool live, int e0, float (&dv)[4], int (&lab)[4],
+                                           bool (&pr)[4]) const
+    {
+        dv[0] = val.x;
+        dv[1] = val.y;
+        dv[2] = val.z;
+        dv[3] = val.w;
+        int cnt = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+        {
+            pr[j] = false;
+            lab[j] = 0;
+            if (live && dv[j] <= r_d)
+            {
+                lab[j] = label_of(e0 + j);
+                pr[j] = pair_lt(dv[j], lab[j], r_d, r_x);
+            }
+            cnt += pr[j] ? 1 : 0;
+        }
+        return cnt;
+    }
+
+    // Warp-inclusive prefix sum of `cnt`.
+    static __device__ __forceinline__ int warp_scan(int cnt)
+    {
+        const int lane = threadIdx.x & 31;
+        int incl = cnt;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1)
+        {
+            const int t = __shfl_up_sync(FULL_MASK, incl, o);
+            if (lane >= o)
+            {
+                incl += t;
+            }
+        }
+        return incl;
+    }
+
+    // Optimistic insertion of one 4-vector (whole warp): survivors beyond the capacity are
+    // dropped; the caller detects that from the stage's slot count and redoes the stage.
+    __device__ __forceinline__ void insert_fast(const float4& val, bool live, int e0, int count0, int* inc)
+    {
+        float dv[4];
+        int lab[4];
+        bool pr[4];
+        const int cnt = filter4(val, live, e0, dv, lab, pr);
+        const int incl = warp_scan(cnt);
+        const int total = __shfl_sync(FULL_MASK, incl, 31);
+        if (total == 0)
+        {
+            return;
+        }
+        const int lane = threadIdx.x & 31;
+        int base = 0;
+        if (lane == 31)
+        {
+            base = atomicAdd(inc, total);
+        }
+        base = __shfl_sync(FULL_MASK, base, 31);
+        int pos = count0 + base + incl - cnt;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+        {
+            if (pr[j])
+            {
+                if (pos < L)
+                {
+                    buf_d[pos] = dv[j];
+                    buf_x[pos] = lab[j];
+                }
+                ++pos;
+            }
+        }
+    }
+
+    // Guaranteed insertion of one stage: the reference's scheme (bits_kernel.cuh:277-302,
+    // 383-391) -- allocate slots for a batch of THREADS*4 values, write those that fit, fold
+    // the full buffer and retry the rest.  Returns the number of folds it needed.
+    __device__ __forceinline__ int stage_slow(const float4* sv, int nv, int e_base, int count0)
+    {
+        const int tid = threadIdx.x;
+        const int lane = tid & 31;
+        int folds = 0;
+        if (tid == 0)
+        {
+            ctrl->count = count0;
+        }
+        __syncthreads();
+        for (int vb = 0; vb < nv; vb += THREADS)
+        {
+            const int v = vb + tid;
+            const bool live = v < nv;
+            const float4 val = live ? sv[v] : make_float4(INFINITY, INFINITY, INFINITY, INFINITY);
+            float dv[4];
+            int lab[4];
+            bool pr[4];
+            const int cnt = filter4(val, live, e_base + 4 * v, dv, lab, pr);
+            const int incl = warp_scan(cnt);
+            const int total = __shfl_sync(FULL_MASK, incl, 31);
+            int base = 0;
+            if (lane == 31 && total > 0)
+            {
+                base = atomicAdd(&ctrl->count, total);
+            }
+            base = __shfl_sync(FULL_MASK, base, 31);
+            int pos = base + incl - cnt;
+            int ps[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+            {
+                ps[j] = pr[j] ? pos++ : -1;
+            }
+            while (true)
+            {
+                bool overflow = false;
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                {
+                    if (ps[j] >= 0)
+                    {
+                        if (ps[j] < L)
+                        {
+                            buf_d[ps[j]] = dv[j];
+                            buf_x[ps[j]] = lab[j];
+                            ps[j] = -1;
+                        }
+                        else
+                        {
+                            ps[j] -= L;
+                            overflow = true;
+                        }
+                    }
+                }
+                if (__syncthreads_or(overflow ? 1 : 0) == 0)
+                {
+                    break;
+                }
+                fold(L, L);
+                ++folds;
+            }
+        }
+        return folds;
+    }
+};
+
+template <int THREADS, int IPT>
+__global__ void __launch_bounds__(THREADS) select_kernel(const select_params p)
+{
+    using block_t = select_block<THREADS, IPT>;
+    constexpr int L = block_t::L;
+    constexpr int UNROLL = 4;
+
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int tid = threadIdx.x;
+    const int CH = p.stage_floats;
+    const int NST = p.stages;
+
+    float* stage_base = reinterpret_cast<float*>(smem);
+    block_t blk;
+    blk.buf_d = stage_base + static_cast<size_t>(NST) * CH;
+    blk.buf_x = reinterpret_cast<int*>(blk.buf_d + L);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(blk.buf_x + L);
+    blk.ctrl = reinterpret_cast<select_ctrl*>(bars + MAX_STAGES);
+    blk.k = p.k;
+
+    // which slice of which row
+    const int64_t vrow = blockIdx.x;
+    const int64_t row = vrow / p.splits;
+    const int64_t begin = (vrow - row * p.splits) * p.slice;
+    int64_t m64 = (p.n < begin + p.slice ? p.n : begin + p.slice) - begin;
+    const int m = m64 > 0 ? static_cast<int>(m64) : 0;
+    const float* rowp = p.dist + row * p.ld + begin;
+    blk.labp = p.labels != nullptr ? p.labels + row * p.ld_labels + begin : nullptr;
+    blk.lab0 = static_cast<int>(begin) + (p.label_offsets != nullptr ? p.label_offsets[row] : 0);
+
+    // [0,h): scalar head up to the first 16-byte boundary, [h,h+mid): streamed, then a tail < 4
+    int h = static_cast<int>(((16U - (reinterpret_cast<uintptr_t>(rowp) & 15U)) & 15U) >> 2);
+    h = h < m ? h : m;
+    const int mid = ((m - h) >> 2) << 2;
+    const int tail = m - h - mid;
+    const int nchunks = (mid + CH - 1) / CH;
+
+#pragma unroll
+    for (int r = 0; r < IPT; ++r)
+    {
+        blk.ld[r] = INFINITY;
+        blk.lx[r] = PAD_IDX;
+    }
+    blk.r_d = INFINITY;
+    blk.r_x = PAD_IDX;
+
+    auto issue = [&](int c) {
+        const int st = c % NST;
+        const int floats = (mid - c * CH) < CH ? (mid - c * CH) : CH;
+        ptx::mbar_expect_tx(&bars[st], static_cast<uint32_t>(floats) * 4U);
+        ptx::bulk_g2s(stage_base + static_cast<size_t>(st) * CH, rowp + h + static_cast<int64_t>(c) * CH,
+                      static_cast<uint32_t>(floats) * 4U, &bars[st]);
+    };
+
+    if (tid == 0)
+    {
+        for (int s = 0; s < NST; ++s)
+        {
+            ptx::mbar_init(&bars[s], 1);
+        }
+        blk.ctrl->count = 0;
+        blk.ctrl->inc[0] = 0;
+        blk.ctrl->inc[1] = 0;
+        blk.ctrl->inc[2] = 0;
+        ptx::mbar_init_fence();
+    }
+    __syncthreads();
+    if (tid == 0)
+    {
+        for (int c = 0; c < NST && c < nchunks; ++c)
+        {
+            issue(c);
+        }
+    }
+
+    // head and tail elements go straight into the buffer (at most 6 of them)
+    if (tid < h + tail)
+    {
+        const int e = tid < h ? tid : mid + tid;
+        const float d = rowp[e];
+        const int lab = blk.label_of(e);
+        if (pair_lt(d, lab, blk.r_d, blk.r_x))
+        {
+            const int pos = atomicAdd(&blk.ctrl->count, 1);
+            blk.buf_d[pos] = d;
+            blk.buf_x[pos] = lab;
+        }
+    }
+    __syncthreads();
+    int count0 = blk.ctrl->count; // candidates in the buffer; identical in every thread
+    bool go_slow = true;          // the first stage always overflows (radius = +inf)
+    bool timed_out = false;
+    int c = 0;
+
+    for (; c < nchunks; ++c)
+    {
+        const int st = c % NST;
+        const float4* sv = reinterpret_cast<const float4*>(stage_base + static_cast<size_t>(st) * CH);
+        const int floats = (mid - c * CH) < CH ? (mid - c * CH) : CH;
+        const int nv = floats >> 2;
+        const int e_base = h + c * CH;
+        int* inc = &blk.ctrl->inc[c % 3];
+
+        if (!ptx::mbar_wait_bounded(&bars[st], static_cast<uint32_t>((c / NST) & 1)))
+        {
+            timed_out = true;
+        }
+
+        bool redo = go_slow;
+        if (!go_slow)
+        {
+            for (int vb = 0; vb < nv; vb += THREADS * UNROLL)
+            {
+                float4 val[UNROLL];
+                bool live[UNROLL];
+#pragma unroll
+                for (int u = 0; u < UNROLL; ++u)
+                {
+                    const int v = vb + u * THREADS + tid;
+                    live[u] = v < nv;
+                    val[u] = live[u] ? sv[v] : make_float4(INFINITY, INFINITY, INFINITY, INFINITY);
+                }
+#pragma unroll
+                for (int u = 0; u < UNROLL; ++u)
+                {
+                    const float mn = fminf(fminf(val[u].x, val[u].y), fminf(val[u].z, val[u].w));
+                    const bool hit = live[u] && mn <= blk.r_d;
+                    if (__any_sync(FULL_MASK, hit))
+                    {
+                        blk.insert_fast(val[u], hit, e_base + 4 * (vb + u * THREADS + tid), count0, inc);
+                    }
+                }
+            }
+        }
+        // one barrier per stage: every thread is done reading the stage and adding to `inc`
+        if (__syncthreads_or(timed_out ? 1 : 0) != 0)
+        {
+            timed_out = true;
+            break;
+        }
+        if (!go_slow)
+        {
+            const int added = *inc;
+            if (count0 + added > L)
+            {
+                redo = true; // some survivors were dropped: forget this pass, redo the stage
+            }
+            else
+            {
+                count0 += added;
+            }
+        }
+        if (tid == 0)
+        {
+            blk.ctrl->inc[(c + 2) % 3] = 0; // last read before this barrier, next used after the next one
+        }
+        if (redo)
+        {
+            const int folds = blk.stage_slow(sv, nv, e_base, count0);
+            count0 = blk.ctrl->count;
+            go_slow = folds > 1;
+        }
+        if (count0 >= p.merge_at)
+        {
+            blk.fold(count0, count0);
+            count0 = 0;
+        }
+        // every thread has passed a barrier after its last read of this stage
+        if (tid == 0 && c + NST < nchunks)
+        {
+            issue(c + NST);
+        }
+    }
+
+    if (timed_out)
+    {
+        // report, let the copies still in flight land (bounded), and leave
+        for (int cc = c + 1; cc < nchunks && cc < c + NST; ++cc)
+        {
+            ptx::mbar_wait_bounded(&bars[cc % NST], static_cast<uint32_t>((cc / NST) & 1), 1U << 16);
+        }
+        if (tid == 0)
+        {
+            atomicOr(p.status, DEVICE_STATUS_TIMEOUT);
+        }
+        return;
+    }
+
+    if (count0 > 0)
+    {
+        blk.fold(count0, count0);
+    }
+
+    float* od = p.out_dist + vrow * p.k;
+    int32_t* ox = p.out_idx + vrow * p.k;
+#pragma unroll
+    for (int r = 0; r < IPT; ++r)
+    {
+        const int e = tid * IPT + r;
+        if (e < p.k)
+        {
+            int x = blk.lx[r];
+            if (p.raw_pad == 0 && x == PAD_IDX)
+            {
+                x = e; // the reference pads short rows with (+inf, position): bits_kernel.cuh:340-358
+            }
+            od[e] = blk.ld[r];
+            ox[e] = x;
+        }
+    }
+}
+
+// Merge of candidate lists: one block per query folds lists*k candidates, L at a time.
+template <int THREADS, int IPT>
+__global__ void __launch_bounds__(THREADS)
+    merge_kernel(const float* __restrict__ cand_dist, const int32_t* __restrict__ cand_idx, int64_t list_stride,
+                 int64_t query_stride, int lists, int k, float* __restrict__ out_dist, int32_t* __restrict__ out_idx)
+{
+    constexpr int L = THREADS * IPT;
+    __shared__ float sd[L];
+    __shared__ int sx[L];
+    const int tid = threadIdx.x;
+    const int64_t query = blockIdx.x;
+    const int total = lists * k;
+
+    float ld[IPT];
+    int lx[IPT];
+#pragma unroll
+    for (int r = 0; r < IPT; ++r)
+    {
+        ld[r] = INFINITY;
+        lx[r] = PAD_IDX;
+    }
+    for (int round = 0; round < total; round += L)
+    {
+        float cd[IPT];
+        int cx[IPT];
+#pragma unroll
+        for (int r = 0; r < IPT; ++r)
+        {
+            const int ci = round + r * THREADS + tid;
+            cd[r] = INFINITY;
+            cx[r] = PAD_IDX;
+            if (ci < total)
+            {
+                const int l = ci / k;
+                const int j = ci - l * k;
+                const int64_t at = l * list_stride + query * query_stride + j;
+                cd[r] = cand_dist[at];
+                cx[r] = cand_idx[at];
+            }
+        }
+        block_fold<THREADS, IPT>(ld, lx, cd, cx, sd, sx);
+    }
+#pragma unroll
+    for (int r = 0; r < IPT; ++r)
+    {
+        const int e = tid * IPT + r;
+        if (e < k)
+        {
+            out_dist[query * k + e] = ld[r];
+            out_idx[query * k + e] = lx[r] == PAD_IDX ? e : lx[r];
+        }
+    }
+}
+
+size_t select_smem_bytes(int L, int stage_floats, int stages)
+{
+    return static_cast<size_t>(stages) * stage_floats * 4 + static_cast<size_t>(L) * 8 + MAX_STAGES * 8 +
+           sizeof(select_ctrl);
+}
+
+template <int IPT>
+int launch_select(select_params p, int64_t vrows, cudaStream_t stream)
+{
+    constexpr int L = SELECT_THREADS * IPT;
+    const int merge_pct = tuning_value("select.merge_at", 100);
+    p.merge_at = std::max(1, (L * merge_pct) / 100);
+    const size_t smem = select_smem_bytes(L, p.stage_floats, p.stages);
+    auto kernel = select_kernel<SELECT_THREADS, IPT>;
+    BITSKNN_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    kernel<<<static_cast<unsigned>(vrows), SELECT_THREADS, smem, stream>>>(p);
+    BITSKNN_CUDA_TRY(cudaGetLastError());
+    return BITSKNN_OK;
+}
+
+int dispatch_select(const select_params& p, int64_t vrows, cudaStream_t stream)
+{
+    // smallest list that holds k: the reference's dynamic_switch_le over K
+    // (src/topk/singlepass/bits_knn.cu:44), with the list never shorter than the block
+    if (p.k <= 256)
+    {
+        return launch_select<1>(p, vrows, stream);
+    }
+    if (p.k <= 512)
+    {
+        return launch_select<2>(p, vrows, stream);
+    }
+    if (p.k <= 1024)
+    {
+        return launch_select<4>(p, vrows, stream);
+    }
+    return launch_select<8>(p, vrows, stream);
+}
+
+template <int IPT>
+int launch_merge(const float* cd, const int32_t* cx, int64_t list_stride, int64_t query_stride, int64_t q, int lists,
+                 int k, float* od, int32_t* ox, cudaStream_t stream)
+{
+    merge_kernel<SELECT_THREADS, IPT>
+        <<<static_cast<unsigned>(q), SELECT_THREADS, 0, stream>>>(cd, cx, list_stride, query_stride, lists, k, od, ox);
+    BITSKNN_CUDA_TRY(cudaGetLastError());
+    return BITSKNN_OK;
+}
+
+int dispatch_merge(const float* cd, const int32_t* cx, int64_t list_stride, int64_t query_stride, int64_t q, int lists,
+                   int k, float* od, int32_t* ox, cudaStream_t stream)
+{
+    if (k <= 256)
+    {
+        return launch_merge<1>(cd, cx, list_stride, query_stride, q, lists, k, od, ox, stream);
+    }
+    if (k <= 512)
+    {
+        return launch_merge<2>(cd, cx, list_stride, query_stride, q, lists, k, od, ox, stream);
+    }
+    if (k <= 1024)
+    {
+        return launch_merge<4>(cd, cx, list_stride, query_stride, q, lists, k, od, ox, stream);
+    }
+    return launch_merge<8>(cd, cx, list_stride, query_stride, q, lists, k, od, ox, stream);
+}
+
+int check_select_args(const float* d_dist, int64_t ld, int64_t q, int64_t n, int k, const float* od, const int32_t* ox)
+{
+    if (d_dist == nullptr || od == nullptr || ox == nullptr)
+    {
+        return fail(BITSKNN_ERR_INVALID_ARGUMENT, "null pointer argument");
+    }
+    if (q < 0 || n <= 0 || ld < n)
+    {
+        return fail(BITSKNN_ERR_INVALID_ARGUMENT, "invalid sizes: q=%lld n=%lld ld=%lld", static_cast<long long>(q),
+                    static_cast<long long>(n), static_cast<long long>(ld));
+    }
+    if (n >= std::numeric_limits<int32_t>::max() - 4 || q > 0x7fffffffLL)
+    {
+        return fail(BITSKNN_ERR_INVALID_ARGUMENT, "row length or row count beyond int32 labels");
+    }
+    if (k < 1 || k > BITSKNN_MAX_K)
+    {
+        // same wording as the reference's dispatcher (src/topk/singlepass/bits_knn.cu:52-55)
+        return fail(BITSKNN_ERR_UNSUPPORTED_K, "Unsupported k value: %d", k);
+    }
+    if ((reinterpret_cast<uintptr_t>(d_dist) & 3U) != 0)
+    {
+        return fail(BITSKNN_ERR_INVALID_ARGUMENT, "distance matrix is not 4-byte aligned");
+    }
+    return BITSKNN_OK;
+}
+
+void fill_stream_config(select_params& p)
+{
+    int stage_bytes = tuning_value("select.stage_bytes", 16384);
+    stage_bytes = (stage_bytes / (16 * SELECT_THREADS)) * (16 * SELECT_THREADS);
+    stage_bytes = std::max(stage_bytes, 16 * SELECT_THREADS);
+    p.stage_floats = stage_bytes / 4;
+    p.stages = std::min(std::max(tuning_value("select.stages", 4), 2), MAX_STAGES);
+}
+
+} // namespace
+
+} // namespace bitsknn
+
+using namespace bitsknn;
+
+extern "C" int bitsknn_select(const float* d_dist, int64_t ld, const int32_t* d_labels, int64_t ld_labels,
+                              const int32_t* d_label_offsets, int64_t q, int64_t n, int k, float* d_out_dist,
+                              int32_t* d_out_idx, bitsknn_stream_t stream)
+{
+    if (const int rc = check_select_args(d_dist, ld, q, n, k, d_out_dist, d_out_idx); rc != BITSKNN_OK)
+    {
+        return rc;
+    }
+    if (d_labels != nullptr && ld_labels < n)
+    {
+        return fail(BITSKNN_ERR_INVALID_ARGUMENT, "label matrix stride %lld shorter than n", static_cast<long long>(ld_labels));
+    }
+    if (q == 0)
+    {
+        return BITSKNN_OK;
+    }
+    select_params p{};
+    p.dist = d_dist;
+    p.ld = ld;
+    p.labels = d_labels;
+    p.ld_labels = ld_labels;
+    p.label_offsets = d_label_offsets;
+    p.n = n;
+    p.k = k;
+    p.splits = 1;
+    p.slice = (n + 3) & ~static_cast<int64_t>(3);
+    p.out_dist = d_out_dist;
+    p.out_idx = d_out_idx;
+    p.raw_pad = 0;
+    p.status = device_status_word();
+    if (p.status == nullptr)
+    {
+        return fail(BITSKNN_ERR_CUDA, "CUDA error. cannot resolve the device status word");
+    }
+    fill_stream_config(p);
+    return dispatch_select(p, q, static_cast<cudaStream_t>(stream));
+}
+
+namespace
+{
+
+int resolve_splits(int64_t q, int64_t n, int splits)
+{
+    if (splits > 0)
+    {
+        return splits;
+    }
+    // enough blocks for a few waves over all SMs, slices no shorter than 32 Ki elements
+    const int64_t want = static_cast<int64_t>(device_sm_count()) * 3 * 4;
+    int64_t s = (want + q - 1) / q;
+    const int64_t longest = std::max<int64_t>(1, n / 32768);
+    s = std::min(s, longest);
+    s = std::min<int64_t>(std::max<int64_t>(s, 1), 64);
+    return static_cast<int>(s);
+}
+
+} // namespace
+
+extern "C" size_t bitsknn_select_split_workspace_bytes(int64_t q, int k, int splits)
+{
+    if (q <= 0 || k <= 0)
+    {
+        return 0;
+    }
+    const int s = splits > 0 ? splits : 64; // upper bound of the automatic choice
+    return static_cast<size_t>(q) * static_cast<size_t>(s) * static_cast<size_t>(k) * 8U;
+}
+
+extern "C" int bitsknn_select_split(const float* d_dist, int64_t ld, const int32_t* d_label_offsets, int64_t q,
+                                    int64_t n, int k, int splits, void* d_workspace, size_t workspace_bytes,
+                                    float* d_out_dist, int32_t* d_out_idx, bitsknn_stream_t stream)
+{
+    if (const int rc = check_select_args(d_dist, ld, q, n, k, d_out_dist, d_out_idx); rc != BITSKNN_OK)
+    {
+        return rc;
+    }
+    if (splits < 0 || splits > 4096)
+    {
+        return fail(BITSKNN_ERR_INVALID_ARGUMENT, "invalid number of slices per row: %d", splits);
+    }
+    if (q == 0)
+    {
+        return BITSKNN_OK;
+    }
+    const int s = resolve_splits(q, n, splits);
+    if (static_cast<int64_t>(s) * k > 65536)
+    {
+        return fail(BITSKNN_ERR_INVALID_ARGUMENT, "slices * k = %lld exceeds 65536", static_cast<long long>(s) * k);
+    }
+    const size_t need = static_cast<size_t>(q) * s * k * 8U;
+    if (d_workspace == nullptr || workspace_bytes < need)
+    {
+        return fail(BITSKNN_ERR_WORKSPACE, "workspace of %zu bytes needed, %zu given", need, workspace_bytes);
+    }
+    auto* cand_dist = static_cast<float*>(d_workspace);
+    auto* cand_idx = reinterpret_cast<int32_t*>(cand_dist + static_cast<size_t>(q) * s * k);
+
+    select_params p{};
+    p.dist = d_dist;
+    p.ld = ld;
+    p.labels = nullptr;
+    p.ld_labels = 0;
+    p.label_offsets = d_label_offsets;
+    p.n = n;
+    p.k = k;
+    p.splits = s;
+    p.slice = (((n + s - 1) / s) + 3) & ~static_cast<int64_t>(3);
+    p.out_dist = cand_dist;
+    p.out_idx = cand_idx;
+    p.raw_pad = 1;
+    p.status = device_status_word();
+    if (p.status == nullptr)
+    {
+        return fail(BITSKNN_ERR_CUDA, "CUDA error. cannot resolve the device status word");
+    }
+    fill_stream_config(p);
+    auto cs = static_cast<cudaStream_t>(stream);
+    if (const int rc = dispatch_select(p, q * s, cs); rc != BITSKNN_OK)
+    {
+        return rc;
+    }
+    return dispatch_merge(cand_dist, cand_idx, k, static_cast<int64_t>(s) * k, q, s, k, d_out_dist, d_out_idx, cs);
+}
+
+extern "C" int bitsknn_merge(const float* d_cand_dist, const int32_t* d_cand_idx, int64_t list_stride,
+                             int64_t query_stride, int64_t q, int lists, int k, float* d_out_dist,
+                             int32_t* d_out_idx, bitsknn_stream_t stream)
+{
+    if (d_cand_dist == nullptr || d_cand_idx == nullptr || d_out_dist == nullptr || d_out_idx == nullptr)
+    {
+        return fail(BITSKNN_ERR_INVALID_ARGUMENT, "null pointer argument");
+    }
+    if (q < 0 || lists < 1 || list_stride < 0 || query_stride < 0 || q > 0x7fffffffLL)
+    {
+        return fail(BITSKNN_ERR_INVALID_ARGUMENT, "invalid sizes: q=%lld lists=%d", static_cast<long long>(q), lists);
+    }
+    if (k < 1 || k > BITSKNN_MAX_K)
+    {
+        return fail(BITSKNN_ERR_UNSUPPORTED_K, "Unsupported k value: %d", k);
+    }
+    if (static_cast<int64_t>(lists) * k > 65536)
+    {
+        return fail(BITSKNN_ERR_INVALID_ARGUMENT, "lists * k = %lld exceeds 65536", static_cast<long long>(lists) * k);
+    }
+    if (q == 0)
+    {
+        return BITSKNN_OK;
+    }
+    return dispatch_merge(d_cand_dist, d_cand_idx, list_stride, query_stride, q, lists, k, d_out_dist, d_out_idx,
+                          static_cast<cudaStream_t>(stream));
+}

@@ -1,0 +1,150 @@
+/* bitsknn.h -- C ABI of the B200 (sm_100a) k-NN hot path.
+ *
+ * Drop-in boundary for the device work behind the reference's algorithm objects
+ * (jiriklepl/bits-knn-jpdc2024).  Every entry point
+ *   - takes plain pointers and sizes (DEVICE pointers unless the name says `host`),
+ *   - is stream-ordered and does not synchronise unless documented,
+ *   - never allocates result memory: outputs and workspaces are the caller's,
+ *   - returns an int status (BITSKNN_OK == 0) and never throws; the text of the last
+ *     failure on the calling thread is available from bitsknn_last_error_string().
+ *
+ * Result convention (the reference's `distance_pair` order, include/bits/knn.hpp:13-17):
+ * per query the k smallest (distance, index) pairs in ascending distance, ties broken by
+ * the lowest index, as two row-major arrays float32[q][k] and int32[q][k].
+ */
+#ifndef BITSKNN_H_
+#define BITSKNN_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* A `cudaStream_t` passed through the C ABI (NULL = the legacy default stream, which is
+ * what the reference uses everywhere: include/bits/cuda_stream.hpp:198). */
+typedef void* bitsknn_stream_t;
+
+enum bitsknn_status
+{
+    BITSKNN_OK = 0,
+    BITSKNN_ERR_INVALID_ARGUMENT = 1, /* null pointer, negative size, misaligned pointer */
+    BITSKNN_ERR_UNSUPPORTED_K = 2,    /* the reference's "Unsupported k value" (bits_knn.cu:52-62) */
+    BITSKNN_ERR_UNSUPPORTED_DIM = 3,
+    BITSKNN_ERR_WORKSPACE = 4,        /* caller-provided workspace too small */
+    BITSKNN_ERR_CUDA = 5,             /* a CUDA runtime call failed (the reference's "CUDA error.") */
+    BITSKNN_ERR_DEVICE_TIMEOUT = 6,   /* a bounded device-side wait expired */
+    BITSKNN_ERR_UNSUPPORTED_MODE = 7
+};
+
+/* Largest k of the selection / merge kernels (the reference's limit,
+ * src/topk/singlepass/detail/definitions_common.hpp:4). */
+#define BITSKNN_MAX_K 2048
+/* Largest k of the fused kernel (src/topk/singlepass/detail/definitions_common.hpp:6). */
+#define BITSKNN_FUSED_MAX_K 256
+
+/* Library version (major * 10000 + minor * 100 + patch). */
+int bitsknn_version(void);
+
+/* Text of the last error reported on the calling thread ("" if none). */
+const char* bitsknn_last_error_string(void);
+
+/* Reads (and clears) the device-side status word that kernels set when one of their bounded
+ * waits gives up.  Synchronises `stream`.  Returns BITSKNN_OK or BITSKNN_ERR_DEVICE_TIMEOUT. */
+int bitsknn_device_status(bitsknn_stream_t stream);
+
+/* Tuning knobs (launch shapes).  Unknown keys return BITSKNN_ERR_INVALID_ARGUMENT.
+ *   "select.stage_bytes"  bytes per shared-memory stage of the row stream (multiple of 4096)
+ *   "select.stages"       stages in the ring (2..8)
+ *   "select.merge_at"     merge the candidate buffer when it holds at least this percentage
+ *                         of its capacity (1..100; 100 = only when full, like the reference)
+ * The reference's `--block-size` / `--items-per-thread` flags tune the same things for its
+ * kernels (src/topk/singlepass/bits_knn.cu:98-114); here they are hints. */
+int bitsknn_set_tuning(const char* key, int value);
+int bitsknn_get_tuning(const char* key, int* value);
+
+/* ---------------------------------------------------------------------------------------
+ * `bits` top-k selection over a precomputed distance matrix.
+ * Replaces run_bits_kernel<...>() (include/bits/topk/singlepass/bits_kernel.hpp:22-27) and
+ * its dispatcher bits::run (src/topk/singlepass/bits_knn.cu:29-65).
+ *
+ *   d_dist           float32[q][ld], row-major, ld >= n; 4-byte aligned (rows whose start
+ *                    is 16-byte aligned stream entirely through bulk copies)
+ *   d_labels         optional int32[q][ld_labels]: explicit label of every matrix element
+ *                    (NULL = the column index), the reference's `in_label`
+ *   d_label_offsets  optional int32[q]: added to the implicit column index of row i, the
+ *                    reference's `label_offsets` (bits_kernel.cuh:235-243)
+ *   k                1 <= k <= BITSKNN_MAX_K (any value, not only powers of two)
+ *   d_out_dist/idx   float32[q][k], int32[q][k]
+ * Rows with n < k are padded with (+inf, position) like the reference's first block load.
+ * --------------------------------------------------------------------------------------- */
+int bitsknn_select(const float* d_dist, int64_t ld, const int32_t* d_labels, int64_t ld_labels,
+                   const int32_t* d_label_offsets, int64_t q, int64_t n, int k, float* d_out_dist,
+                   int32_t* d_out_idx, bitsknn_stream_t stream);
+
+/* Split-row selection: every row is cut into `splits` slices scanned by separate thread
+ * blocks, whose candidates (q * splits * k pairs in the caller's workspace) are merged by a
+ * second kernel.  Replaces single_query_bits (src/topk/singlepass/bits_knn.cu:116-186, the
+ * `bits-sq --deg` algorithm).  splits == 0 lets the library choose from q and the SM count.
+ * Workspace size: bitsknn_select_split_workspace_bytes(q, k, splits). */
+size_t bitsknn_select_split_workspace_bytes(int64_t q, int k, int splits);
+int bitsknn_select_split(const float* d_dist, int64_t ld, const int32_t* d_label_offsets, int64_t q,
+                         int64_t n, int k, int splits, void* d_workspace, size_t workspace_bytes,
+                         float* d_out_dist, int32_t* d_out_idx, bitsknn_stream_t stream);
+
+/* Merge of `lists` candidate lists per query into the k smallest pairs (candidate j of
+ * list l of query i is at [l * list_stride + i * query_stride + j], strides in elements).
+ * Pass 2 of the reference's split-row scheme (bits_knn.cu:170-183) and the merge step of
+ * the database-sharded search (lists = number of shards). lists * k <= 65536. */
+int bitsknn_merge(const float* d_cand_dist, const int32_t* d_cand_idx, int64_t list_stride,
+                  int64_t query_stride, int64_t q, int lists, int k, float* d_out_dist,
+                  int32_t* d_out_idx, bitsknn_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Squared-L2 distance matrix, GEMM form.
+ * Replaces magma_distance::compute / magma_partial_distance::compute
+ * (src/distance/magma_distance.cu:73-103) and run_abstract_gemm<Ops>
+ * (include/bits/distance/abstract_gemm.cuh:730-755).
+ *
+ *   d_points   float32[n][dim] row-major,  d_queries float32[q][dim] row-major
+ *   d_dist     float32[q][ld] row-major, ld >= n
+ *   mode       BITSKNN_L2_EXACT    sum_d fmaf(x-y, x-y, acc), dims ascending (l2_ops)
+ *              BITSKNN_L2_PARTIAL  |x|^2 - 2 x.y, FMA chains in dim order (partial_l2_ops);
+ *                                  the query norm is NOT added, as in the reference
+ *              BITSKNN_L2_TF32 / BITSKNN_L2_BF16  tensor-core modes (tcgen05, TMEM
+ *                                  accumulators): |x|^2 + |y|^2 - 2 x.y with the dot product in
+ *                                  reduced input precision and FP32 accumulation
+ * Tensor-core modes need a workspace of bitsknn_l2_workspace_bytes(n, q, dim, mode). */
+enum bitsknn_l2_mode
+{
+    BITSKNN_L2_EXACT = 0,
+    BITSKNN_L2_PARTIAL = 1,
+    BITSKNN_L2_TF32 = 2,
+    BITSKNN_L2_BF16 = 3
+};
+size_t bitsknn_l2_workspace_bytes(int64_t n, int64_t q, int dim, int mode);
+int bitsknn_l2(const float* d_points, const float* d_queries, int64_t n, int64_t q, int dim, int mode,
+               float* d_dist, int64_t ld, void* d_workspace, size_t workspace_bytes,
+               bitsknn_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------
+ * `bits-fused`: distances computed tile by tile on chip and fed straight into the top-k;
+ * the q x n matrix is never written.  Replaces fused_cache_knn::selection /
+ * fused_cache::run / launch_fused_cache (src/topk/singlepass/fused_cache_knn.cu:29-216,
+ * include/bits/topk/singlepass/fused_cache_kernel.hpp:35-36).
+ *
+ *   mode        BITSKNN_L2_PARTIAL (FP32 FFMA, bit-exact with the reference's fused kernel:
+ *               reported distances are |x|^2 - 2 x.y) or BITSKNN_L2_EXACT
+ *   k           1 <= k <= BITSKNN_FUSED_MAX_K
+ *   index_base  added to every reported index (shard base of a sharded database)
+ * --------------------------------------------------------------------------------------- */
+int bitsknn_fused(const float* d_points, const float* d_queries, int64_t n, int64_t q, int dim, int k,
+                  int mode, int32_t index_base, float* d_out_dist, int32_t* d_out_idx,
+                  bitsknn_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* BITSKNN_H_ */

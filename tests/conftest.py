@@ -18,3 +18,21 @@ def oracle():
     from oracle import oracle as mod
     mod.build()
     return mod
+
+
+@pytest.fixture(scope="session")
+def bk():
+    """The Python access layer of the C-ABI library (raises if the library is not built)."""
+    import __graft_entry__ as entry
+    pkg = entry.load_package()
+    pkg.lib()
+    return pkg
+
+
+@pytest.fixture(scope="session")
+def cuda():
+    import torch
+    if not torch.cuda.is_available():
+        pytest.fail("a test marked gpu was started without a CUDA device")
+    torch.cuda.set_device(0)
+    return torch.device("cuda:0")
