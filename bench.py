@@ -67,12 +67,18 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
             return
         self.thread = threading.Thread(target=self._pump, daemon=True)
         self.thread.start()
+
+    def wait_first_sample(self, limit_s=3.0):
+        t_end = time.perf_counter() + limit_s
+        while self.proc is not None and not self.lines and time.perf_counter() < t_end:
+            time.sleep(0.02)
+        self.lines.clear()
 
     def _pump(self):
         for line in self.proc.stdout:
@@ -244,12 +250,19 @@ def main():
         return float(t.item())
 
     # ---- resident-input throughput (`value`) and the kernel time for the roofline ----------
-    for _ in range(args.warmup):
-        step()
-    barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+        sampler.wait_first_sample()
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    # keep the GPU under the same load a little longer so that the clock sampler (20 ms period)
+    # sees the clocks this workload settles at; still untimed
+    t_end = time.perf_counter() + 0.4
+    while time.perf_counter() < t_end:
+        step()
+        torch.cuda.synchronize()
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(2 * args.steps + 2)]
     barrier()
     ev[-2].record()

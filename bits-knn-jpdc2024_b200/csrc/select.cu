@@ -99,7 +99,7 @@ struct select_block
             cx[r] = in ? buf_x[s] : PAD_IDX;
         }
         __syncthreads(); // the buffer now doubles as exchange scratch of the networks
-        block_fold<THREADS, IPT>(ld, lx, cd, cx, buf_d, buf_x);
+        block_fold<THREADS, IPT>(ld, lx, cd, cx, buf_d, buf_x, tid);
 #pragma unroll
         for (int r = 0; r < IPT; ++r)
         {
@@ -142,21 +142,20 @@ struct select_block
         return cnt;
     }
 
-    // Warp-inclusive prefix sum of `cnt`.
-    static __device__ __forceinline__ int warp_scan(int cnt)
+    // Slot offsets of this lane's survivors inside the warp's allocation: one ballot per vector
+    // component, no dependent shuffle chain.  Returns the warp's total.
+    static __device__ __forceinline__ int warp_slots(const bool (&pr)[4], int (&off)[4])
     {
-        const int lane = threadIdx.x & 31;
-        int incl = cnt;
+        const unsigned below = (1U << (threadIdx.x & 31)) - 1U;
+        int total = 0;
 #pragma unroll
-        for (int o = 1; o < 32; o <<= 1)
+        for (int j = 0; j < 4; ++j)
         {
-            const int t = __shfl_up_sync(FULL_MASK, incl, o);
-            if (lane >= o)
-            {
-                incl += t;
-            }
+            const unsigned b = __ballot_sync(FULL_MASK, pr[j]);
+            off[j] = total + __popc(b & below);
+            total += __popc(b);
         }
-        return incl;
+        return total;
     }
 
     // Optimistic insertion of one 4-vector (whole warp): survivors beyond the capacity are
@@ -166,32 +165,50 @@ struct select_block
         float dv[4];
         int lab[4];
         bool pr[4];
-        const int cnt = filter4(val, live, e0, dv, lab, pr);
-        const int incl = warp_scan(cnt);
-        const int total = __shfl_sync(FULL_MASK, incl, 31);
+        int off[4];
+        filter4(val, live, e0, dv, lab, pr);
+        const int total = warp_slots(pr, off);
         if (total == 0)
         {
             return;
         }
-        const int lane = threadIdx.x & 31;
         int base = 0;
-        if (lane == 31)
+        if ((threadIdx.x & 31) == 0)
         {
             base = atomicAdd(inc, total);
         }
-        base = __shfl_sync(FULL_MASK, base, 31);
-        int pos = count0 + base + incl - cnt;
+        base = count0 + __shfl_sync(FULL_MASK, base, 0);
 #pragma unroll
         for (int j = 0; j < 4; ++j)
         {
-            if (pr[j])
+            const int pos = base + off[j];
+            if (pr[j] && pos < L)
             {
-                if (pos < L)
+                buf_d[pos] = dv[j];
+                buf_x[pos] = lab[j];
+            }
+        }
+    }
+
+    // Optimistic insertion by a single lane (no warp cooperation): used when hits are sparse.
+    __device__ __forceinline__ void insert_lane(const float4& val, int e0, int count0, int* inc)
+    {
+        const float dv[4] = {val.x, val.y, val.z, val.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+        {
+            if (dv[j] <= r_d)
+            {
+                const int lab = label_of(e0 + j);
+                if (pair_lt(dv[j], lab, r_d, r_x))
                 {
-                    buf_d[pos] = dv[j];
-                    buf_x[pos] = lab[j];
+                    const int pos = count0 + atomicAdd(inc, 1);
+                    if (pos < L)
+                    {
+                        buf_d[pos] = dv[j];
+                        buf_x[pos] = lab;
+                    }
                 }
-                ++pos;
             }
         }
     }
@@ -217,21 +234,20 @@ struct select_block
             float dv[4];
             int lab[4];
             bool pr[4];
-            const int cnt = filter4(val, live, e_base + 4 * v, dv, lab, pr);
-            const int incl = warp_scan(cnt);
-            const int total = __shfl_sync(FULL_MASK, incl, 31);
+            int off[4];
+            filter4(val, live, e_base + 4 * v, dv, lab, pr);
+            const int total = warp_slots(pr, off);
             int base = 0;
-            if (lane == 31 && total > 0)
+            if (lane == 0 && total > 0)
             {
                 base = atomicAdd(&ctrl->count, total);
             }
-            base = __shfl_sync(FULL_MASK, base, 31);
-            int pos = base + incl - cnt;
+            base = __shfl_sync(FULL_MASK, base, 0);
             int ps[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j)
             {
-                ps[j] = pr[j] ? pos++ : -1;
+                ps[j] = pr[j] ? base + off[j] : -1;
             }
             while (true)
             {
@@ -272,6 +288,7 @@ __global__ void __launch_bounds__(THREADS) select_kernel(const select_params p)
     using block_t = select_block<THREADS, IPT>;
     constexpr int L = block_t::L;
     constexpr int UNROLL = 4;
+    constexpr int SPARSE_LANES = 6; // up to this many lanes with a candidate: per-lane insertion
 
     extern __shared__ __align__(128) unsigned char smem[];
     const int tid = threadIdx.x;
@@ -312,8 +329,7 @@ __global__ void __launch_bounds__(THREADS) select_kernel(const select_params p)
     blk.r_d = INFINITY;
     blk.r_x = PAD_IDX;
 
-    auto issue = [&](int c) {
-        const int st = c % NST;
+    auto issue = [&](int c, int st) {
         const int floats = (mid - c * CH) < CH ? (mid - c * CH) : CH;
         ptx::mbar_expect_tx(&bars[st], static_cast<uint32_t>(floats) * 4U);
         ptx::bulk_g2s(stage_base + static_cast<size_t>(st) * CH, rowp + h + static_cast<int64_t>(c) * CH,
@@ -337,7 +353,7 @@ __global__ void __launch_bounds__(THREADS) select_kernel(const select_params p)
     {
         for (int c = 0; c < NST && c < nchunks; ++c)
         {
-            issue(c);
+            issue(c, c);
         }
     }
 
@@ -360,16 +376,19 @@ __global__ void __launch_bounds__(THREADS) select_kernel(const select_params p)
     bool timed_out = false;
     int c = 0;
 
+    int st = 0;          // stage of chunk c            (c % NST without a division)
+    uint32_t phase = 0;  // parity of that stage's use  ((c / NST) & 1)
+    int i3 = 0;          // c % 3
+
     for (; c < nchunks; ++c)
     {
-        const int st = c % NST;
         const float4* sv = reinterpret_cast<const float4*>(stage_base + static_cast<size_t>(st) * CH);
         const int floats = (mid - c * CH) < CH ? (mid - c * CH) : CH;
         const int nv = floats >> 2;
         const int e_base = h + c * CH;
-        int* inc = &blk.ctrl->inc[c % 3];
+        int* inc = &blk.ctrl->inc[i3];
 
-        if (!ptx::mbar_wait_bounded(&bars[st], static_cast<uint32_t>((c / NST) & 1)))
+        if (!ptx::mbar_wait_bounded(&bars[st], phase))
         {
             timed_out = true;
         }
@@ -377,26 +396,66 @@ __global__ void __launch_bounds__(THREADS) select_kernel(const select_params p)
         bool redo = go_slow;
         if (!go_slow)
         {
-            for (int vb = 0; vb < nv; vb += THREADS * UNROLL)
+            int vb = 0;
+            // groups of UNROLL vectors per thread, no bounds checks; one vote per group
+            for (; vb + THREADS * UNROLL <= nv; vb += THREADS * UNROLL)
             {
                 float4 val[UNROLL];
-                bool live[UNROLL];
 #pragma unroll
                 for (int u = 0; u < UNROLL; ++u)
                 {
-                    const int v = vb + u * THREADS + tid;
-                    live[u] = v < nv;
-                    val[u] = live[u] ? sv[v] : make_float4(INFINITY, INFINITY, INFINITY, INFINITY);
+                    val[u] = sv[vb + u * THREADS + tid];
                 }
+                float mn[UNROLL];
 #pragma unroll
                 for (int u = 0; u < UNROLL; ++u)
                 {
-                    const float mn = fminf(fminf(val[u].x, val[u].y), fminf(val[u].z, val[u].w));
-                    const bool hit = live[u] && mn <= blk.r_d;
-                    if (__any_sync(FULL_MASK, hit))
+                    mn[u] = fminf(fminf(val[u].x, val[u].y), fminf(val[u].z, val[u].w));
+                }
+                const float mall = fminf(fminf(mn[0], mn[1]), fminf(mn[2], mn[3]));
+                const unsigned hitters = __ballot_sync(FULL_MASK, mall <= blk.r_d);
+                if (hitters == 0)
+                {
+                    continue;
+                }
+                if (__popc(hitters) <= SPARSE_LANES)
+                {
+                    // few lanes saw a candidate: they take slots one by one, the others idle
+                    if (mall <= blk.r_d)
                     {
-                        blk.insert_fast(val[u], hit, e_base + 4 * (vb + u * THREADS + tid), count0, inc);
+#pragma unroll
+                        for (int u = 0; u < UNROLL; ++u)
+                        {
+                            if (mn[u] <= blk.r_d)
+                            {
+                                blk.insert_lane(val[u], e_base + 4 * (vb + u * THREADS + tid), count0, inc);
+                            }
+                        }
                     }
+                }
+                else
+                {
+#pragma unroll
+                    for (int u = 0; u < UNROLL; ++u)
+                    {
+                        const bool hit = mn[u] <= blk.r_d;
+                        if (__any_sync(FULL_MASK, hit))
+                        {
+                            blk.insert_fast(val[u], hit, e_base + 4 * (vb + u * THREADS + tid), count0, inc);
+                        }
+                    }
+                }
+            }
+            // ragged end of the last stage
+            for (; vb < nv; vb += THREADS)
+            {
+                const int v = vb + tid;
+                const bool live = v < nv;
+                const float4 val = live ? sv[v] : make_float4(INFINITY, INFINITY, INFINITY, INFINITY);
+                const bool hit = live && fminf(fminf(val.x, val.y), fminf(val.z, val.w)) <= blk.r_d;
+                if (__any_sync(FULL_MASK, hit))
+                {
+                    blk.insert_fast(val, hit, e_base + 4 * v, count0, inc);
                 }
             }
         }
@@ -420,7 +479,7 @@ __global__ void __launch_bounds__(THREADS) select_kernel(const select_params p)
         }
         if (tid == 0)
         {
-            blk.ctrl->inc[(c + 2) % 3] = 0; // last read before this barrier, next used after the next one
+            blk.ctrl->inc[i3 == 0 ? 2 : i3 - 1] = 0; // slot of stage c+2: last read before this barrier
         }
         if (redo)
         {
@@ -436,7 +495,13 @@ __global__ void __launch_bounds__(THREADS) select_kernel(const select_params p)
         // every thread has passed a barrier after its last read of this stage
         if (tid == 0 && c + NST < nchunks)
         {
-            issue(c + NST);
+            issue(c + NST, st);
+        }
+        i3 = i3 == 2 ? 0 : i3 + 1;
+        if (++st == NST)
+        {
+            st = 0;
+            phase ^= 1U;
         }
     }
 
@@ -518,7 +583,7 @@ __global__ void __launch_bounds__(THREADS)
                 cx[r] = cand_idx[at];
             }
         }
-        block_fold<THREADS, IPT>(ld, lx, cd, cx, sd, sx);
+        block_fold<THREADS, IPT>(ld, lx, cd, cx, sd, sx, tid);
     }
 #pragma unroll
     for (int r = 0; r < IPT; ++r)
@@ -632,7 +697,7 @@ void fill_stream_config(select_params& p)
     stage_bytes = (stage_bytes / (16 * SELECT_THREADS)) * (16 * SELECT_THREADS);
     stage_bytes = std::max(stage_bytes, 16 * SELECT_THREADS);
     p.stage_floats = stage_bytes / 4;
-    p.stages = std::min(std::max(tuning_value("select.stages", 4), 2), MAX_STAGES);
+    p.stages = std::min(std::max(tuning_value("select.stages", 3), 2), MAX_STAGES);
 }
 
 } // namespace

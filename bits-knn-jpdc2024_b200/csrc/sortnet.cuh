@@ -1,6 +1,7 @@
 // Block-wide bitonic networks over a register-resident array of (distance, index) pairs.
 //
-// Data arrangement: THREADS threads hold IPT pairs each; pair r of thread t is element
+// Data arrangement: a group of THREADS threads (a whole block, or one warp when THREADS == 32;
+// `tid` is the thread's rank in the group) holds IPT pairs each; pair r of thread t is element
 // e = t * IPT + r of a block-wide array of N = THREADS * IPT elements ("blocked"
 // arrangement, the one the reference keeps its sorted lists in:
 // include/bits/topk/bitonic_sort_regs.cuh:411).  A compare-exchange with partner e ^ J is
@@ -23,9 +24,8 @@ namespace bitsknn
 // no element has the bit, so the whole array goes one way.
 // `sd`/`sx` are shared-memory scratch arrays of N floats / ints (used only when J >= 32*IPT).
 template <int THREADS, int IPT, int K, int J>
-__device__ __forceinline__ void cx_step(float (&d)[IPT], int (&x)[IPT], bool desc, float* sd, int* sx)
+__device__ __forceinline__ void cx_step(float (&d)[IPT], int (&x)[IPT], bool desc, float* sd, int* sx, int tid)
 {
-    const int tid = threadIdx.x;
     if constexpr (J < IPT)
     {
 #pragma unroll
@@ -103,12 +103,13 @@ __device__ __forceinline__ void cx_step(float (&d)[IPT], int (&x)[IPT], bool des
 template <int THREADS, int IPT, int K, int J>
 struct merge_steps
 {
-    static __device__ __forceinline__ void run(float (&d)[IPT], int (&x)[IPT], bool desc, float* sd, int* sx)
+    static __device__ __forceinline__ void run(float (&d)[IPT], int (&x)[IPT], bool desc, float* sd, int* sx,
+                                               int tid)
     {
-        cx_step<THREADS, IPT, K, J>(d, x, desc, sd, sx);
+        cx_step<THREADS, IPT, K, J>(d, x, desc, sd, sx, tid);
         if constexpr (J > 1)
         {
-            merge_steps<THREADS, IPT, K, J / 2>::run(d, x, desc, sd, sx);
+            merge_steps<THREADS, IPT, K, J / 2>::run(d, x, desc, sd, sx, tid);
         }
     }
 };
@@ -117,28 +118,29 @@ struct merge_steps
 template <int THREADS, int IPT, int K>
 struct sort_phases
 {
-    static __device__ __forceinline__ void run(float (&d)[IPT], int (&x)[IPT], bool desc, float* sd, int* sx)
+    static __device__ __forceinline__ void run(float (&d)[IPT], int (&x)[IPT], bool desc, float* sd, int* sx,
+                                               int tid)
     {
         if constexpr (K > 2)
         {
-            sort_phases<THREADS, IPT, K / 2>::run(d, x, desc, sd, sx);
+            sort_phases<THREADS, IPT, K / 2>::run(d, x, desc, sd, sx, tid);
         }
-        merge_steps<THREADS, IPT, K, K / 2>::run(d, x, desc, sd, sx);
+        merge_steps<THREADS, IPT, K, K / 2>::run(d, x, desc, sd, sx, tid);
     }
 };
 
 // Sorts the block-wide array (ascending, or descending when `desc`).
 template <int THREADS, int IPT>
-__device__ __forceinline__ void block_sort(float (&d)[IPT], int (&x)[IPT], bool desc, float* sd, int* sx)
+__device__ __forceinline__ void block_sort(float (&d)[IPT], int (&x)[IPT], bool desc, float* sd, int* sx, int tid)
 {
-    sort_phases<THREADS, IPT, THREADS * IPT>::run(d, x, desc, sd, sx);
+    sort_phases<THREADS, IPT, THREADS * IPT>::run(d, x, desc, sd, sx, tid);
 }
 
 // Sorts a block-wide BITONIC array ascending (the last phase of the sort alone).
 template <int THREADS, int IPT>
-__device__ __forceinline__ void block_merge_bitonic(float (&d)[IPT], int (&x)[IPT], float* sd, int* sx)
+__device__ __forceinline__ void block_merge_bitonic(float (&d)[IPT], int (&x)[IPT], float* sd, int* sx, int tid)
 {
-    merge_steps<THREADS, IPT, THREADS * IPT, THREADS * IPT / 2>::run(d, x, false, sd, sx);
+    merge_steps<THREADS, IPT, THREADS * IPT, THREADS * IPT / 2>::run(d, x, false, sd, sx, tid);
 }
 
 // Folds N unsorted candidates (cd, cx) into the ascending list (ld, lx): sorts the candidates
@@ -147,9 +149,9 @@ __device__ __forceinline__ void block_merge_bitonic(float (&d)[IPT], int (&x)[IP
 // shared_buffer::merge (include/bits/topk/singlepass/detail/bits_kernel.cuh:145-199).
 template <int THREADS, int IPT>
 __device__ __forceinline__ void block_fold(float (&ld)[IPT], int (&lx)[IPT], float (&cd)[IPT], int (&cx)[IPT],
-                                           float* sd, int* sx)
+                                           float* sd, int* sx, int tid)
 {
-    block_sort<THREADS, IPT>(cd, cx, true, sd, sx);
+    block_sort<THREADS, IPT>(cd, cx, true, sd, sx, tid);
 #pragma unroll
     for (int r = 0; r < IPT; ++r)
     {
@@ -159,7 +161,7 @@ __device__ __forceinline__ void block_fold(float (&ld)[IPT], int (&lx)[IPT], flo
             lx[r] = cx[r];
         }
     }
-    block_merge_bitonic<THREADS, IPT>(ld, lx, sd, sx);
+    block_merge_bitonic<THREADS, IPT>(ld, lx, sd, sx, tid);
 }
 
 } // namespace bitsknn
