@@ -259,10 +259,10 @@ def main():
     barrier()
     # keep the GPU under the same load a little longer so that the clock sampler (20 ms period)
     # sees the clocks this workload settles at; still untimed
-    t_end = time.perf_counter() + 0.4
-    while time.perf_counter() < t_end:
+    # (a fixed count, identical on every rank: each step holds collectives when N > 1)
+    for _ in range(300):
         step()
-        torch.cuda.synchronize()
+    barrier()
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(2 * args.steps + 2)]
     barrier()
     ev[-2].record()
