@@ -222,19 +222,17 @@ def main():
     out_d = torch.empty((q, k), dtype=torch.float32, device=dev)
     out_i = torch.empty((q, k), dtype=torch.int32, device=dev)
     if world > 1:
-        all_d = torch.empty((world, q, k), dtype=torch.float32, device=dev)
-        all_i = torch.empty((world, q, k), dtype=torch.int32, device=dev)
         fin_d = torch.empty((q, k), dtype=torch.float32, device=dev)
         fin_i = torch.empty((q, k), dtype=torch.int32, device=dev)
 
     launches_per_step = 1 if world == 1 else 2
+    from importlib import import_module
+    search = import_module(entry.PKG_NAME + ".sharded").ShardedSearch(bk, rank, world)
 
     def step(src=matrix):
-        bk.select(src, k, label_offsets=offsets, out=(out_d, out_i))
-        if world > 1:
-            dist_pg.all_gather_into_tensor(all_d, out_d)
-            dist_pg.all_gather_into_tensor(all_i, out_i)
-            bk.merge(all_d, all_i, out=(fin_d, fin_i))
+        # local selection with global labels, then (N > 1) NCCL all-gather + merge kernel
+        search.select(src, k, rank * n, offsets=offsets, local_out=(out_d, out_i),
+                      out=None if world == 1 else (fin_d, fin_i))
 
     def barrier():
         torch.cuda.synchronize()
@@ -271,9 +269,7 @@ def main():
         bk.select(matrix, k, label_offsets=offsets, out=(out_d, out_i))
         ev[2 * s + 1].record()
         if world > 1:
-            dist_pg.all_gather_into_tensor(all_d, out_d)
-            dist_pg.all_gather_into_tensor(all_i, out_i)
-            bk.merge(all_d, all_i, out=(fin_d, fin_i))
+            search._exchange_and_merge(out_d, out_i, out=(fin_d, fin_i))
     ev[-1].record()
     barrier()
     clocks = sampler.stop() if rank == 0 else None

@@ -1,0 +1,345 @@
+// Algorithm objects of the registry: thin adapters from the reference's plug-in API to the
+// C ABI.  Each phase ends with a stream synchronisation so that host timers around the
+// phases measure what the reference's do (src/main.cpp:366-408, src/knn.cpp:24-29,
+// src/topk/singlepass/bits_knn.cu:95,113).
+#include <algorithm>
+#include <cmath>
+#include <cstdio>
+#include <iostream>
+
+#include "bitsknn/knn.hpp"
+
+namespace bits
+{
+
+void cuda_check(cudaError_t status, const char* what, const char* file, int line)
+{
+    if (status != cudaSuccess)
+    {
+        std::cerr << file << ":" << line << " " << cudaGetErrorName(status) << ": " << cudaGetErrorString(status)
+                  << "\n\t" << what << '\n';
+        throw std::runtime_error{"CUDA error."};
+    }
+}
+
+void abi_check(int status)
+{
+    if (status != BITSKNN_OK)
+    {
+        throw std::runtime_error{bitsknn_last_error_string()};
+    }
+}
+
+// events are created on first use, so that building the registry needs no device
+transfer_timer::transfer_timer() = default;
+
+transfer_timer::~transfer_timer()
+{
+    if (begin_ != nullptr)
+    {
+        cudaEventDestroy(begin_);
+    }
+    if (end_ != nullptr)
+    {
+        cudaEventDestroy(end_);
+    }
+}
+
+void transfer_timer::begin()
+{
+    if (begin_ == nullptr)
+    {
+        BITS_CUCH(cudaEventCreate(&begin_));
+        BITS_CUCH(cudaEventCreate(&end_));
+    }
+    BITS_CUCH(cudaEventRecord(begin_, nullptr));
+}
+
+void transfer_timer::end()
+{
+    BITS_CUCH(cudaEventRecord(end_, nullptr));
+    BITS_CUCH(cudaEventSynchronize(end_));
+    measured_ = true;
+}
+
+float transfer_timer::seconds() const
+{
+    if (!measured_)
+    {
+        return 0;
+    }
+    float ms = 0;
+    BITS_CUCH(cudaEventElapsedTime(&ms, begin_, end_));
+    return ms / 1e3F;
+}
+
+namespace
+{
+
+// host transpose of a cols x rows (column-major view of rows x cols) matrix to row major
+std::vector<float> to_row_major(const float* src, std::size_t rows, std::size_t cols)
+{
+    std::vector<float> out(rows * cols);
+    for (std::size_t c = 0; c < cols; ++c)
+    {
+        for (std::size_t r = 0; r < rows; ++r)
+        {
+            out[r * cols + c] = src[c * rows + r];
+        }
+    }
+    return out;
+}
+
+inline bool pair_less(const distance_pair& a, const distance_pair& b)
+{
+    return a.distance < b.distance || (a.distance == b.distance && a.index < b.index);
+}
+
+} // namespace
+
+void cuda_distance::prepare(const knn_args& args)
+{
+    args_ = args;
+    dist_gpu_.release();
+    points_gpu_.release();
+    queries_gpu_.release();
+    points_gpu_ = device_buffer<float>{args_.point_count * args_.dim};
+    queries_gpu_ = device_buffer<float>{args_.query_count * args_.dim};
+    if (needs_matrix_)
+    {
+        dist_gpu_ = device_buffer<float>{args_.query_count * args_.point_count};
+    }
+    // the device always holds row-major inputs; a column-major host matrix is transposed here
+    std::vector<float> tmp_points;
+    std::vector<float> tmp_queries;
+    const float* points = args_.points;
+    const float* queries = args_.queries;
+    if (args_.points_layout == matrix_layout::column_major)
+    {
+        tmp_points = to_row_major(points, args_.point_count, args_.dim);
+        points = tmp_points.data();
+    }
+    if (args_.queries_layout == matrix_layout::column_major)
+    {
+        tmp_queries = to_row_major(queries, args_.query_count, args_.dim);
+        queries = tmp_queries.data();
+    }
+    timer_.begin();
+    BITS_CUCH(cudaMemcpyAsync(points_gpu_.data(), points, points_gpu_.size() * sizeof(float), cudaMemcpyHostToDevice,
+                              nullptr));
+    BITS_CUCH(cudaMemcpyAsync(queries_gpu_.data(), queries, queries_gpu_.size() * sizeof(float),
+                              cudaMemcpyHostToDevice, nullptr));
+    timer_.end();
+    if (needs_matrix_)
+    {
+        BITS_CUCH(cudaMemsetAsync(dist_gpu_.data(), 0, dist_gpu_.size() * sizeof(float), nullptr));
+    }
+    BITS_CUCH(cudaStreamSynchronize(nullptr));
+}
+
+const std::vector<float>& cuda_distance::matrix_cpu()
+{
+    dist_cpu_.resize(args_.query_count * args_.point_count);
+    BITS_CUCH(cudaMemcpy(dist_cpu_.data(), dist_gpu_.data(), dist_cpu_.size() * sizeof(float),
+                         cudaMemcpyDeviceToHost));
+    return dist_cpu_;
+}
+
+void gemm_distance::compute()
+{
+    const auto n = static_cast<std::int64_t>(args_.point_count);
+    const auto q = static_cast<std::int64_t>(args_.query_count);
+    const int dim = static_cast<int>(args_.dim);
+    const std::size_t need = bitsknn_l2_workspace_bytes(n, q, dim, mode_);
+    if (need > workspace_.size())
+    {
+        workspace_ = device_buffer<unsigned char>{need};
+    }
+    abi_check(bitsknn_l2(points_gpu_.data(), queries_gpu_.data(), n, q, dim, mode_, dist_gpu_.data(), n,
+                         workspace_.data(), workspace_.size(), nullptr));
+}
+
+std::unique_ptr<cuda_distance> knn::default_distance() const
+{
+    // the reference's default for every algorithm is its full-L2 GEMM-form distance
+    // (src/knn.cpp:16-20)
+    return std::make_unique<gemm_distance>(BITSKNN_L2_EXACT, "magma-dist");
+}
+
+void knn::initialize(const knn_args& args)
+{
+    args_ = args;
+    args_.dist_layout = matrix_layout::row_major;
+    if (dist_impl_ == nullptr)
+    {
+        dist_impl_ = default_distance();
+    }
+    dist_impl_->prepare(args_);
+}
+
+void knn::distances()
+{
+    dist_impl_->compute();
+    BITS_CUCH(cudaStreamSynchronize(nullptr));
+}
+
+void cuda_knn::initialize(const knn_args& args)
+{
+    knn::initialize(args);
+    out_dist_gpu_ = device_buffer<float>{query_count() * k()};
+    out_label_gpu_ = device_buffer<std::int32_t>{query_count() * k()};
+}
+
+std::vector<distance_pair> cuda_knn::finish()
+{
+    if (no_output_)
+    {
+        out_timer_.begin();
+        out_timer_.end();
+        return {};
+    }
+    const std::size_t count = query_count() * k();
+    std::vector<float> dist(count);
+    std::vector<std::int32_t> label(count);
+    out_timer_.begin();
+    BITS_CUCH(cudaMemcpyAsync(dist.data(), out_dist_gpu_.data(), count * sizeof(float), cudaMemcpyDeviceToHost, nullptr));
+    BITS_CUCH(cudaMemcpyAsync(label.data(), out_label_gpu_.data(), count * sizeof(std::int32_t),
+                              cudaMemcpyDeviceToHost, nullptr));
+    out_timer_.end();
+    std::vector<distance_pair> result(count);
+    for (std::size_t i = 0; i < count; ++i)
+    {
+        result[i] = distance_pair{dist[i], label[i]};
+    }
+    return result;
+}
+
+void bits_knn::selection()
+{
+    const auto n = static_cast<std::int64_t>(point_count());
+    abi_check(bitsknn_select(in_dist_gpu(), n, nullptr, 0, nullptr, static_cast<std::int64_t>(query_count()), n,
+                             static_cast<int>(k()), out_dist_gpu(), out_label_gpu(), nullptr));
+    BITS_CUCH(cudaStreamSynchronize(nullptr));
+}
+
+void bits_sq_knn::initialize(const knn_args& args)
+{
+    cuda_knn::initialize(args);
+    const int deg = static_cast<int>(std::max<std::size_t>(args_.deg, 1));
+    workspace_ = device_buffer<unsigned char>{bitsknn_select_split_workspace_bytes(
+        static_cast<std::int64_t>(query_count()), static_cast<int>(k()), deg)};
+}
+
+void bits_sq_knn::selection()
+{
+    const auto n = static_cast<std::int64_t>(point_count());
+    const int deg = static_cast<int>(std::max<std::size_t>(args_.deg, 1));
+    abi_check(bitsknn_select_split(in_dist_gpu(), n, nullptr, static_cast<std::int64_t>(query_count()), n,
+                                   static_cast<int>(k()), deg, workspace_.data(), workspace_.size(), out_dist_gpu(),
+                                   out_label_gpu(), nullptr));
+    BITS_CUCH(cudaStreamSynchronize(nullptr));
+}
+
+void fused_knn::selection()
+{
+    abi_check(bitsknn_fused(dist_impl_->points_gpu(), dist_impl_->queries_gpu(), static_cast<std::int64_t>(point_count()),
+                            static_cast<std::int64_t>(query_count()), static_cast<int>(dim()), static_cast<int>(k()),
+                            BITSKNN_L2_PARTIAL, 0, out_dist_gpu(), out_label_gpu(), nullptr));
+    BITS_CUCH(cudaStreamSynchronize(nullptr));
+}
+
+void serial_knn::distances()
+{
+    knn::distances();
+    const auto& matrix = dist_impl_->matrix_cpu();
+    dist_.resize(matrix.size());
+    for (std::size_t i = 0; i < query_count(); ++i)
+    {
+        for (std::size_t j = 0; j < point_count(); ++j)
+        {
+            dist_[i * point_count() + j] = distance_pair{matrix[i * point_count() + j], static_cast<std::int32_t>(j)};
+        }
+    }
+}
+
+void serial_knn::selection()
+{
+    for (std::size_t i = 0; i < query_count(); ++i)
+    {
+        const auto begin = dist_.begin() + static_cast<std::ptrdiff_t>(i * point_count());
+        std::sort(begin, begin + static_cast<std::ptrdiff_t>(point_count()), pair_less);
+    }
+}
+
+std::vector<distance_pair> serial_knn::finish()
+{
+    std::vector<distance_pair> result(query_count() * k());
+    for (std::size_t i = 0; i < query_count(); ++i)
+    {
+        for (std::size_t j = 0; j < k(); ++j)
+        {
+            result[i * k() + j] = j < point_count()
+                                      ? dist_[i * point_count() + j]
+                                      : distance_pair{INFINITY, static_cast<std::int32_t>(j)};
+        }
+    }
+    return result;
+}
+
+void parallel_knn::distances()
+{
+    knn::distances();
+    matrix_ = &dist_impl_->matrix_cpu();
+}
+
+void parallel_knn::selection()
+{
+    const std::size_t n = point_count();
+    const std::size_t kk = std::min(k(), n);
+    result_.assign(query_count() * k(), distance_pair{INFINITY, 0});
+#pragma omp parallel for
+    for (std::size_t i = 0; i < query_count(); ++i)
+    {
+        const float* row = matrix_->data() + i * n;
+        const auto begin = result_.begin() + static_cast<std::ptrdiff_t>(i * k());
+        const auto end = begin + static_cast<std::ptrdiff_t>(kk);
+        for (std::size_t j = 0; j < kk; ++j)
+        {
+            begin[static_cast<std::ptrdiff_t>(j)] = distance_pair{row[j], static_cast<std::int32_t>(j)};
+        }
+        std::make_heap(begin, end, pair_less);
+        for (std::size_t j = kk; j < n; ++j)
+        {
+            if (begin->distance > row[j])
+            {
+                std::pop_heap(begin, end, pair_less);
+                *(end - 1) = distance_pair{row[j], static_cast<std::int32_t>(j)};
+                std::push_heap(begin, end, pair_less);
+            }
+        }
+        std::sort(begin, end, pair_less);
+        for (std::size_t j = kk; j < k(); ++j)
+        {
+            begin[static_cast<std::ptrdiff_t>(j)] = distance_pair{INFINITY, static_cast<std::int32_t>(j)};
+        }
+    }
+}
+
+std::vector<std::unique_ptr<knn>> make_registry()
+{
+    std::vector<std::unique_ptr<knn>> algorithms;
+    algorithms.push_back(std::make_unique<serial_knn>());
+    algorithms.push_back(std::make_unique<parallel_knn>());
+    algorithms.push_back(std::make_unique<bits_knn>("bits"));
+    algorithms.push_back(std::make_unique<bits_knn>("bits-prefetch"));
+    algorithms.push_back(std::make_unique<bits_sq_knn>());
+    algorithms.push_back(std::make_unique<fused_knn>("fused-cache"));
+    algorithms.push_back(std::make_unique<fused_knn>("bits-fused"));
+    algorithms.push_back(std::make_unique<dist_runner>(BITSKNN_L2_EXACT, "magma-dist"));
+    algorithms.push_back(std::make_unique<dist_runner>(BITSKNN_L2_PARTIAL, "magma-part-dist"));
+    algorithms.push_back(std::make_unique<dist_runner>(BITSKNN_L2_TF32, "tc-dist-tf32"));
+    algorithms.push_back(std::make_unique<dist_runner>(BITSKNN_L2_BF16, "tc-dist-bf16"));
+    return algorithms;
+}
+
+} // namespace bits
