@@ -23,6 +23,7 @@ ERR_DEVICE_TIMEOUT = 6
 ERR_UNSUPPORTED_MODE = 7
 
 L2_EXACT, L2_PARTIAL, L2_TF32, L2_BF16 = 0, 1, 2, 3
+STATIC_SCRATCH_BYTES = 8 << 20  # BITSKNN_STATIC_SCRATCH_BYTES
 
 # every symbol include/bitsknn.h declares, with its ctypes signature
 _i64 = ctypes.c_int64
@@ -38,6 +39,7 @@ SIGNATURES = {
     "bitsknn_select": (_int, [_ptr, _i64, _ptr, _i64, _ptr, _i64, _i64, _int, _ptr, _ptr, _ptr]),
     "bitsknn_select_split_workspace_bytes": (_sz, [_i64, _int, _int]),
     "bitsknn_select_split": (_int, [_ptr, _i64, _ptr, _i64, _i64, _int, _int, _ptr, _sz, _ptr, _ptr, _ptr]),
+    "bitsknn_select_split_static": (_int, [_ptr, _i64, _ptr, _i64, _i64, _int, _int, _ptr, _ptr, _ptr]),
     "bitsknn_merge": (_int, [_ptr, _ptr, _i64, _i64, _i64, _int, _int, _ptr, _ptr, _ptr]),
     "bitsknn_l2_workspace_bytes": (_sz, [_i64, _i64, _int, _int]),
     "bitsknn_l2": (_int, [_ptr, _ptr, _i64, _i64, _int, _int, _ptr, _i64, _ptr, _sz, _ptr]),
@@ -151,6 +153,19 @@ def select_split(dist, k, splits=0, label_offsets=None, workspace=None, out=None
                torch.empty((q, k), dtype=torch.int32, device=dist.device))
     _check(lib().bitsknn_select_split(_p(dist), ld, _p(label_offsets), q, n, k, splits, _p(workspace),
                                       workspace.numel(), _p(out[0]), _p(out[1]), _stream()))
+    return out
+
+
+def select_split_static(dist, k, splits, label_offsets=None, out=None):
+    """Split-row selection whose candidate scratch is the library's built-in device array."""
+    import torch
+    _device_check(dist, torch.float32, "dist")
+    q, n = dist.shape
+    ld = dist.stride(0) if q > 1 else n
+    if out is None:
+        raise ValueError("pass the output tensors: this entry point is for callers that do not allocate")
+    _check(lib().bitsknn_select_split_static(_p(dist), ld, _p(label_offsets), q, n, k, splits, _p(out[0]), _p(out[1]),
+                                             _stream()))
     return out
 
 

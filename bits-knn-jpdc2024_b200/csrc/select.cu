@@ -23,6 +23,7 @@
 #include <cmath>
 #include <cstdint>
 #include <limits>
+#include <mutex>
 
 #include "common.cuh"
 #include "ptx.cuh"
@@ -828,6 +829,120 @@ extern "C" int bitsknn_select_split(const float* d_dist, int64_t ld, const int32
         return rc;
     }
     return dispatch_merge(cand_dist, cand_idx, k, static_cast<int64_t>(s) * k, q, s, k, d_out_dist, d_out_idx, cs);
+}
+
+// ---------------------------------------------------------------------------------------
+// Split-row selection for callers that must not allocate device memory.
+//
+// Some hosts of this library cannot call cudaMalloc at the point where they need a search:
+// a plug-in running inside an engine that reserved the whole device for its own pool, code
+// between two latency-critical launches where an allocation would serialise the device, or
+// a process whose memory budget was fixed at start-up.  For them the candidate lists of the
+// two-pass scheme live in a file-scope device array of fixed size that is part of the loaded
+// library image (each GPU that loads the library holds these bytes until the process exits).
+//
+// In host code `g_static_candidates` is only a host-side handle of the symbol, NOT a device
+// address: handing it to a kernel would fault or, on systems where the GPU can reach host
+// memory, silently read and write the wrong bytes.  The device address is looked up once per
+// device with cudaGetSymbolAddress while that device is current, and that pointer is what
+// the kernels get.
+constexpr size_t STATIC_CANDIDATE_BYTES = static_cast<size_t>(BITSKNN_STATIC_SCRATCH_BYTES);
+static __device__ __align__(256) unsigned char g_static_candidates[STATIC_CANDIDATE_BYTES];
+
+namespace
+{
+
+constexpr int MAX_DEVICES = 64;
+std::mutex g_static_mutex;
+void* g_static_ptr[MAX_DEVICES] = {};
+
+// Device address of the static candidate array on the current device (looked up on the first
+// call per device; that first call should therefore happen outside any stream capture).
+int static_candidates(void** out)
+{
+    int device = 0;
+    BITSKNN_CUDA_TRY(cudaGetDevice(&device));
+    if (device < 0 || device >= MAX_DEVICES)
+    {
+        return fail(BITSKNN_ERR_INVALID_ARGUMENT, "device ordinal %d beyond the %d supported", device, MAX_DEVICES);
+    }
+    std::lock_guard<std::mutex> lock{g_static_mutex};
+    if (g_static_ptr[device] == nullptr)
+    {
+        void* ptr = nullptr;
+        BITSKNN_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_static_candidates));
+        g_static_ptr[device] = ptr;
+    }
+    *out = g_static_ptr[device];
+    return BITSKNN_OK;
+}
+
+} // namespace
+
+extern "C" int bitsknn_select_split_static(const float* d_dist, int64_t ld, const int32_t* d_label_offsets,
+                                           int64_t q, int64_t n, int k, int splits, float* d_out_dist,
+                                           int32_t* d_out_idx, bitsknn_stream_t stream)
+{
+    if (const int rc = check_select_args(d_dist, ld, q, n, k, d_out_dist, d_out_idx); rc != BITSKNN_OK)
+    {
+        return rc;
+    }
+    if (splits < 1 || splits > 4096)
+    {
+        return fail(BITSKNN_ERR_INVALID_ARGUMENT, "invalid number of slices per row: %d", splits);
+    }
+    if (static_cast<int64_t>(splits) * k > 65536)
+    {
+        return fail(BITSKNN_ERR_INVALID_ARGUMENT, "slices * k = %lld exceeds 65536", static_cast<long long>(splits) * k);
+    }
+    const size_t need = static_cast<size_t>(q) * static_cast<size_t>(splits) * static_cast<size_t>(k) * 8U;
+    if (need > STATIC_CANDIDATE_BYTES)
+    {
+        return fail(BITSKNN_ERR_WORKSPACE,
+                    "q * splits * k = %lld candidate pairs need %zu bytes; the built-in scratch holds %zu bytes "
+                    "(use bitsknn_select_split with your own workspace for larger problems)",
+                    static_cast<long long>(q) * splits * k, need, STATIC_CANDIDATE_BYTES);
+    }
+    if (q == 0)
+    {
+        return BITSKNN_OK;
+    }
+    void* scratch = nullptr;
+    if (const int rc = static_candidates(&scratch); rc != BITSKNN_OK)
+    {
+        return rc;
+    }
+    // pass 1 overwrites every candidate slot that pass 2 reads (each block stores all k pairs of
+    // its slice, padding included), so nothing in the array has to be cleared between calls
+    auto* cand_dist = static_cast<float*>(scratch);
+    auto* cand_idx = reinterpret_cast<int32_t*>(cand_dist + static_cast<size_t>(q) * splits * k);
+
+    select_params p{};
+    p.dist = d_dist;
+    p.ld = ld;
+    p.labels = nullptr;
+    p.ld_labels = 0;
+    p.label_offsets = d_label_offsets;
+    p.n = n;
+    p.k = k;
+    p.splits = splits;
+    p.slice = (((n + splits - 1) / splits) + 3) & ~static_cast<int64_t>(3);
+    p.out_dist = cand_dist;
+    p.out_idx = cand_idx;
+    p.raw_pad = 1;
+    p.status = device_status_word();
+    if (p.status == nullptr)
+    {
+        return fail(BITSKNN_ERR_CUDA, "CUDA error. cannot resolve the device status word");
+    }
+    fill_stream_config(p);
+    auto cs = static_cast<cudaStream_t>(stream);
+    if (const int rc = dispatch_select(p, q * splits, cs); rc != BITSKNN_OK)
+    {
+        return rc;
+    }
+    return dispatch_merge(cand_dist, cand_idx, k, static_cast<int64_t>(splits) * k, q, splits, k, d_out_dist,
+                          d_out_idx, cs);
 }
 
 extern "C" int bitsknn_merge(const float* d_cand_dist, const int32_t* d_cand_idx, int64_t list_stride,

@@ -93,6 +93,24 @@ int bitsknn_select_split(const float* d_dist, int64_t ld, const int32_t* d_label
                          int64_t n, int k, int splits, void* d_workspace, size_t workspace_bytes,
                          float* d_out_dist, int32_t* d_out_idx, bitsknn_stream_t stream);
 
+/* Split-row selection that allocates nothing (no counterpart in the reference).
+ * For callers that cannot obtain device memory when they need a search -- a plug-in inside an
+ * engine that owns the whole device pool, code on a path where an allocation would stall the
+ * device, a process with a memory budget fixed at start-up.  Same result as
+ * bitsknn_select_split, but the q * splits * k candidate pairs are kept in a fixed array that
+ * is part of the library's device image: BITSKNN_STATIC_SCRATCH_BYTES on every GPU that
+ * loads the library, for the life of the process.  Limits and rules:
+ *   - q * splits * k * 8 bytes must fit (BITSKNN_ERR_WORKSPACE otherwise); splits >= 1;
+ *   - the first call on each device looks up the array's device address; make that call
+ *     before starting any stream capture on that device;
+ *   - every call on a device uses the same array: calls that can overlap on the GPU (different
+ *     streams, different host threads) race and must be serialised by the caller;
+ *   - neither this function nor anything it calls allocates or frees memory. */
+#define BITSKNN_STATIC_SCRATCH_BYTES (8u << 20)
+int bitsknn_select_split_static(const float* d_dist, int64_t ld, const int32_t* d_label_offsets, int64_t q,
+                                int64_t n, int k, int splits, float* d_out_dist, int32_t* d_out_idx,
+                                bitsknn_stream_t stream);
+
 /* Merge of `lists` candidate lists per query into the k smallest pairs (candidate j of
  * list l of query i is at [l * list_stride + i * query_stride + j], strides in elements).
  * Pass 2 of the reference's split-row scheme (bits_knn.cu:170-183) and the merge step of
