@@ -39,6 +39,8 @@ METRIC = "bits top-k selection throughput"
 UNIT = "distances/s"
 # the reference's published H100-PCIe numbers for this shape (q=1024, n=2^20), by k:
 # plots/kselection-hopper01-108424.csv lines 13, 45, 61, 106
+# ncu: (2.4831 GB read + 5.6 MB written) / 592 rows, k = 256
+NCU_DRAM_BYTES_PER_ROW = (2.4831e9 + 5.6e6) / 592
 PUBLISHED_H100 = {32: 4.781e11, 128: 4.637e11, 256: 4.674e11, 2048: 3.599e11}
 
 
@@ -286,15 +288,11 @@ def main():
                 "frac": achieved / peak_gbs, "peak_source": f"{peak_kind} (copy bandwidth, burst)",
                 "algorithmic_bytes_per_launch": algo_bytes, "kernel_ms": kernel_ms,
                 "traffic": None}
-    traffic_file = ROOT / "profiles" / "select_kernel_traffic.json"
-    if traffic_file.exists():
-        try:
-            t = json.loads(traffic_file.read_text())
-            # ncu capture of a smaller case of the same kernel, scaled by rows (traffic is per row)
-            roofline["traffic"] = t["dram_bytes_per_row"] * q
-            roofline["traffic_source"] = t.get("source")
-        except (KeyError, ValueError):
-            pass
+    # DRAM traffic of the same kernel from one ncu capture of a 592-row case (one full wave), per
+    # row; traffic is proportional to the rows, so a full launch is rows x that.
+    roofline["traffic"] = NCU_DRAM_BYTES_PER_ROW * q
+    roofline["traffic_source"] = ("ncu dram__bytes_read.sum + dram__bytes_write.sum of select_kernel<256,1>, "
+                                  "592 x 2^20 capture, scaled by rows")
 
     # ---- sweep: other k, and the adversarial descending rows (kernel time only) -------------
     sweep = None

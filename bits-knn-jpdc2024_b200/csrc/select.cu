@@ -85,8 +85,8 @@ struct select_block
     __device__ __forceinline__ int label_of(int e) const { return labp != nullptr ? labp[e] : lab0 + e; }
 
     // Folds the first `valid` buffer entries into the list and refreshes the radius.
-    // Entered and left with all threads; `consumed` is taken off ctrl->count.
-    __device__ __forceinline__ void fold(int valid, int consumed)
+    // Entered and left with all threads; leaves the buffer empty (ctrl->count = 0).
+    __device__ __forceinline__ void fold(int valid)
     {
         const int tid = threadIdx.x;
         float cd[IPT];
@@ -112,7 +112,7 @@ struct select_block
         }
         if (tid == 0)
         {
-            ctrl->count -= consumed;
+            ctrl->count = 0;
         }
         __syncthreads();
         r_d = ctrl->r_d;
@@ -235,38 +235,33 @@ struct select_block
             float dv[4];
             int lab[4];
             bool pr[4];
-            int off[4];
             filter4(val, live, e_base + 4 * v, dv, lab, pr);
-            const int total = warp_slots(pr, off);
-            int base = 0;
-            if (lane == 0 && total > 0)
-            {
-                base = atomicAdd(&ctrl->count, total);
-            }
-            base = __shfl_sync(FULL_MASK, base, 0);
-            int ps[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-            {
-                ps[j] = pr[j] ? base + off[j] : -1;
-            }
             while (true)
             {
+                // allocate slots for what is still pending, write what fits
+                int off[4];
+                const int total = warp_slots(pr, off);
+                int base = 0;
+                if (lane == 0 && total > 0)
+                {
+                    base = atomicAdd(&ctrl->count, total);
+                }
+                base = __shfl_sync(FULL_MASK, base, 0);
                 bool overflow = false;
 #pragma unroll
                 for (int j = 0; j < 4; ++j)
                 {
-                    if (ps[j] >= 0)
+                    if (pr[j])
                     {
-                        if (ps[j] < L)
+                        const int pos = base + off[j];
+                        if (pos < L)
                         {
-                            buf_d[ps[j]] = dv[j];
-                            buf_x[ps[j]] = lab[j];
-                            ps[j] = -1;
+                            buf_d[pos] = dv[j];
+                            buf_x[pos] = lab[j];
+                            pr[j] = false;
                         }
                         else
                         {
-                            ps[j] -= L;
                             overflow = true;
                         }
                     }
@@ -275,8 +270,15 @@ struct select_block
                 {
                     break;
                 }
-                fold(L, L);
+                // the buffer is full: fold it, then offer the rest again under the tighter radius
+                // (unlike the reference, which carries every allocated slot over)
+                fold(L);
                 ++folds;
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                {
+                    pr[j] = pr[j] && pair_lt(dv[j], lab[j], r_d, r_x);
+                }
             }
         }
         return folds;
@@ -490,7 +492,7 @@ __global__ void __launch_bounds__(THREADS) select_kernel(const select_params p)
         }
         if (count0 >= p.merge_at)
         {
-            blk.fold(count0, count0);
+            blk.fold(count0);
             count0 = 0;
         }
         // every thread has passed a barrier after its last read of this stage
@@ -522,7 +524,7 @@ __global__ void __launch_bounds__(THREADS) select_kernel(const select_params p)
 
     if (count0 > 0)
     {
-        blk.fold(count0, count0);
+        blk.fold(count0);
     }
 
     float* od = p.out_dist + vrow * p.k;

@@ -35,9 +35,10 @@ __device__ __forceinline__ void cx_step(float (&d)[IPT], int (&x)[IPT], bool des
             {
                 const int e = tid * IPT + r;
                 const bool asc = (((e & K) == 0) != desc);
+                // all real keys are distinct, so "not (upper < lower)" means "lower < upper" except
+                // for identical padding pairs, whose exchange changes nothing
                 const bool upper_lt_lower = pair_lt(d[r | J], x[r | J], d[r], x[r]);
-                const bool lower_lt_upper = pair_lt(d[r], x[r], d[r | J], x[r | J]);
-                const bool swap = asc ? upper_lt_lower : lower_lt_upper;
+                const bool swap = (upper_lt_lower == asc);
                 if (swap)
                 {
                     const float td = d[r];
@@ -89,7 +90,8 @@ __device__ __forceinline__ void cx_step(float (&d)[IPT], int (&x)[IPT], bool des
             const int e = tid * IPT + r;
             const bool asc = (((e & K) == 0) != desc);
             const bool keep_min = (lower == asc);
-            const bool take = keep_min ? pair_lt(pd[r], px[r], d[r], x[r]) : pair_lt(d[r], x[r], pd[r], px[r]);
+            // one comparison serves both directions (see above: equal pairs are identical pairs)
+            const bool take = (pair_lt(pd[r], px[r], d[r], x[r]) == keep_min);
             if (take)
             {
                 d[r] = pd[r];
