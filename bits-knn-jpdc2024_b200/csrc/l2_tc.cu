@@ -1,9 +1,571 @@
+// Squared-L2 distance matrix on the 5th-generation tensor cores (tcgen05), TF32 / BF16 inputs,
+// FP32 accumulation in tensor memory:  dist = |x|^2 + |y|^2 - 2 x.y.
+//
+// This is the only dense contraction of the engine (the role of the reference's
+// abstract_gemm<partial_l2_ops>, include/bits/distance/abstract_gemm.cuh:139-169,494-714, and
+// of its tensor-core experiment fused_tc_kernel.cuh:109-158,346,440: a pre-pass that converts
+// the inputs and computes the norms, then `fmaf(-2, dot, |x|^2) + |y|^2`).
+//
+//   pre-pass   rounds the inputs to the MMA input type (round-to-nearest) into a padded image
+//              in the caller's workspace and writes the FP32 norms of the ORIGINAL vectors;
+//              for dim <= 85 (TF32) / 170 (BF16) the image carries a hi/lo split along K that
+//              compensates the input rounding (see tc_prepare_kernel), which is what keeps
+//              recall@k >= 0.999 against the FP32 path
+//   main       320 threads per block, one block per SM:
+//              warp 8  TMA producer: query tile once, then point tiles through a ring of
+//                      16 KiB stages (128 rows x 128 bytes, 128-byte swizzle)
+//              warp 9  allocates 256 TMEM columns, issues tcgen05.mma (M = 128 queries,
+//                      N = 128 points, K = 8 TF32 / 16 BF16 per instruction), commits stage and
+//                      accumulator barriers
+//              warps 0-7  epilogue, two groups of four: group g drains accumulator buffer g
+//                      (every other tile) with tcgen05.ld 32 lanes x 32 columns, transposes
+//                      through a shared-memory staging tile so that every 128-byte row segment
+//                      is written by 8 lanes, adds the norms, streaming 128-bit stores; the two
+//                      buffers let the epilogue of tile t overlap the MMAs of tile t + 1
+// Every mbarrier wait is bounded; on expiry the role stops, the block reaches its final barrier,
+// frees its TMEM and sets the device status word.
+#include <algorithm>
+#include <cstdint>
+#include <mutex>
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+
 #include "common.cuh"
+#include "ptx.cuh"
+#include "tc.cuh"
+
 namespace bitsknn
 {
-size_t l2_tc_workspace_bytes(int64_t, int64_t, int, int) { return 0; }
-int l2_tc_launch(const float*, const float*, int64_t, int64_t, int, int, float*, int64_t, void*, size_t, cudaStream_t)
+
+namespace
 {
-    return fail(BITSKNN_ERR_UNSUPPORTED_MODE, "tensor-core distance modes are not built yet");
+
+constexpr int TILE_M = 128;        // queries per block tile (TMEM lanes)
+constexpr int TILE_N = 128;        // points per MMA tile (TMEM columns per accumulator)
+constexpr int STAGE_BYTES = 16384; // 128 rows x 128 bytes
+constexpr int MAX_KB = 8;          // K blocks of 128 bytes: dim <= 256 (TF32) / 512 (BF16)
+constexpr int TC_THREADS = 320;     // 8 epilogue warps + TMA producer warp + MMA warp
+constexpr int PRODUCER_WARP = 8;
+constexpr int MMA_WARP = 9;
+constexpr int TMEM_COLS = 256;
+constexpr int STAGE_LD = 36;       // row stride (floats) of the epilogue staging tiles
+
+struct tc_params
+{
+    const float* qn; // [q] query norms
+    const float* pn; // [n] point norms
+    float* out;
+    int64_t ld;
+    int64_t n;
+    int64_t q;
+    int nkb;      // K blocks per tile
+    int stages;   // ring stages
+    int parts;    // blocks per query tile
+    int64_t tiles; // point tiles
+    int* status;
+};
+
+// Pre-pass, one warp per row: writes the FP32 norm of the row and its MMA-input image.
+//
+// Plain image: the row rounded to nearest in the input type, zero padded to `ext_pad`.
+// Split image (`split` != 0): every coordinate v is written as hi = rn(v) and lo = rn(v - hi),
+// and the row is laid out along K as
+//     queries  [hi | hi | lo]      points  [hi | lo | hi]
+// so that ONE contraction over 3 * dim yields hi.hi + hi.lo + lo.hi -- the product with the
+// rounding error of both inputs compensated to first order (only lo.lo is dropped).
+template <bool BF16>
+__global__ void tc_prepare_kernel(const float* __restrict__ src, int64_t rows, int dim, int ext_pad, int split,
+                                  int is_points, void* __restrict__ dst, float* __restrict__ norms)
+{
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    if (row >= rows)
+    {
+        return;
+    }
+    auto round_in = [](float v) -> float {
+        if constexpr (BF16)
+        {
+            return __bfloat162float(__float2bfloat16_rn(v));
+        }
+        else
+        {
+            uint32_t t;
+            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(t) : "f"(v));
+            return __uint_as_float(t);
+        }
+    };
+    auto store = [&](int c, float v) {
+        if constexpr (BF16)
+        {
+            static_cast<__nv_bfloat16*>(dst)[row * ext_pad + c] = __float2bfloat16_rn(v);
+        }
+        else
+        {
+            static_cast<float*>(dst)[row * ext_pad + c] = v;
+        }
+    };
+    const float* in = src + row * dim;
+    float nrm = 0.0F;
+    for (int d = lane; d < dim; d += 32)
+    {
+        const float v = in[d];
+        nrm = fmaf(v, v, nrm);
+        const float hi = round_in(v);
+        if (split != 0)
+        {
+            const float lo = round_in(v - hi);
+            store(d, hi);
+            store(dim + d, is_points != 0 ? lo : hi);
+            store(2 * dim + d, is_points != 0 ? hi : lo);
+        }
+        else
+        {
+            store(d, hi);
+        }
+    }
+    for (int c = (split != 0 ? 3 : 1) * dim + lane; c < ext_pad; c += 32)
+    {
+        store(c, 0.0F);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+    {
+        nrm += __shfl_xor_sync(FULL_MASK, nrm, o);
+    }
+    if (lane == 0)
+    {
+        norms[row] = nrm;
+    }
 }
+
+template <bool BF16>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+    l2_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_p, const tc_params p)
+{
+    extern __shared__ unsigned char smem_raw[];
+    // 1024-byte alignment for the swizzled tiles
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    unsigned char* a_tiles = smem;                                       // nkb x 16 KiB
+    unsigned char* b_ring = a_tiles + static_cast<size_t>(p.nkb) * STAGE_BYTES; // stages x 16 KiB
+    uint64_t* bars = reinterpret_cast<uint64_t*>(b_ring + static_cast<size_t>(p.stages) * STAGE_BYTES);
+    uint64_t* a_full = bars;
+    uint64_t* full_b = bars + 1;
+    uint64_t* empty_b = full_b + 16;
+    uint64_t* acc_full = empty_b + 16;
+    uint64_t* acc_empty = acc_full + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    float* staging = reinterpret_cast<float*>(bars + 64); // 8 warps x 32 rows x STAGE_LD floats
+
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5;
+    const int lane = tid & 31;
+    constexpr int KB_ELEMS = BF16 ? 64 : 32; // elements per 128-byte K block
+    constexpr int K_STEP_BYTES = 32;         // one MMA consumes 32 bytes of K (8 TF32 / 16 BF16)
+
+    const int64_t qb = blockIdx.x / p.parts;
+    const int part = static_cast<int>(blockIdx.x - qb * p.parts);
+    const int64_t per = (p.tiles + p.parts - 1) / p.parts;
+    const int64_t t_begin = part * per;
+    const int64_t t_end = t_begin + per < p.tiles ? t_begin + per : p.tiles;
+
+    if (tid == 0)
+    {
+        ptx::mbar_init(a_full, 1);
+        for (int s = 0; s < p.stages; ++s)
+        {
+            ptx::mbar_init(&full_b[s], 1);
+            ptx::mbar_init(&empty_b[s], 1);
+        }
+        for (int a = 0; a < 2; ++a)
+        {
+            ptx::mbar_init(&acc_full[a], 1);
+            ptx::mbar_init(&acc_empty[a], 128);
+        }
+        ptx::mbar_init_fence();
+    }
+    if (warp == MMA_WARP)
+    {
+        tc::tmem_alloc(tmem_slot, TMEM_COLS);
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    bool ok = true;
+
+    if (warp == PRODUCER_WARP)
+    {
+        if (lane == 0 && t_begin < t_end)
+        {
+            ptx::mbar_expect_tx(a_full, static_cast<uint32_t>(p.nkb) * STAGE_BYTES);
+            for (int kb = 0; kb < p.nkb; ++kb)
+            {
+                tc::tma_load_2d(a_tiles + static_cast<size_t>(kb) * STAGE_BYTES, &map_q, kb * KB_ELEMS,
+                                static_cast<int>(qb * TILE_M), a_full);
+            }
+            int s = 0;
+            uint32_t ph = 0;
+            for (int64_t t = t_begin; t < t_end && ok; ++t)
+            {
+                for (int kb = 0; kb < p.nkb; ++kb)
+                {
+                    // a fresh barrier passes a wait on the opposite parity at once
+                    if (!ptx::mbar_wait_bounded(&empty_b[s], ph ^ 1U))
+                    {
+                        ok = false;
+                        break;
+                    }
+                    ptx::mbar_expect_tx(&full_b[s], STAGE_BYTES);
+                    tc::tma_load_2d(b_ring + static_cast<size_t>(s) * STAGE_BYTES, &map_p, kb * KB_ELEMS,
+                                    static_cast<int>(t * TILE_N), &full_b[s]);
+                    if (++s == p.stages)
+                    {
+                        s = 0;
+                        ph ^= 1U;
+                    }
+                }
+            }
+        }
+    }
+    else if (warp == MMA_WARP)
+    {
+        if (lane == 0 && t_begin < t_end)
+        {
+            constexpr uint32_t idesc = tc::instr_desc(BF16 ? 1U : 2U, TILE_M, TILE_N);
+            ok = ptx::mbar_wait_bounded(a_full, 0);
+            int s = 0;
+            uint32_t ph = 0;
+            int64_t lt = 0;
+            for (int64_t t = t_begin; t < t_end && ok; ++t, ++lt)
+            {
+                const int a = static_cast<int>(lt & 1);
+                const uint32_t aph = static_cast<uint32_t>((lt >> 1) & 1);
+                if (!ptx::mbar_wait_bounded(&acc_empty[a], aph ^ 1U))
+                {
+                    ok = false;
+                    break;
+                }
+                tc::fence_after_sync();
+                for (int kb = 0; kb < p.nkb && ok; ++kb)
+                {
+                    if (!ptx::mbar_wait_bounded(&full_b[s], ph))
+                    {
+                        ok = false;
+                        break;
+                    }
+                    tc::fence_after_sync();
+                    const uint64_t adesc = tc::smem_desc_sw128(a_tiles + static_cast<size_t>(kb) * STAGE_BYTES);
+                    const uint64_t bdesc = tc::smem_desc_sw128(b_ring + static_cast<size_t>(s) * STAGE_BYTES);
+#pragma unroll
+                    for (int ks = 0; ks < 128 / K_STEP_BYTES; ++ks)
+                    {
+                        tc::mma<BF16>(tmem_base + static_cast<uint32_t>(a * TILE_N), adesc + (ks * K_STEP_BYTES >> 4),
+                                      bdesc + (ks * K_STEP_BYTES >> 4), idesc, kb > 0 || ks > 0);
+                    }
+                    tc::mma_commit(&empty_b[s]); // the stage is free once these MMAs have read it
+                    if (++s == p.stages)
+                    {
+                        s = 0;
+                        ph ^= 1U;
+                    }
+                }
+                tc::mma_commit(&acc_full[a]);
+            }
+        }
+    }
+    else
+    {
+        // epilogue: two groups of four warps; group g drains accumulator buffer g, i.e. every
+        // other tile.  Warp w of a group owns TMEM lanes 32 * w .. + 31 = 32 query rows.
+        const int group = warp >> 2;
+        const int w4 = warp & 3;
+        const bool vec_out = (p.ld % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15U) == 0);
+        float* stage = staging + warp * (32 * STAGE_LD);
+        // after the transposition through `stage`, lane l writes the column quad (l & 7) * 4 of
+        // rows 4 * i + (l >> 3), i = 0..7: their query norms stay in registers
+        const int sub = lane >> 3;
+        const int cq4 = (lane & 7) * 4;
+        float qn[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+        {
+            const int64_t r = qb * TILE_M + w4 * 32 + i * 4 + sub;
+            qn[i] = r < p.q ? __ldg(p.qn + r) : 0.0F;
+        }
+        const uint32_t lane_base = (static_cast<uint32_t>(w4 * 32) << 16) + static_cast<uint32_t>(group * TILE_N);
+        int64_t use = 0; // how many times this group has used its buffer
+        for (int64_t t = t_begin + group; t < t_end && ok; t += 2, ++use)
+        {
+            // point norms of this lane's four column quads, fetched before the wait so that their
+            // latency hides behind it
+            float pn_all[TILE_N / 32][4];
+#pragma unroll
+            for (int c = 0; c < TILE_N / 32; ++c)
+            {
+                const int64_t col = t * TILE_N + c * 32 + cq4;
+                if (col + 3 < p.n)
+                {
+                    const float4 t4 = __ldg(reinterpret_cast<const float4*>(p.pn + col));
+                    pn_all[c][0] = t4.x;
+                    pn_all[c][1] = t4.y;
+                    pn_all[c][2] = t4.z;
+                    pn_all[c][3] = t4.w;
+                }
+                else
+                {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                    {
+                        pn_all[c][e] = col + e < p.n ? __ldg(p.pn + col + e) : 0.0F;
+                    }
+                }
+            }
+            if (!ptx::mbar_wait_bounded(&acc_full[group], static_cast<uint32_t>(use & 1)))
+            {
+                ok = false;
+                break;
+            }
+            tc::fence_after_sync();
+            uint32_t v[32];
+            tc::tmem_ld_32x32(tmem_base + lane_base, v);
+            tc::tmem_ld_wait();
+#pragma unroll
+            for (int c = 0; c < TILE_N / 32; ++c)
+            {
+                // raw accumulators of this thread's row -> staging tile (row stride 36 floats:
+                // conflict-free 128-bit writes and reads)
+#pragma unroll
+                for (int j = 0; j < 32; j += 4)
+                {
+                    *reinterpret_cast<uint4*>(stage + lane * STAGE_LD + j) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                }
+                // the next 32 columns travel from TMEM while this chunk is finished and stored
+                if (c + 1 < TILE_N / 32)
+                {
+                    tc::tmem_ld_32x32(tmem_base + lane_base + static_cast<uint32_t>((c + 1) * 32), v);
+                }
+                __syncwarp();
+                const int64_t col = t * TILE_N + c * 32 + cq4;
+                const float(&pn4)[4] = pn_all[c];
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                {
+                    const int rr = i * 4 + sub;
+                    const int64_t orow = qb * TILE_M + w4 * 32 + rr;
+                    const float4 acc = *reinterpret_cast<const float4*>(stage + rr * STAGE_LD + cq4);
+                    float4 r;
+                    r.x = fmaf(-2.0F, acc.x, pn4[0]) + qn[i];
+                    r.y = fmaf(-2.0F, acc.y, pn4[1]) + qn[i];
+                    r.z = fmaf(-2.0F, acc.z, pn4[2]) + qn[i];
+                    r.w = fmaf(-2.0F, acc.w, pn4[3]) + qn[i];
+                    if (orow < p.q)
+                    {
+                        float* dst = p.out + orow * p.ld + col;
+                        if (vec_out && col + 3 < p.n)
+                        {
+                            __stcs(reinterpret_cast<float4*>(dst), r);
+                        }
+                        else
+                        {
+                            const float e4[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+                            for (int e = 0; e < 4; ++e)
+                            {
+                                if (col + e < p.n)
+                                {
+                                    __stcs(dst + e, e4[e]);
+                                }
+                            }
+                        }
+                    }
+                }
+                __syncwarp();
+                if (c + 1 < TILE_N / 32)
+                {
+                    tc::tmem_ld_wait();
+                }
+                else
+                {
+                    // every accumulator of this thread has been read: the MMA warp may reuse the buffer
+                    tc::fence_before_sync();
+                    tc::mbar_arrive(&acc_empty[group]);
+                }
+            }
+        }
+    }
+
+    if (!ok)
+    {
+        atomicOr(p.status, DEVICE_STATUS_TIMEOUT);
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    if (warp == MMA_WARP)
+    {
+        tc::fence_after_sync();
+        tc::tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+using encode_fn_t = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+encode_fn_t tensor_map_encoder()
+{
+    static std::once_flag once;
+    static encode_fn_t fn = nullptr;
+    std::call_once(once, [] {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult res;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &res) == cudaSuccess &&
+            res == cudaDriverEntryPointSuccess)
+        {
+            fn = reinterpret_cast<encode_fn_t>(ptr);
+        }
+    });
+    return fn;
+}
+
+// rows x dim_pad matrix of 4-byte (TF32) or 2-byte (BF16) elements, box = 128 bytes x 128 rows
+int make_map(CUtensorMap* map, void* base, int64_t rows, int dim_pad, bool bf16)
+{
+    encode_fn_t encode = tensor_map_encoder();
+    if (encode == nullptr)
+    {
+        return fail(BITSKNN_ERR_CUDA, "CUDA error. cuTensorMapEncodeTiled is not available from this driver");
+    }
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(dim_pad), static_cast<cuuint64_t>(rows)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(dim_pad) * (bf16 ? 2U : 4U)};
+    const cuuint32_t box[2] = {bf16 ? 64U : 32U, 128U};
+    const cuuint32_t elem[2] = {1U, 1U};
+    const CUresult rc = encode(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, base,
+                               dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS)
+    {
+        return fail(BITSKNN_ERR_CUDA, "CUDA error. cuTensorMapEncodeTiled failed with code %d", static_cast<int>(rc));
+    }
+    return BITSKNN_OK;
+}
+
+size_t align256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
+
+struct tc_layout
+{
+    int dim_pad; // length of a row image along K (elements), whole 128-byte blocks
+    int split;   // 1: error-compensated 3-term image
+    size_t off_pn, off_qn, off_p, off_q, total;
+};
+
+tc_layout layout_of(int64_t n, int64_t q, int dim, bool bf16)
+{
+    tc_layout l{};
+    // padded to whole 128-byte K blocks, so that a TMA box never exceeds the row; the
+    // compensated image is used whenever 3 * dim fits the resident query tile (MAX_KB blocks)
+    const int unit = bf16 ? 64 : 32;
+    l.split = 3 * dim <= MAX_KB * unit ? 1 : 0;
+    const int ext = (l.split != 0 ? 3 : 1) * dim;
+    l.dim_pad = ((ext + unit - 1) / unit) * unit;
+    const size_t esz = bf16 ? 2 : 4;
+    l.off_pn = 0;
+    l.off_qn = align256(static_cast<size_t>(n) * 4);
+    l.off_p = l.off_qn + align256(static_cast<size_t>(q) * 4);
+    // rows padded to a whole tile so that a box never starts beyond the allocation
+    l.off_q = l.off_p + align256(static_cast<size_t>(n) * l.dim_pad * esz);
+    l.total = l.off_q + align256(static_cast<size_t>(q) * l.dim_pad * esz);
+    return l;
+}
+
+template <bool BF16>
+int run_tc(const float* points, const float* queries, int64_t n, int64_t q, int dim, float* dist, int64_t ld,
+           unsigned char* ws, cudaStream_t stream)
+{
+    const tc_layout l = layout_of(n, q, dim, BF16);
+    float* pn = reinterpret_cast<float*>(ws + l.off_pn);
+    float* qn = reinterpret_cast<float*>(ws + l.off_qn);
+    void* cp = ws + l.off_p;
+    void* cq = ws + l.off_q;
+    tc_prepare_kernel<BF16>
+        <<<static_cast<unsigned>((n + 7) / 8), 256, 0, stream>>>(points, n, dim, l.dim_pad, l.split, 1, cp, pn);
+    tc_prepare_kernel<BF16>
+        <<<static_cast<unsigned>((q + 7) / 8), 256, 0, stream>>>(queries, q, dim, l.dim_pad, l.split, 0, cq, qn);
+    BITSKNN_CUDA_TRY(cudaGetLastError());
+
+    CUtensorMap map_q;
+    CUtensorMap map_p;
+    if (const int rc = make_map(&map_q, cq, q, l.dim_pad, BF16); rc != BITSKNN_OK)
+    {
+        return rc;
+    }
+    if (const int rc = make_map(&map_p, cp, n, l.dim_pad, BF16); rc != BITSKNN_OK)
+    {
+        return rc;
+    }
+
+    tc_params p{};
+    p.qn = qn;
+    p.pn = pn;
+    p.out = dist;
+    p.ld = ld;
+    p.n = n;
+    p.q = q;
+    const int kb_elems = BF16 ? 64 : 32;
+    p.nkb = (l.dim_pad + kb_elems - 1) / kb_elems;
+    p.tiles = (n + TILE_N - 1) / TILE_N;
+    const int64_t nqb = (q + TILE_M - 1) / TILE_M;
+    const int sms = device_sm_count();
+    p.parts = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(p.tiles, sms / std::max<int64_t>(nqb, 1))));
+    p.stages = std::max(2, std::min(12, 11 - p.nkb));
+    p.status = device_status_word();
+    if (p.status == nullptr)
+    {
+        return fail(BITSKNN_ERR_CUDA, "CUDA error. cannot resolve the device status word");
+    }
+    const size_t smem = 1024 + static_cast<size_t>(p.nkb + p.stages) * STAGE_BYTES + 64 * 8 + 8 * 32 * STAGE_LD * 4;
+    auto kernel = l2_tc_kernel<BF16>;
+    BITSKNN_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    const int64_t grid = nqb * p.parts;
+    kernel<<<static_cast<unsigned>(grid), TC_THREADS, smem, stream>>>(map_q, map_p, p);
+    BITSKNN_CUDA_TRY(cudaGetLastError());
+    return BITSKNN_OK;
+}
+
+} // namespace
+
+size_t l2_tc_workspace_bytes(int64_t n, int64_t q, int dim, int mode)
+{
+    if (n <= 0 || q <= 0 || dim <= 0)
+    {
+        return 0;
+    }
+    return layout_of(n, q, dim, mode == BITSKNN_L2_BF16).total;
+}
+
+int l2_tc_launch(const float* points, const float* queries, int64_t n, int64_t q, int dim, int mode, float* dist,
+                 int64_t ld, void* workspace, size_t workspace_bytes, cudaStream_t stream)
+{
+    const bool bf16 = mode == BITSKNN_L2_BF16;
+    const int max_dim = MAX_KB * (bf16 ? 64 : 32);
+    if (dim > max_dim)
+    {
+        return fail(BITSKNN_ERR_UNSUPPORTED_DIM, "Unsupported dimension: %d (tensor-core modes take up to %d)", dim, max_dim);
+    }
+    if (n > 0x7fffffffLL - TILE_N || q > 0x7fffffffLL - TILE_M)
+    {
+        return fail(BITSKNN_ERR_INVALID_ARGUMENT, "sizes beyond the 32-bit tensor-map coordinates");
+    }
+    const size_t need = l2_tc_workspace_bytes(n, q, dim, mode);
+    if (workspace == nullptr || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255U) != 0)
+    {
+        return fail(BITSKNN_ERR_WORKSPACE, "workspace of %zu bytes (256-byte aligned) needed, %zu given", need,
+                    workspace_bytes);
+    }
+    auto* ws = static_cast<unsigned char*>(workspace);
+    return bf16 ? run_tc<true>(points, queries, n, q, dim, dist, ld, ws, stream)
+                : run_tc<false>(points, queries, n, q, dim, dist, ld, ws, stream);
+}
+
 } // namespace bitsknn
