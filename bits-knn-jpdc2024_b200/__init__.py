@@ -43,7 +43,8 @@ SIGNATURES = {
     "bitsknn_merge": (_int, [_ptr, _ptr, _i64, _i64, _i64, _int, _int, _ptr, _ptr, _ptr]),
     "bitsknn_l2_workspace_bytes": (_sz, [_i64, _i64, _int, _int]),
     "bitsknn_l2": (_int, [_ptr, _ptr, _i64, _i64, _int, _int, _ptr, _i64, _ptr, _sz, _ptr]),
-    "bitsknn_fused": (_int, [_ptr, _ptr, _i64, _i64, _int, _int, _int, ctypes.c_int32, _ptr, _ptr, _ptr]),
+    "bitsknn_fused_workspace_bytes": (_sz, [_i64, _i64, _int, _int, _int]),
+    "bitsknn_fused": (_int, [_ptr, _ptr, _i64, _i64, _int, _int, _int, ctypes.c_int32, _ptr, _ptr, _ptr, _sz, _ptr]),
 }
 
 _LIB = None
@@ -206,7 +207,11 @@ def l2(points, queries, mode=L2_EXACT, out=None, workspace=None):
     return out
 
 
-def fused(points, queries, k, mode=L2_PARTIAL, index_base=0, out=None):
+def fused_workspace_bytes(n, q, dim, k, mode):
+    return int(lib().bitsknn_fused_workspace_bytes(n, q, dim, k, mode))
+
+
+def fused(points, queries, k, mode=L2_PARTIAL, index_base=0, out=None, workspace=None):
     """Brute-force k-NN without materialising the distance matrix."""
     import torch
     _device_check(points, torch.float32, "points")
@@ -217,6 +222,9 @@ def fused(points, queries, k, mode=L2_PARTIAL, index_base=0, out=None):
     if out is None:
         out = (torch.empty((q, k), dtype=torch.float32, device=points.device),
                torch.empty((q, k), dtype=torch.int32, device=points.device))
+    need = fused_workspace_bytes(n, q, dim, k, mode)
+    if workspace is None and need > 0:
+        workspace = torch.empty(need, dtype=torch.uint8, device=points.device)
     _check(lib().bitsknn_fused(_p(points), _p(queries), n, q, dim, k, mode, index_base, _p(out[0]), _p(out[1]),
-                               _stream()))
+                               _p(workspace), 0 if workspace is None else workspace.numel(), _stream()))
     return out

@@ -45,4 +45,10 @@ int tuning_value(const char* key, int fallback);
 
 int device_sm_count();
 
+// Merge of `lists` candidate lists of `kin` pairs per query (pair j of list l of query i at
+// [l * list_stride + i * query_stride + j]) into the `k` smallest pairs; `bias` (nullable, one
+// value per query) is added to the reported distances.  Defined in select.cu.
+int merge_lists(const float* cand_dist, const int32_t* cand_idx, int64_t list_stride, int64_t query_stride, int64_t q,
+                int lists, int kin, int k, const float* bias, float* out_dist, int32_t* out_idx, cudaStream_t stream);
+
 } // namespace bitsknn

@@ -25,6 +25,12 @@
 namespace bitsknn
 {
 
+// tensor-core modes live in fused_tc.cu
+size_t fused_tc_workspace_bytes(int64_t n, int64_t q, int dim, int k, int mode);
+int fused_tc_launch(const float* points, const float* queries, int64_t n, int64_t q, int dim, int k, int mode,
+                    int32_t index_base, float* out_dist, int32_t* out_idx, void* workspace, size_t workspace_bytes,
+                    cudaStream_t stream);
+
 namespace
 {
 
@@ -344,9 +350,18 @@ int launch_fused(const fused_params& p, int mode, cudaStream_t stream)
 
 using namespace bitsknn;
 
+extern "C" size_t bitsknn_fused_workspace_bytes(int64_t n, int64_t q, int dim, int k, int mode)
+{
+    if (mode == BITSKNN_L2_TF32 || mode == BITSKNN_L2_BF16)
+    {
+        return fused_tc_workspace_bytes(n, q, dim, k, mode);
+    }
+    return 0;
+}
+
 extern "C" int bitsknn_fused(const float* d_points, const float* d_queries, int64_t n, int64_t q, int dim, int k,
-                             int mode, int32_t index_base, float* d_out_dist, int32_t* d_out_idx,
-                             bitsknn_stream_t stream)
+                             int mode, int32_t index_base, float* d_out_dist, int32_t* d_out_idx, void* d_workspace,
+                             size_t workspace_bytes, bitsknn_stream_t stream)
 {
     if (d_points == nullptr || d_queries == nullptr || d_out_dist == nullptr || d_out_idx == nullptr)
     {
@@ -370,13 +385,18 @@ extern "C" int bitsknn_fused(const float* d_points, const float* d_queries, int6
         // the reference's fused dispatcher rejects k the same way (fused_cache_knn.cu:76-80)
         return fail(BITSKNN_ERR_UNSUPPORTED_K, "Unsupported k value: %d", k);
     }
-    if (mode != BITSKNN_L2_PARTIAL && mode != BITSKNN_L2_EXACT)
+    if (mode != BITSKNN_L2_PARTIAL && mode != BITSKNN_L2_EXACT && mode != BITSKNN_L2_TF32 && mode != BITSKNN_L2_BF16)
     {
         return fail(BITSKNN_ERR_UNSUPPORTED_MODE, "fused mode %d is not available", mode);
     }
     if (q == 0)
     {
         return BITSKNN_OK;
+    }
+    if (mode == BITSKNN_L2_TF32 || mode == BITSKNN_L2_BF16)
+    {
+        return fused_tc_launch(d_points, d_queries, n, q, dim, k, mode, index_base, d_out_dist, d_out_idx, d_workspace,
+                               workspace_bytes, static_cast<cudaStream_t>(stream));
     }
     fused_params p{};
     p.points = d_points;

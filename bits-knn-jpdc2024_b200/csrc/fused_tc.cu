@@ -1,0 +1,594 @@
+// `bits-fused` on the tensor cores: the partial distance tile is produced by tcgen05.mma in
+// tensor memory and consumed from there by the top-k -- no distance ever reaches HBM.
+//
+// The contraction runs over the pre-pass image of tc_host.cuh with the norm columns enabled,
+// so an accumulator holds  s = x.y - |x|^2 / 2  and the partial distance is d = -2 s
+// (= |x|^2 - 2 x.y, the quantity the reference's fused kernel ranks by,
+// include/bits/topk/singlepass/fused_cache_kernel_structs.cuh:622-630).  The consumer compares
+// raw accumulators against  -radius / 2: one max-tree and one compare per 32 columns.
+//
+// Block = 320 threads on one SM, 128 queries (the TMEM lanes):
+//   warp 8   TMA producer (query image once, point image tiles through a ring of 16 KiB stages)
+//   warp 9   TMEM allocation (2 x 128 columns) and tcgen05.mma issue
+//   warps 0-7  consumers, two groups of four.  Group g takes every other point tile (accumulator
+//            buffer g); thread t of a group is query 32 * (warp % 4) + t and reads its row with
+//            tcgen05.ld.  Each (group, query) has a private 32-slot candidate buffer in shared
+//            memory (no atomics: one writer) and a sorted list of KL = 32 * IPT pairs in the
+//            workspace (HBM/L2), touched only when the buffer is folded: the warp sorts the 32
+//            candidates with shuffles, takes the element-wise minimum against the list's last 32
+//            entries and finishes with a bitonic merge (striped arrangement: entry e in lane
+//            e % 32).  A group's radius is tightened by its partner group's (both are upper
+//            bounds of the true k-th distance).
+// After the scan the 2 * parts lists of every query are merged by merge_lists(), which also adds
+// the query norm so that the reported distance is |x|^2 + |y|^2 - 2 x.y.
+// Role of the reference's fused_tc_kernel (detail/fused_tc_kernel.cuh:177-445, wmma based and
+// "suboptimal" by its authors' note in src/gen.py:45), rebuilt on tcgen05 / TMEM / TMA.
+#include <algorithm>
+#include <cstdint>
+
+#include "common.cuh"
+#include "ptx.cuh"
+#include "sortnet.cuh"
+#include "tc.cuh"
+#include "tc_host.cuh"
+
+namespace bitsknn
+{
+
+namespace
+{
+
+constexpr int FT_THREADS = 320;
+constexpr int FT_PRODUCER_WARP = 8;
+constexpr int FT_MMA_WARP = 9;
+constexpr int FT_TMEM_COLS = 256;
+constexpr int CAP = 32; // candidate slots per (group, query)
+
+struct ftc_params
+{
+    float* list_d;   // [parts * 2][q][KL]
+    int32_t* list_x; // [parts * 2][q][KL]
+    int64_t n;
+    int64_t q;
+    int nkb;
+    int stages;
+    int parts;
+    int64_t tiles;
+    int k;
+    int32_t index_base;
+    int* status;
+};
+
+// Sorts a bitonic array of 32 * IPT pairs ascending; entry e lives in lane e % 32, register
+// e / 32.  Strides of 32 and more are exchanges between registers of one lane (M = stride / 32,
+// a compile-time constant so that the arrays stay in registers), smaller ones are shuffles.
+template <int IPT, int M>
+struct striped_reg_steps
+{
+    static __device__ __forceinline__ void run(float (&d)[IPT], int (&x)[IPT])
+    {
+        if constexpr (M >= 1)
+        {
+#pragma unroll
+            for (int r = 0; r < IPT; ++r)
+            {
+                if ((r & M) == 0)
+                {
+                    if (pair_lt(d[r | M], x[r | M], d[r], x[r]))
+                    {
+                        const float td = d[r];
+                        d[r] = d[r | M];
+                        d[r | M] = td;
+                        const int tx = x[r];
+                        x[r] = x[r | M];
+                        x[r | M] = tx;
+                    }
+                }
+            }
+            striped_reg_steps<IPT, M / 2>::run(d, x);
+        }
+    }
+};
+
+template <int IPT>
+__device__ __forceinline__ void merge_striped(float (&d)[IPT], int (&x)[IPT], int lane)
+{
+    striped_reg_steps<IPT, IPT / 2>::run(d, x);
+#pragma unroll
+    for (int J = 16; J >= 1; J >>= 1)
+    {
+        const bool keep_min = (lane & J) == 0;
+#pragma unroll
+        for (int r = 0; r < IPT; ++r)
+        {
+            const float pd = __shfl_xor_sync(FULL_MASK, d[r], J);
+            const int px = __shfl_xor_sync(FULL_MASK, x[r], J);
+            if (pair_lt(pd, px, d[r], x[r]) == keep_min)
+            {
+                d[r] = pd;
+                x[r] = px;
+            }
+        }
+    }
+}
+
+template <bool BF16, int IPT>
+__global__ void __launch_bounds__(FT_THREADS, 1)
+    fused_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_p, const ftc_params p)
+{
+    constexpr int KL = 32 * IPT;
+    constexpr int KB_ELEMS = BF16 ? 64 : 32;
+    constexpr int K_STEP_BYTES = 32;
+
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    unsigned char* a_tiles = smem;
+    unsigned char* b_ring = a_tiles + static_cast<size_t>(p.nkb) * STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(b_ring + static_cast<size_t>(p.stages) * STAGE_BYTES);
+    uint64_t* a_full = bars;
+    uint64_t* full_b = bars + 1;
+    uint64_t* empty_b = full_b + 16;
+    uint64_t* acc_full = empty_b + 16;
+    uint64_t* acc_empty = acc_full + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    float* rad = reinterpret_cast<float*>(bars + 64);     // [2][128] radius distance per group and query
+    float* buf_d = rad + 2 * TILE_M;                      // [8 warps][CAP][32 lanes]
+    int* buf_x = reinterpret_cast<int*>(buf_d + 8 * CAP * 32);
+
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5;
+    const int lane = tid & 31;
+
+    const int64_t qb = blockIdx.x / p.parts;
+    const int part = static_cast<int>(blockIdx.x - qb * p.parts);
+    const int64_t per = (p.tiles + p.parts - 1) / p.parts;
+    const int64_t t_begin = part * per;
+    const int64_t t_end = t_begin + per < p.tiles ? t_begin + per : p.tiles;
+
+    if (tid == 0)
+    {
+        ptx::mbar_init(a_full, 1);
+        for (int s = 0; s < p.stages; ++s)
+        {
+            ptx::mbar_init(&full_b[s], 1);
+            ptx::mbar_init(&empty_b[s], 1);
+        }
+        for (int a = 0; a < 2; ++a)
+        {
+            ptx::mbar_init(&acc_full[a], 1);
+            ptx::mbar_init(&acc_empty[a], 128);
+        }
+        ptx::mbar_init_fence();
+    }
+    if (tid < 2 * TILE_M)
+    {
+        rad[tid] = INFINITY;
+    }
+    if (warp == FT_MMA_WARP)
+    {
+        tc::tmem_alloc(tmem_slot, FT_TMEM_COLS);
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    bool ok = true;
+
+    if (warp == FT_PRODUCER_WARP)
+    {
+        if (lane == 0 && t_begin < t_end)
+        {
+            ptx::mbar_expect_tx(a_full, static_cast<uint32_t>(p.nkb) * STAGE_BYTES);
+            for (int kb = 0; kb < p.nkb; ++kb)
+            {
+                tc::tma_load_2d(a_tiles + static_cast<size_t>(kb) * STAGE_BYTES, &map_q, kb * KB_ELEMS,
+                                static_cast<int>(qb * TILE_M), a_full);
+            }
+            int s = 0;
+            uint32_t ph = 0;
+            for (int64_t t = t_begin; t < t_end && ok; ++t)
+            {
+                for (int kb = 0; kb < p.nkb; ++kb)
+                {
+                    if (!ptx::mbar_wait_bounded(&empty_b[s], ph ^ 1U))
+                    {
+                        ok = false;
+                        break;
+                    }
+                    ptx::mbar_expect_tx(&full_b[s], STAGE_BYTES);
+                    tc::tma_load_2d(b_ring + static_cast<size_t>(s) * STAGE_BYTES, &map_p, kb * KB_ELEMS,
+                                    static_cast<int>(t * TILE_N), &full_b[s]);
+                    if (++s == p.stages)
+                    {
+                        s = 0;
+                        ph ^= 1U;
+                    }
+                }
+            }
+        }
+    }
+    else if (warp == FT_MMA_WARP)
+    {
+        if (lane == 0 && t_begin < t_end)
+        {
+            constexpr uint32_t idesc = tc::instr_desc(BF16 ? 1U : 2U, TILE_M, TILE_N);
+            ok = ptx::mbar_wait_bounded(a_full, 0);
+            int s = 0;
+            uint32_t ph = 0;
+            int64_t lt = 0;
+            for (int64_t t = t_begin; t < t_end && ok; ++t, ++lt)
+            {
+                const int a = static_cast<int>(lt & 1);
+                const uint32_t aph = static_cast<uint32_t>((lt >> 1) & 1);
+                if (!ptx::mbar_wait_bounded(&acc_empty[a], aph ^ 1U))
+                {
+                    ok = false;
+                    break;
+                }
+                tc::fence_after_sync();
+                for (int kb = 0; kb < p.nkb && ok; ++kb)
+                {
+                    if (!ptx::mbar_wait_bounded(&full_b[s], ph))
+                    {
+                        ok = false;
+                        break;
+                    }
+                    tc::fence_after_sync();
+                    const uint64_t adesc = tc::smem_desc_sw128(a_tiles + static_cast<size_t>(kb) * STAGE_BYTES);
+                    const uint64_t bdesc = tc::smem_desc_sw128(b_ring + static_cast<size_t>(s) * STAGE_BYTES);
+#pragma unroll
+                    for (int ks = 0; ks < 128 / K_STEP_BYTES; ++ks)
+                    {
+                        tc::mma<BF16>(tmem_base + static_cast<uint32_t>(a * TILE_N), adesc + (ks * K_STEP_BYTES >> 4),
+                                      bdesc + (ks * K_STEP_BYTES >> 4), idesc, kb > 0 || ks > 0);
+                    }
+                    tc::mma_commit(&empty_b[s]);
+                    if (++s == p.stages)
+                    {
+                        s = 0;
+                        ph ^= 1U;
+                    }
+                }
+                tc::mma_commit(&acc_full[a]);
+            }
+        }
+    }
+    else
+    {
+        const int group = warp >> 2;
+        const int w4 = warp & 3;
+        const int qrow = w4 * 32 + lane;              // query of this thread inside the tile
+        const int64_t gq = qb * TILE_M + qrow;        // global query
+        const bool live = gq < p.q;
+        float* my_buf_d = buf_d + warp * (CAP * 32);  // slot s of lane l at [s * 32 + l]
+        int* my_buf_x = buf_x + warp * (CAP * 32);
+        const int64_t list_id = static_cast<int64_t>(part) * 2 + group;
+        const uint32_t lane_base = (static_cast<uint32_t>(w4 * 32) << 16) + static_cast<uint32_t>(group * TILE_N);
+
+        // radius pair of this (group, query); a dead row (query beyond q) never accepts anything
+        float r_d = live ? INFINITY : -INFINITY;
+        int r_x = PAD_IDX;
+        float thr = live ? -INFINITY : INFINITY; // accumulators >= thr are candidates
+        int cnt = 0;
+        bool has_list = false;
+
+        // Folds the buffers of the queries whose lanes are set in `mask` into their lists.
+        auto fold_queries = [&](unsigned mask) {
+            while (mask != 0)
+            {
+                const int L = __ffs(static_cast<int>(mask)) - 1;
+                mask &= mask - 1;
+                const int cnt_l = __shfl_sync(FULL_MASK, cnt, L);
+                const bool has_l = __shfl_sync(FULL_MASK, has_list ? 1 : 0, L) != 0;
+                const int64_t gq_l = qb * TILE_M + w4 * 32 + L;
+                float* gl_d = p.list_d + (list_id * p.q + gq_l) * KL;
+                int32_t* gl_x = p.list_x + (list_id * p.q + gq_l) * KL;
+                // candidates: slot `lane` of query L's buffer, sorted descending over the lanes
+                float cd[1] = {lane < cnt_l ? my_buf_d[lane * 32 + L] : INFINITY};
+                int cx[1] = {lane < cnt_l ? my_buf_x[lane * 32 + L] : PAD_IDX};
+                block_sort<32, 1>(cd, cx, true, nullptr, nullptr, lane);
+                float ld[IPT];
+                int lx[IPT];
+#pragma unroll
+                for (int r = 0; r < IPT; ++r)
+                {
+                    ld[r] = has_l ? gl_d[r * 32 + lane] : INFINITY;
+                    lx[r] = has_l ? gl_x[r * 32 + lane] : PAD_IDX;
+                }
+                // element-wise minimum against the last 32 entries (ascending in the lanes), which
+                // leaves the KL smallest pairs as a bitonic array, then the merge network
+                if (pair_lt(cd[0], cx[0], ld[IPT - 1], lx[IPT - 1]))
+                {
+                    ld[IPT - 1] = cd[0];
+                    lx[IPT - 1] = cx[0];
+                }
+                merge_striped<IPT>(ld, lx, lane);
+#pragma unroll
+                for (int r = 0; r < IPT; ++r)
+                {
+                    gl_d[r * 32 + lane] = ld[r];
+                    gl_x[r * 32 + lane] = lx[r];
+                }
+                // new radius = entry k - 1
+                float nd = ld[0];
+                int nx = lx[0];
+#pragma unroll
+                for (int r = 1; r < IPT; ++r)
+                {
+                    // (opaque selects: a plain ?: chain is turned into an indexed load from a
+                    // stack copy of the list, which costs a local store per list update)
+                    const int pick = r == (p.k - 1) / 32 ? 1 : 0;
+                    asm("{\n.reg .pred p;\nsetp.ne.s32 p, %2, 0;\nselp.f32 %0, %1, %0, p;\n}" : "+f"(nd) : "f"(ld[r]), "r"(pick));
+                    asm("{\n.reg .pred p;\nsetp.ne.s32 p, %2, 0;\nselp.s32 %0, %1, %0, p;\n}" : "+r"(nx) : "r"(lx[r]), "r"(pick));
+                }
+                nd = __shfl_sync(FULL_MASK, nd, (p.k - 1) & 31);
+                nx = __shfl_sync(FULL_MASK, nx, (p.k - 1) & 31);
+                if (lane == L)
+                {
+                    r_d = nd;
+                    r_x = nx;
+                    cnt = 0;
+                    has_list = true;
+                    rad[group * TILE_M + qrow] = nd;
+                }
+                __syncwarp(); // the list stores are ordered before any later load by this warp
+            }
+        };
+
+        int64_t use = 0;
+        for (int64_t t = t_begin + group; t < t_end && ok; t += 2, ++use)
+        {
+            if (live)
+            {
+                // both groups' radii bound the true k-th distance from above
+                const float r_eff = fminf(r_d, rad[(group ^ 1) * TILE_M + qrow]);
+                thr = -0.5F * r_eff;
+            }
+            // (the verdict is made warp-uniform: the lanes poll independently)
+            if (!__all_sync(FULL_MASK, ptx::mbar_wait_bounded(&acc_full[group], static_cast<uint32_t>(use & 1))))
+            {
+                ok = false;
+                break;
+            }
+            tc::fence_after_sync();
+#pragma unroll 1
+            for (int c = 0; c < TILE_N / 32; ++c)
+            {
+                uint32_t v[32];
+                tc::tmem_ld_32x32(tmem_base + lane_base + static_cast<uint32_t>(c * 32), v);
+                tc::tmem_ld_wait();
+                if (c == TILE_N / 32 - 1)
+                {
+                    // every accumulator of this thread is in registers: the buffer may be reused
+                    tc::fence_before_sync();
+                    tc::mbar_arrive(&acc_empty[group]);
+                }
+                const int64_t col0 = t * TILE_N + c * 32;
+                const int ncols = p.n - col0 < 32 ? static_cast<int>(p.n - col0) : 32; // valid columns
+                // two halves of 16 columns; a buffer holds at most 16 pairs when a half starts,
+                // so the at most 16 pushes of a half always fit its 32 slots
+#pragma unroll
+                for (int half = 0; half < 2; ++half)
+                {
+                    float mx = __uint_as_float(v[half * 16]);
+#pragma unroll
+                    for (int j = 1; j < 16; ++j)
+                    {
+                        mx = fmaxf(mx, __uint_as_float(v[half * 16 + j]));
+                    }
+                    if (!__any_sync(FULL_MASK, mx >= thr))
+                    {
+                        continue;
+                    }
+                    const float r_part = -2.0F * thr; // the tighter of the two groups' radii
+#pragma unroll
+                    for (int j = half * 16; j < half * 16 + 16; ++j)
+                    {
+                        const float s = __uint_as_float(v[j]);
+                        const bool cand = s >= thr && j < ncols;
+                        if (__any_sync(FULL_MASK, cand))
+                        {
+                            if (cand)
+                            {
+                                const float d = -2.0F * s;
+                                const int idx = p.index_base + static_cast<int>(col0 + j);
+                                if (d <= r_part && pair_lt(d, idx, r_d, r_x))
+                                {
+                                    my_buf_d[cnt * 32 + lane] = d;
+                                    my_buf_x[cnt * 32 + lane] = idx;
+                                    ++cnt;
+                                }
+                            }
+                        }
+                    }
+                    const unsigned need = __ballot_sync(FULL_MASK, cnt > CAP / 2);
+                    if (need != 0)
+                    {
+                        __syncwarp();
+                        fold_queries(need);
+                        if (live)
+                        {
+                            thr = fmaxf(thr, -0.5F * r_d);
+                        }
+                    }
+                }
+            }
+        }
+        // flush: every live (group, query) leaves a complete list behind, padding included
+        __syncwarp();
+        fold_queries(__ballot_sync(FULL_MASK, live && ok));
+    }
+
+    if (!ok)
+    {
+        atomicOr(p.status, DEVICE_STATUS_TIMEOUT);
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    if (warp == FT_MMA_WARP)
+    {
+        tc::fence_after_sync();
+        tc::tmem_dealloc(tmem_base, FT_TMEM_COLS);
+    }
+}
+
+struct ftc_layout
+{
+    int dim_pad;
+    int split;
+    int kl;
+    int parts;
+    size_t off_pn, off_qn, off_p, off_q, off_ld, off_lx, total;
+};
+
+ftc_layout ftc_layout_of(int64_t n, int64_t q, int dim, int k, bool bf16)
+{
+    ftc_layout l{};
+    const int unit = bf16 ? 64 : 32;
+    l.split = 3 * dim + 3 <= MAX_KB * unit ? 1 : 0;
+    const int ext = (l.split != 0 ? 3 : 1) * dim + 3;
+    l.dim_pad = ((ext + unit - 1) / unit) * unit;
+    l.kl = k <= 32 ? 32 : (k <= 64 ? 64 : (k <= 128 ? 128 : 256));
+    const int64_t nqb = (q + TILE_M - 1) / TILE_M;
+    const int64_t tiles = (n + TILE_N - 1) / TILE_N;
+    // every extra part is one more pair of lists per query that has to find its own radius, so
+    // the database is only split when the query tiles alone cannot occupy the SMs (parts of at
+    // least 64 tiles)
+    const int sms = device_sm_count();
+    const int64_t want = 4 * nqb >= 3 * sms ? 1 : (sms + nqb - 1) / nqb;
+    l.parts = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(want, std::max<int64_t>(1, tiles / 64))));
+    const size_t esz = bf16 ? 2 : 4;
+    l.off_pn = 0;
+    l.off_qn = align256(static_cast<size_t>(n) * 4);
+    l.off_p = l.off_qn + align256(static_cast<size_t>(q) * 4);
+    l.off_q = l.off_p + align256(static_cast<size_t>(n) * l.dim_pad * esz);
+    l.off_ld = l.off_q + align256(static_cast<size_t>(q) * l.dim_pad * esz);
+    const size_t lists = static_cast<size_t>(l.parts) * 2 * static_cast<size_t>(q) * l.kl;
+    l.off_lx = l.off_ld + align256(lists * 4);
+    l.total = l.off_lx + align256(lists * 4);
+    return l;
+}
+
+template <bool BF16, int IPT>
+int launch_ftc(const CUtensorMap& map_q, const CUtensorMap& map_p, const ftc_params& p, size_t smem, int64_t grid,
+               cudaStream_t stream)
+{
+    auto kernel = fused_tc_kernel<BF16, IPT>;
+    BITSKNN_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    kernel<<<static_cast<unsigned>(grid), FT_THREADS, smem, stream>>>(map_q, map_p, p);
+    BITSKNN_CUDA_TRY(cudaGetLastError());
+    return BITSKNN_OK;
+}
+
+template <bool BF16>
+int run_ftc(const float* points, const float* queries, int64_t n, int64_t q, int dim, int k, int32_t index_base,
+            float* out_dist, int32_t* out_idx, unsigned char* ws, cudaStream_t stream)
+{
+    const ftc_layout l = ftc_layout_of(n, q, dim, k, BF16);
+    float* pn = reinterpret_cast<float*>(ws + l.off_pn);
+    float* qn = reinterpret_cast<float*>(ws + l.off_qn);
+    void* cp = ws + l.off_p;
+    void* cq = ws + l.off_q;
+    tc_prepare_kernel<BF16>
+        <<<static_cast<unsigned>((n + 7) / 8), 256, 0, stream>>>(points, n, dim, l.dim_pad, l.split, 1, 1, cp, pn);
+    tc_prepare_kernel<BF16>
+        <<<static_cast<unsigned>((q + 7) / 8), 256, 0, stream>>>(queries, q, dim, l.dim_pad, l.split, 0, 1, cq, qn);
+    BITSKNN_CUDA_TRY(cudaGetLastError());
+
+    CUtensorMap map_q;
+    CUtensorMap map_p;
+    if (const int rc = make_map(&map_q, cq, q, l.dim_pad, BF16); rc != BITSKNN_OK)
+    {
+        return rc;
+    }
+    if (const int rc = make_map(&map_p, cp, n, l.dim_pad, BF16); rc != BITSKNN_OK)
+    {
+        return rc;
+    }
+
+    ftc_params p{};
+    p.list_d = reinterpret_cast<float*>(ws + l.off_ld);
+    p.list_x = reinterpret_cast<int32_t*>(ws + l.off_lx);
+    p.n = n;
+    p.q = q;
+    p.nkb = l.dim_pad / (BF16 ? 64 : 32);
+    p.parts = l.parts;
+    p.tiles = (n + TILE_N - 1) / TILE_N;
+    p.k = k;
+    p.index_base = index_base;
+    p.status = device_status_word();
+    if (p.status == nullptr)
+    {
+        return fail(BITSKNN_ERR_CUDA, "CUDA error. cannot resolve the device status word");
+    }
+    // shared memory: query image + ring + barriers + radii + candidate buffers
+    const size_t fixed = 1024 + 64 * 8 + 2 * TILE_M * 4 + 2 * (8 * CAP * 32 * 4);
+    const int room = static_cast<int>((227 * 1024 - fixed) / STAGE_BYTES) - p.nkb;
+    if (room < 2)
+    {
+        return fail(BITSKNN_ERR_UNSUPPORTED_DIM, "Unsupported dimension: %d (query image does not fit shared memory)", dim);
+    }
+    p.stages = std::min(8, room);
+    const size_t smem = fixed + static_cast<size_t>(p.nkb + p.stages) * STAGE_BYTES;
+    const int64_t nqb = (q + TILE_M - 1) / TILE_M;
+    const int64_t grid = nqb * p.parts;
+    int rc;
+    switch (l.kl)
+    {
+    case 32:
+        rc = launch_ftc<BF16, 1>(map_q, map_p, p, smem, grid, stream);
+        break;
+    case 64:
+        rc = launch_ftc<BF16, 2>(map_q, map_p, p, smem, grid, stream);
+        break;
+    case 128:
+        rc = launch_ftc<BF16, 4>(map_q, map_p, p, smem, grid, stream);
+        break;
+    default:
+        rc = launch_ftc<BF16, 8>(map_q, map_p, p, smem, grid, stream);
+        break;
+    }
+    if (rc != BITSKNN_OK)
+    {
+        return rc;
+    }
+    // merge the 2 * parts lists of every query; the query norm turns the partial distance into
+    // the full squared distance
+    return merge_lists(p.list_d, p.list_x, static_cast<int64_t>(q) * l.kl, l.kl, q, 2 * l.parts, l.kl, k, qn, out_dist,
+                       out_idx, stream);
+}
+
+} // namespace
+
+size_t fused_tc_workspace_bytes(int64_t n, int64_t q, int dim, int k, int mode)
+{
+    if (n <= 0 || q <= 0 || dim <= 0 || k <= 0)
+    {
+        return 0;
+    }
+    return ftc_layout_of(n, q, dim, k, mode == BITSKNN_L2_BF16).total;
+}
+
+int fused_tc_launch(const float* points, const float* queries, int64_t n, int64_t q, int dim, int k, int mode,
+                    int32_t index_base, float* out_dist, int32_t* out_idx, void* workspace, size_t workspace_bytes,
+                    cudaStream_t stream)
+{
+    const bool bf16 = mode == BITSKNN_L2_BF16;
+    const int max_dim = MAX_KB * (bf16 ? 64 : 32) - 3;
+    if (dim > max_dim)
+    {
+        return fail(BITSKNN_ERR_UNSUPPORTED_DIM, "Unsupported dimension: %d (fused tensor-core modes take up to %d)", dim,
+                    max_dim);
+    }
+    const size_t need = fused_tc_workspace_bytes(n, q, dim, k, mode);
+    if (workspace == nullptr || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255U) != 0)
+    {
+        return fail(BITSKNN_ERR_WORKSPACE, "workspace of %zu bytes (256-byte aligned) needed, %zu given", need,
+                    workspace_bytes);
+    }
+    auto* ws = static_cast<unsigned char*>(workspace);
+    return bf16 ? run_ftc<true>(points, queries, n, q, dim, k, index_base, out_dist, out_idx, ws, stream)
+                : run_ftc<false>(points, queries, n, q, dim, k, index_base, out_dist, out_idx, ws, stream);
+}
+
+} // namespace bitsknn

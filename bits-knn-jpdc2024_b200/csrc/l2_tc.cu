@@ -34,6 +34,7 @@
 #include "common.cuh"
 #include "ptx.cuh"
 #include "tc.cuh"
+#include "tc_host.cuh"
 
 namespace bitsknn
 {
@@ -41,10 +42,6 @@ namespace bitsknn
 namespace
 {
 
-constexpr int TILE_M = 128;        // queries per block tile (TMEM lanes)
-constexpr int TILE_N = 128;        // points per MMA tile (TMEM columns per accumulator)
-constexpr int STAGE_BYTES = 16384; // 128 rows x 128 bytes
-constexpr int MAX_KB = 8;          // K blocks of 128 bytes: dim <= 256 (TF32) / 512 (BF16)
 constexpr int TC_THREADS = 320;     // 8 epilogue warps + TMA producer warp + MMA warp
 constexpr int PRODUCER_WARP = 8;
 constexpr int MMA_WARP = 9;
@@ -65,80 +62,6 @@ struct tc_params
     int64_t tiles; // point tiles
     int* status;
 };
-
-// Pre-pass, one warp per row: writes the FP32 norm of the row and its MMA-input image.
-//
-// Plain image: the row rounded to nearest in the input type, zero padded to `ext_pad`.
-// Split image (`split` != 0): every coordinate v is written as hi = rn(v) and lo = rn(v - hi),
-// and the row is laid out along K as
-//     queries  [hi | hi | lo]      points  [hi | lo | hi]
-// so that ONE contraction over 3 * dim yields hi.hi + hi.lo + lo.hi -- the product with the
-// rounding error of both inputs compensated to first order (only lo.lo is dropped).
-template <bool BF16>
-__global__ void tc_prepare_kernel(const float* __restrict__ src, int64_t rows, int dim, int ext_pad, int split,
-                                  int is_points, void* __restrict__ dst, float* __restrict__ norms)
-{
-    const int lane = threadIdx.x & 31;
-    const int64_t row = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-    if (row >= rows)
-    {
-        return;
-    }
-    auto round_in = [](float v) -> float {
-        if constexpr (BF16)
-        {
-            return __bfloat162float(__float2bfloat16_rn(v));
-        }
-        else
-        {
-            uint32_t t;
-            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(t) : "f"(v));
-            return __uint_as_float(t);
-        }
-    };
-    auto store = [&](int c, float v) {
-        if constexpr (BF16)
-        {
-            static_cast<__nv_bfloat16*>(dst)[row * ext_pad + c] = __float2bfloat16_rn(v);
-        }
-        else
-        {
-            static_cast<float*>(dst)[row * ext_pad + c] = v;
-        }
-    };
-    const float* in = src + row * dim;
-    float nrm = 0.0F;
-    for (int d = lane; d < dim; d += 32)
-    {
-        const float v = in[d];
-        nrm = fmaf(v, v, nrm);
-        const float hi = round_in(v);
-        if (split != 0)
-        {
-            const float lo = round_in(v - hi);
-            store(d, hi);
-            store(dim + d, is_points != 0 ? lo : hi);
-            store(2 * dim + d, is_points != 0 ? hi : lo);
-        }
-        else
-        {
-            store(d, hi);
-        }
-    }
-    for (int c = (split != 0 ? 3 : 1) * dim + lane; c < ext_pad; c += 32)
-    {
-        store(c, 0.0F);
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1)
-    {
-        nrm += __shfl_xor_sync(FULL_MASK, nrm, o);
-    }
-    if (lane == 0)
-    {
-        norms[row] = nrm;
-    }
-}
 
 template <bool BF16>
 __global__ void __launch_bounds__(TC_THREADS, 1)
@@ -322,7 +245,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                     }
                 }
             }
-            if (!ptx::mbar_wait_bounded(&acc_full[group], static_cast<uint32_t>(use & 1)))
+            // (the verdict is made warp-uniform: the lanes poll independently)
+            if (!__all_sync(FULL_MASK, ptx::mbar_wait_bounded(&acc_full[group], static_cast<uint32_t>(use & 1))))
             {
                 ok = false;
                 break;
@@ -409,50 +333,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     }
 }
 
-using encode_fn_t = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-encode_fn_t tensor_map_encoder()
-{
-    static std::once_flag once;
-    static encode_fn_t fn = nullptr;
-    std::call_once(once, [] {
-        void* ptr = nullptr;
-        cudaDriverEntryPointQueryResult res;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &res) == cudaSuccess &&
-            res == cudaDriverEntryPointSuccess)
-        {
-            fn = reinterpret_cast<encode_fn_t>(ptr);
-        }
-    });
-    return fn;
-}
-
-// rows x dim_pad matrix of 4-byte (TF32) or 2-byte (BF16) elements, box = 128 bytes x 128 rows
-int make_map(CUtensorMap* map, void* base, int64_t rows, int dim_pad, bool bf16)
-{
-    encode_fn_t encode = tensor_map_encoder();
-    if (encode == nullptr)
-    {
-        return fail(BITSKNN_ERR_CUDA, "CUDA error. cuTensorMapEncodeTiled is not available from this driver");
-    }
-    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(dim_pad), static_cast<cuuint64_t>(rows)};
-    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(dim_pad) * (bf16 ? 2U : 4U)};
-    const cuuint32_t box[2] = {bf16 ? 64U : 32U, 128U};
-    const cuuint32_t elem[2] = {1U, 1U};
-    const CUresult rc = encode(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, base,
-                               dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (rc != CUDA_SUCCESS)
-    {
-        return fail(BITSKNN_ERR_CUDA, "CUDA error. cuTensorMapEncodeTiled failed with code %d", static_cast<int>(rc));
-    }
-    return BITSKNN_OK;
-}
-
-size_t align256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
-
 struct tc_layout
 {
     int dim_pad; // length of a row image along K (elements), whole 128-byte blocks
@@ -489,9 +369,9 @@ int run_tc(const float* points, const float* queries, int64_t n, int64_t q, int 
     void* cp = ws + l.off_p;
     void* cq = ws + l.off_q;
     tc_prepare_kernel<BF16>
-        <<<static_cast<unsigned>((n + 7) / 8), 256, 0, stream>>>(points, n, dim, l.dim_pad, l.split, 1, cp, pn);
+        <<<static_cast<unsigned>((n + 7) / 8), 256, 0, stream>>>(points, n, dim, l.dim_pad, l.split, 1, 0, cp, pn);
     tc_prepare_kernel<BF16>
-        <<<static_cast<unsigned>((q + 7) / 8), 256, 0, stream>>>(queries, q, dim, l.dim_pad, l.split, 0, cq, qn);
+        <<<static_cast<unsigned>((q + 7) / 8), 256, 0, stream>>>(queries, q, dim, l.dim_pad, l.split, 0, 0, cq, qn);
     BITSKNN_CUDA_TRY(cudaGetLastError());
 
     CUtensorMap map_q;

@@ -550,14 +550,15 @@ __global__ void __launch_bounds__(THREADS) select_kernel(const select_params p)
 template <int THREADS, int IPT>
 __global__ void __launch_bounds__(THREADS)
     merge_kernel(const float* __restrict__ cand_dist, const int32_t* __restrict__ cand_idx, int64_t list_stride,
-                 int64_t query_stride, int lists, int k, float* __restrict__ out_dist, int32_t* __restrict__ out_idx)
+                 int64_t query_stride, int lists, int kin, int k, const float* __restrict__ bias,
+                 float* __restrict__ out_dist, int32_t* __restrict__ out_idx)
 {
     constexpr int L = THREADS * IPT;
     __shared__ float sd[L];
     __shared__ int sx[L];
     const int tid = threadIdx.x;
     const int64_t query = blockIdx.x;
-    const int total = lists * k;
+    const int total = lists * kin; // `kin` candidates per list, the `k` smallest pairs are reported
 
     float ld[IPT];
     int lx[IPT];
@@ -579,8 +580,8 @@ __global__ void __launch_bounds__(THREADS)
             cx[r] = PAD_IDX;
             if (ci < total)
             {
-                const int l = ci / k;
-                const int j = ci - l * k;
+                const int l = ci / kin;
+                const int j = ci - l * kin;
                 const int64_t at = l * list_stride + query * query_stride + j;
                 cd[r] = cand_dist[at];
                 cx[r] = cand_idx[at];
@@ -594,11 +595,21 @@ __global__ void __launch_bounds__(THREADS)
         const int e = tid * IPT + r;
         if (e < k)
         {
-            out_dist[query * k + e] = ld[r];
+            // `bias` (optional, one value per query) is added to every reported distance
+            out_dist[query * k + e] = bias != nullptr ? ld[r] + bias[query] : ld[r];
             out_idx[query * k + e] = lx[r] == PAD_IDX ? e : lx[r];
         }
     }
 }
+
+} // namespace
+
+// Merge `lists` lists of `kin` pairs per query into the `k` smallest (library-internal; see common.cuh).
+int merge_lists(const float* cd, const int32_t* cx, int64_t list_stride, int64_t query_stride, int64_t q, int lists,
+                int kin, int k, const float* bias, float* od, int32_t* ox, cudaStream_t stream);
+
+namespace
+{
 
 size_t select_smem_bytes(int L, int stage_floats, int stages)
 {
@@ -641,10 +652,10 @@ int dispatch_select(const select_params& p, int64_t vrows, cudaStream_t stream)
 
 template <int IPT>
 int launch_merge(const float* cd, const int32_t* cx, int64_t list_stride, int64_t query_stride, int64_t q, int lists,
-                 int k, float* od, int32_t* ox, cudaStream_t stream)
+                 int kin, int k, const float* bias, float* od, int32_t* ox, cudaStream_t stream)
 {
-    merge_kernel<SELECT_THREADS, IPT>
-        <<<static_cast<unsigned>(q), SELECT_THREADS, 0, stream>>>(cd, cx, list_stride, query_stride, lists, k, od, ox);
+    merge_kernel<SELECT_THREADS, IPT><<<static_cast<unsigned>(q), SELECT_THREADS, 0, stream>>>(
+        cd, cx, list_stride, query_stride, lists, kin, k, bias, od, ox);
     BITSKNN_CUDA_TRY(cudaGetLastError());
     return BITSKNN_OK;
 }
@@ -652,20 +663,31 @@ int launch_merge(const float* cd, const int32_t* cx, int64_t list_stride, int64_
 int dispatch_merge(const float* cd, const int32_t* cx, int64_t list_stride, int64_t query_stride, int64_t q, int lists,
                    int k, float* od, int32_t* ox, cudaStream_t stream)
 {
+    return merge_lists(cd, cx, list_stride, query_stride, q, lists, k, k, nullptr, od, ox, stream);
+}
+
+} // namespace
+
+int merge_lists(const float* cd, const int32_t* cx, int64_t list_stride, int64_t query_stride, int64_t q, int lists,
+                int kin, int k, const float* bias, float* od, int32_t* ox, cudaStream_t stream)
+{
     if (k <= 256)
     {
-        return launch_merge<1>(cd, cx, list_stride, query_stride, q, lists, k, od, ox, stream);
+        return launch_merge<1>(cd, cx, list_stride, query_stride, q, lists, kin, k, bias, od, ox, stream);
     }
     if (k <= 512)
     {
-        return launch_merge<2>(cd, cx, list_stride, query_stride, q, lists, k, od, ox, stream);
+        return launch_merge<2>(cd, cx, list_stride, query_stride, q, lists, kin, k, bias, od, ox, stream);
     }
     if (k <= 1024)
     {
-        return launch_merge<4>(cd, cx, list_stride, query_stride, q, lists, k, od, ox, stream);
+        return launch_merge<4>(cd, cx, list_stride, query_stride, q, lists, kin, k, bias, od, ox, stream);
     }
-    return launch_merge<8>(cd, cx, list_stride, query_stride, q, lists, k, od, ox, stream);
+    return launch_merge<8>(cd, cx, list_stride, query_stride, q, lists, kin, k, bias, od, ox, stream);
 }
+
+namespace
+{
 
 int check_select_args(const float* d_dist, int64_t ld, int64_t q, int64_t n, int k, const float* od, const int32_t* ox)
 {

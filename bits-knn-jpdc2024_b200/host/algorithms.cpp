@@ -240,11 +240,19 @@ void bits_sq_knn::selection()
     BITS_CUCH(cudaStreamSynchronize(nullptr));
 }
 
+void fused_knn::initialize(const knn_args& args)
+{
+    cuda_knn::initialize(args);
+    workspace_ = device_buffer<unsigned char>{bitsknn_fused_workspace_bytes(
+        static_cast<std::int64_t>(point_count()), static_cast<std::int64_t>(query_count()), static_cast<int>(dim()),
+        static_cast<int>(k()), mode_)};
+}
+
 void fused_knn::selection()
 {
     abi_check(bitsknn_fused(dist_impl_->points_gpu(), dist_impl_->queries_gpu(), static_cast<std::int64_t>(point_count()),
                             static_cast<std::int64_t>(query_count()), static_cast<int>(dim()), static_cast<int>(k()),
-                            BITSKNN_L2_PARTIAL, 0, out_dist_gpu(), out_label_gpu(), nullptr));
+                            mode_, 0, out_dist_gpu(), out_label_gpu(), workspace_.data(), workspace_.size(), nullptr));
     BITS_CUCH(cudaStreamSynchronize(nullptr));
 }
 
@@ -335,6 +343,8 @@ std::vector<std::unique_ptr<knn>> make_registry()
     algorithms.push_back(std::make_unique<bits_sq_knn>());
     algorithms.push_back(std::make_unique<fused_knn>("fused-cache"));
     algorithms.push_back(std::make_unique<fused_knn>("bits-fused"));
+    algorithms.push_back(std::make_unique<fused_knn>("bits-fused-tf32", BITSKNN_L2_TF32));
+    algorithms.push_back(std::make_unique<fused_knn>("bits-fused-bf16", BITSKNN_L2_BF16));
     algorithms.push_back(std::make_unique<dist_runner>(BITSKNN_L2_EXACT, "magma-dist"));
     algorithms.push_back(std::make_unique<dist_runner>(BITSKNN_L2_PARTIAL, "magma-part-dist"));
     algorithms.push_back(std::make_unique<dist_runner>(BITSKNN_L2_TF32, "tc-dist-tf32"));

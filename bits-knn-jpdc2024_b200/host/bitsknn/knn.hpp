@@ -267,8 +267,9 @@ private:
 class fused_knn : public cuda_knn
 {
 public:
-    explicit fused_knn(std::string id = "fused-cache") : id_(std::move(id)) {}
+    explicit fused_knn(std::string id = "fused-cache", int mode = BITSKNN_L2_PARTIAL) : id_(std::move(id)), mode_(mode) {}
     std::string id() const override { return id_; }
+    void initialize(const knn_args& args) override;
     void distances() override {}
     void selection() override;
 
@@ -277,6 +278,8 @@ protected:
 
 private:
     std::string id_;
+    int mode_;
+    device_buffer<unsigned char> workspace_; // tensor-core modes only
 };
 
 // Distance-only registry entries (reference: dist_runner<D>, include/bits/distance/dist_runner.hpp:8-15).

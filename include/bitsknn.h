@@ -153,13 +153,20 @@ int bitsknn_l2(const float* d_points, const float* d_queries, int64_t n, int64_t
  * include/bits/topk/singlepass/fused_cache_kernel.hpp:35-36).
  *
  *   mode        BITSKNN_L2_PARTIAL (FP32 FFMA, bit-exact with the reference's fused kernel:
- *               reported distances are |x|^2 - 2 x.y) or BITSKNN_L2_EXACT
+ *               reported distances are |x|^2 - 2 x.y), BITSKNN_L2_EXACT (FP32, sum (x-y)^2), or
+ *               BITSKNN_L2_TF32 / BITSKNN_L2_BF16: the distance tile is produced by tcgen05
+ *               tensor-core MMAs in tensor memory and consumed from there (reported distances
+ *               are |x|^2 + |y|^2 - 2 x.y; checked against the FP32 path by recall@k and k-th
+ *               distance error, not bit-exact)
  *   k           1 <= k <= BITSKNN_FUSED_MAX_K
  *   index_base  added to every reported index (shard base of a sharded database)
+ *   d_workspace tensor-core modes only: bitsknn_fused_workspace_bytes() bytes, 256-byte aligned
+ *               (input images, norms and the per-block partial lists); FP32 modes pass NULL, 0
  * --------------------------------------------------------------------------------------- */
+size_t bitsknn_fused_workspace_bytes(int64_t n, int64_t q, int dim, int k, int mode);
 int bitsknn_fused(const float* d_points, const float* d_queries, int64_t n, int64_t q, int dim, int k,
-                  int mode, int32_t index_base, float* d_out_dist, int32_t* d_out_idx,
-                  bitsknn_stream_t stream);
+                  int mode, int32_t index_base, float* d_out_dist, int32_t* d_out_idx, void* d_workspace,
+                  size_t workspace_bytes, bitsknn_stream_t stream);
 
 #ifdef __cplusplus
 }

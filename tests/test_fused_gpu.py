@@ -85,5 +85,5 @@ def test_argument_errors(bk, cuda):
         bk.fused(x, x, 512)
     assert err.value.status == bk.ERR_UNSUPPORTED_K and "Unsupported k value: 512" in err.value.message
     with pytest.raises(bk.BitsKnnError) as err:
-        bk.fused(x, x, 8, mode=bk.L2_BF16)
+        bk.fused(x, x, 8, mode=42)
     assert err.value.status == bk.ERR_UNSUPPORTED_MODE

@@ -1,0 +1,82 @@
+"""`bits-fused` tensor-core modes (tcgen05 MMA into tensor memory feeding the top-k directly)
+against the FP32 fused path.  Tolerances stated for these modes: recall@k >= 0.999 and
+relative error of the k-th distance <= 1e-3.  Structural properties are exact: ascending
+distances, valid distinct indices, reported distance consistent with the reported index."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def check_against_fp32(bk, points, queries, k, mode, index_base=0):
+    d_tc, i_tc = bk.fused(points, queries, k, mode=mode, index_base=index_base)
+    torch.cuda.synchronize()
+    bk.device_status()
+    d_ex, i_ex = bk.fused(points, queries, k, mode=bk.L2_EXACT, index_base=index_base)
+    n = points.shape[0]
+    kk = min(k, n)
+    # structure
+    assert bool((d_tc[:, 1:kk] >= d_tc[:, :kk - 1]).all())
+    local = (i_tc[:, :kk] - index_base).long()
+    assert bool(((local >= 0) & (local < n)).all())
+    srt = torch.sort(local, dim=1).values
+    assert bool((srt[:, 1:] != srt[:, :-1]).all()), "duplicate indices in a result"
+    # reported distance belongs to the reported index (FP32 recomputation)
+    diff = queries[:, None, :] - points[local]
+    true_d = (diff * diff).sum(-1)
+    scale = true_d.abs().max().item() + 1.0
+    assert (d_tc[:, :kk] - true_d).abs().max().item() <= 2e-3 * scale
+    # quality
+    a, b = i_tc[:, :kk].cpu().numpy(), i_ex[:, :kk].cpu().numpy()
+    hits = sum(len(np.intersect1d(a[r], b[r])) for r in range(a.shape[0]))
+    recall = hits / a.size
+    rel = ((d_tc[:, kk - 1] - d_ex[:, kk - 1]).abs() / d_ex[:, kk - 1].abs().clamp_min(1e-6)).max().item()
+    assert recall >= 0.999, recall
+    assert rel <= 1e-3, rel
+
+
+@pytest.mark.parametrize("mode_name,dim", [("tf32", 4), ("tf32", 16), ("tf32", 32), ("tf32", 64), ("bf16", 8),
+                                           ("bf16", 32), ("bf16", 64), ("bf16", 128)])
+@pytest.mark.parametrize("k", [16, 128])
+def test_quality_versus_fp32(bk, cuda, mode_name, dim, k):
+    mode = bk.L2_TF32 if mode_name == "tf32" else bk.L2_BF16
+    gen = torch.Generator(device="cuda").manual_seed(dim * 1000 + k)
+    points = torch.rand((50000, dim), generator=gen, device="cuda")
+    queries = torch.rand((300, dim), generator=gen, device="cuda")
+    check_against_fp32(bk, points, queries, k, mode)
+
+
+@pytest.mark.parametrize("n,q,k", [(1000, 1, 32), (129, 129, 64), (128, 128, 128), (5000, 257, 100), (20001, 64, 256),
+                                   (40, 3, 64)])
+def test_ragged_shapes(bk, cuda, n, q, k):
+    gen = torch.Generator(device="cuda").manual_seed(n + q + k)
+    points = torch.rand((n, 16), generator=gen, device="cuda")
+    queries = torch.rand((q, 16), generator=gen, device="cuda")
+    check_against_fp32(bk, points, queries, k, bk.L2_TF32, index_base=1000)
+
+
+def test_many_parts_and_clustered_data(bk, cuda):
+    # 2^18 points: several blocks per query tile; clustered data (256 centres, sigma 0.05)
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    dim, n, q = 32, 1 << 18, 512
+    centres = torch.rand((256, dim), generator=gen, device="cuda")
+    pick = torch.randint(0, 256, (n,), generator=gen, device="cuda")
+    points = centres[pick] + 0.05 * torch.randn((n, dim), generator=gen, device="cuda")
+    pickq = torch.randint(0, 256, (q,), generator=gen, device="cuda")
+    queries = centres[pickq] + 0.05 * torch.randn((q, dim), generator=gen, device="cuda")
+    check_against_fp32(bk, points.contiguous(), queries.contiguous(), 32, bk.L2_BF16)
+
+
+def test_workspace_and_dim_limits(bk, cuda):
+    x = torch.rand((256, 16), device="cuda")
+    assert bk.fused_workspace_bytes(256, 256, 16, 32, bk.L2_PARTIAL) == 0
+    need = bk.fused_workspace_bytes(256, 256, 16, 32, bk.L2_TF32)
+    assert need > 0
+    with pytest.raises(bk.BitsKnnError) as err:
+        bk.fused(x, x, 32, mode=bk.L2_TF32, workspace=torch.empty(256, dtype=torch.uint8, device="cuda"))
+    assert err.value.status == bk.ERR_WORKSPACE
+    big = torch.rand((64, 300), device="cuda")
+    with pytest.raises(bk.BitsKnnError) as err:
+        bk.fused(big, big, 8, mode=bk.L2_TF32)
+    assert err.value.status == bk.ERR_UNSUPPORTED_DIM
