@@ -137,6 +137,70 @@ def cpu_selection_baseline(host_matrix, k, budget_s=20.0):
                       f"median of {len(times)} runs"}
 
 
+def knn_section(bk, dev):
+    """Fused k-NN (the other hot path): n = 2^20 points, q = 2^14 queries, Uniform[0,1), kernel
+    time by CUDA events.  FP32 is the bit-exact mode; tf32 / bf16 run on tcgen05.  For the
+    largest case the unfused pipelines (distance GEMM + bits selection, in query batches) and,
+    where it was compiled, the reference's own fused-cache kernel are timed beside it."""
+    import torch
+
+    def timed(fn, reps):
+        fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    n, q = 1 << 20, 1 << 14
+    gen = torch.Generator(device=dev).manual_seed(42)
+    result = {"n": n, "q": q, "data": "Uniform[0,1) coordinates, seed 42", "cases": {}}
+    modes = (("fp32", bk.L2_PARTIAL), ("tf32", bk.L2_TF32), ("bf16", bk.L2_BF16))
+    for dim, k in ((16, 32), (64, 128)):
+        points = torch.rand((n, dim), generator=gen, device=dev)
+        queries = torch.rand((q, dim), generator=gen, device=dev)
+        out = (torch.empty((q, k), device=dev), torch.empty((q, k), dtype=torch.int32, device=dev))
+        for name, mode in modes:
+            ws = torch.empty(max(bk.fused_workspace_bytes(n, q, dim, k, mode), 256), dtype=torch.uint8, device=dev)
+            ms = timed(lambda: bk.fused(points, queries, k, mode=mode, out=out, workspace=ws), 1 if name == "fp32" else 3)
+            result["cases"][f"fused_{name}_dim{dim}_k{k}"] = {"ms": ms, "queries_per_s": q / (ms * 1e-3),
+                                                             "distances_per_s": q * n / (ms * 1e-3)}
+            del ws
+        # unfused: distance matrix for 2048 queries at a time (8 GiB), then the bits selection
+        qb = 2048
+        dist = torch.empty((qb, n), device=dev)
+        sel = (torch.empty((qb, k), device=dev), torch.empty((qb, k), dtype=torch.int32, device=dev))
+        for name, mode in (("fp32", bk.L2_PARTIAL), ("bf16", bk.L2_BF16)):
+            ws = torch.empty(max(bk.l2_workspace_bytes(n, qb, dim, mode), 256), dtype=torch.uint8, device=dev)
+
+            def unfused():
+                for b in range(0, q, qb):
+                    bk.l2(points, queries[b:b + qb], mode=mode, out=dist, workspace=ws)
+                    bk.select(dist, k, out=sel)
+
+            ms = timed(unfused, 1)
+            result["cases"][f"unfused_{name}_gemm_plus_bits_dim{dim}_k{k}"] = {"ms": ms, "queries_per_s": q / (ms * 1e-3)}
+            del ws
+        del dist
+        try:
+            from oracle import ref_select
+            if ref_select.available():
+                sub = 4096  # a quarter of the queries; the kernel is linear in q
+                _, _, sec = ref_select.fused_cache(points.cpu().numpy(), queries[:sub].cpu().numpy(), k,
+                                                   block_query_dim=1, dim_mult=1, repeats=1)
+                result["cases"][f"reference_fused_cache_dim{dim}_k{k}"] = {
+                    "ms": sec * 1e3 * (q / sub), "queries_per_s": sub / sec,
+                    "note": "the reference's fused-cache kernel (8,4,2 / block-query-dim 1 / dim-mult 1) compiled "
+                            f"from its sources, timed on {sub} queries and scaled to {q}"}
+        except Exception as err:
+            result["cases"][f"reference_fused_cache_dim{dim}_k{k}"] = {"unavailable": str(err)}
+        torch.cuda.empty_cache()
+    return result
+
+
 def run_reference_arm(args):
     """The reference's own CPU implementation of the path, timed on the host cores."""
     import numpy as np
@@ -233,8 +297,6 @@ def main():
     gen = torch.Generator(device=dev).manual_seed(42 + rank)
     matrix = torch.rand((q, n), generator=gen, device=dev, dtype=torch.float32)
     offsets = torch.full((q,), rank * n, dtype=torch.int32, device=dev)  # global column index of the shard
-    out_d = torch.empty((q, k), dtype=torch.float32, device=dev)
-    out_i = torch.empty((q, k), dtype=torch.int32, device=dev)
     if world > 1:
         fin_d = torch.empty((q, k), dtype=torch.float32, device=dev)
         fin_i = torch.empty((q, k), dtype=torch.int32, device=dev)
@@ -243,10 +305,11 @@ def main():
     from importlib import import_module
     search = import_module(entry.PKG_NAME + ".sharded").ShardedSearch(bk, rank, world)
 
+    out_d, out_i = search.local_views(q, k, dev)  # the local candidates live in the exchange buffer
+
     def step(src=matrix):
-        # local selection with global labels, then (N > 1) NCCL all-gather + merge kernel
-        search.select(src, k, rank * n, offsets=offsets, local_out=(out_d, out_i),
-                      out=None if world == 1 else (fin_d, fin_i))
+        # local selection with global labels, then (N > 1) ONE NCCL all-gather + merge kernel
+        search.select(src, k, rank * n, offsets=offsets, out=None if world == 1 else (fin_d, fin_i))
 
     def barrier():
         torch.cuda.synchronize()
@@ -283,7 +346,7 @@ def main():
         bk.select(matrix, k, label_offsets=offsets, out=(out_d, out_i))
         ev[2 * s + 1].record()
         if world > 1:
-            search._exchange_and_merge(out_d, out_i, out=(fin_d, fin_i))
+            search._exchange_and_merge(q, k, dev, out=(fin_d, fin_i))
     ev[-1].record()
     barrier()
     clocks = sampler.stop() if rank == 0 else None
@@ -368,10 +431,36 @@ def main():
                "h2d_bytes_per_step": 4 * q * n, "d2h_bytes_per_step": 8 * q * k}
         del staging
 
+    # ---- same-box comparator: the reference's own `bits-prefetch` kernel, recompiled ---------
+    reference_gpu = None
+    if rank == 0 and world == 1 and not args.no_cpu and host is not None:
+        try:
+            from oracle import ref_select
+            if ref_select.available():
+                host_np = host.numpy()
+                ref_sel = {}
+                for kk in sorted({32, k, 2048}):
+                    _, _, sec = ref_select.select("bits-prefetch", host_np, kk, block_size=256, batch=13, repeats=3)
+                    ref_sel[f"k{kk}"] = {"ms": sec * 1e3, "distances_per_s": q * n / sec}
+                reference_gpu = {"what": "the reference's bits-prefetch kernel compiled from its sources for sm_100a "
+                                         "(block 256, batch 13: its tuned H100 shape), same matrix, host-timed "
+                                         "selection() like its main loop, fastest of 3",
+                                 "uniform": ref_sel}
+        except Exception as err:  # the comparator is optional
+            reference_gpu = {"unavailable": str(err)}
+
+    knn = None
+    if rank == 0 and world == 1 and not args.no_sweep:
+        del matrix
+        torch.cuda.empty_cache()
+        knn = knn_section(bk, dev)
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
-        host_np = (host if host is not None else matrix.cpu()).numpy()
-        cpu = cpu_selection_baseline(host_np, k)
+        if host is None:
+            gen2 = torch.Generator(device=dev).manual_seed(42)
+            host = torch.rand((64, n), generator=gen2, device=dev, dtype=torch.float32).cpu()
+        cpu = cpu_selection_baseline(host.numpy(), k)
 
     if rank == 0:
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
@@ -385,6 +474,10 @@ def main():
                 "gpu_launches": launches_per_step * args.steps, "clocks": clocks}
         if sweep is not None:
             line["sweep"] = sweep
+        if reference_gpu is not None:
+            line["reference_gpu"] = reference_gpu
+        if knn is not None:
+            line["knn"] = knn
         print(json.dumps(line), flush=True)
     if world > 1:
         dist_pg.destroy_process_group()

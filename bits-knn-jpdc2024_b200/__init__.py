@@ -185,6 +185,20 @@ def merge(cand_dist, cand_idx, out=None):
     return out
 
 
+def merge_strided(cand_dist, cand_idx, list_stride, query_stride, q, lists, k, out=None):
+    """Merge with explicit element strides: pair j of list l of query i at
+    [l * list_stride + i * query_stride + j] from the first element of each tensor."""
+    import torch
+    _device_check(cand_dist, torch.float32, "cand_dist")
+    _device_check(cand_idx, torch.int32, "cand_idx")
+    if out is None:
+        out = (torch.empty((q, k), dtype=torch.float32, device=cand_dist.device),
+               torch.empty((q, k), dtype=torch.int32, device=cand_dist.device))
+    _check(lib().bitsknn_merge(_p(cand_dist), _p(cand_idx), list_stride, query_stride, q, lists, k, _p(out[0]),
+                               _p(out[1]), _stream()))
+    return out
+
+
 def l2_workspace_bytes(n, q, dim, mode):
     return int(lib().bitsknn_l2_workspace_bytes(n, q, dim, mode))
 

@@ -28,36 +28,46 @@ class ShardedSearch:
         self.rank = rank
         self.world = world
         self.group = group
-        self._gather = {}
+        self._packs = {}
 
     def _buffers(self, q, k, device):
+        """One float32 buffer [2][q][k] for this rank's candidates (plane 0: distances, plane 1:
+        the int32 labels, bit-cast) and one [world][2][q][k] for the gathered ones, so that the
+        exchange is a single collective."""
         key = (q, k, str(device))
-        if key not in self._gather:
-            self._gather[key] = (torch.empty((self.world, q, k), dtype=torch.float32, device=device),
-                                 torch.empty((self.world, q, k), dtype=torch.int32, device=device))
-        return self._gather[key]
+        if key not in self._packs:
+            self._packs[key] = (torch.empty((2, q, k), dtype=torch.float32, device=device),
+                                torch.empty((self.world, 2, q, k), dtype=torch.float32, device=device))
+        return self._packs[key]
 
-    def _exchange_and_merge(self, local_d, local_i, out=None):
+    def local_views(self, q, k, device):
+        """(distances, labels) views of the local candidate buffer: kernels write straight into it."""
+        local, _ = self._buffers(q, k, device)
+        return local[0], local.view(torch.int32)[1]
+
+    def _exchange_and_merge(self, q, k, device, out=None):
+        local, gathered = self._buffers(q, k, device)
         if self.world == 1:
-            return local_d, local_i
+            return local[0], local.view(torch.int32)[1]
         import torch.distributed as dist
-        q, k = local_d.shape
-        all_d, all_i = self._buffers(q, k, local_d.device)
-        # (world*q, k) output view: the concatenated form every backend accepts
-        dist.all_gather_into_tensor(all_d.view(self.world * q, k), local_d.contiguous(), group=self.group)
-        dist.all_gather_into_tensor(all_i.view(self.world * q, k), local_i.contiguous(), group=self.group)
-        return self.kernels.merge(all_d, all_i, out=out)
+        # (world*2*q, k) / (2*q, k) views: the concatenated form every backend accepts
+        dist.all_gather_into_tensor(gathered.view(self.world * 2 * q, k), local.view(2 * q, k), group=self.group)
+        return self.kernels.merge_strided(gathered[:, 0], gathered.view(torch.int32)[:, 1], list_stride=2 * q * k,
+                                          query_stride=k, q=q, lists=self.world, k=k, out=out)
 
-    def select(self, local_matrix, k, shard_begin, offsets=None, local_out=None, out=None):
+    def select(self, local_matrix, k, shard_begin, offsets=None, out=None):
         """Top-k of the rows of the full matrix whose columns [shard_begin, ...) this rank holds."""
         q = local_matrix.shape[0]
         if offsets is None:
             offsets = torch.full((q,), shard_begin, dtype=torch.int32, device=local_matrix.device)
-        d, i = self.kernels.select(local_matrix, k, label_offsets=offsets, out=local_out)
-        return self._exchange_and_merge(d, i, out=out)
+        views = self.local_views(q, k, local_matrix.device)
+        self.kernels.select(local_matrix, k, label_offsets=offsets, out=views)
+        return self._exchange_and_merge(q, k, local_matrix.device, out=out)
 
-    def knn(self, local_points, queries, k, shard_begin, local_out=None, out=None, **kw):
+    def knn(self, local_points, queries, k, shard_begin, out=None, **kw):
         """k nearest points of the full database for every query; this rank holds
         points [shard_begin, shard_begin + len(local_points))."""
-        d, i = self.kernels.fused(local_points, queries, k, index_base=shard_begin, out=local_out, **kw)
-        return self._exchange_and_merge(d, i, out=out)
+        q = queries.shape[0]
+        views = self.local_views(q, k, queries.device)
+        self.kernels.fused(local_points, queries, k, index_base=shard_begin, out=views, **kw)
+        return self._exchange_and_merge(q, k, queries.device, out=out)

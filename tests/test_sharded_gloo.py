@@ -23,14 +23,21 @@ class OracleKernels:
 
     def select(self, dist, k, label_offsets=None, out=None):
         d, i = self.oracle.select(dist.numpy(), k, label_offsets=None if label_offsets is None else label_offsets.numpy())
-        return torch.from_numpy(d), torch.from_numpy(i)
+        out[0].copy_(torch.from_numpy(d))
+        out[1].copy_(torch.from_numpy(i))
+        return out
 
     def fused(self, points, queries, k, index_base=0, out=None):
         d, i = self.oracle.knn(points.numpy(), queries.numpy(), k, partial=True, index_base=index_base)
-        return torch.from_numpy(d), torch.from_numpy(i)
+        out[0].copy_(torch.from_numpy(d))
+        out[1].copy_(torch.from_numpy(i))
+        return out
 
-    def merge(self, cand_d, cand_i, out=None):
-        d, i = self.oracle.merge(cand_d.numpy(), cand_i.numpy())
+    def merge_strided(self, cand_d, cand_i, list_stride, query_stride, q, lists, k, out=None):
+        # strided views of the gathered buffer -> (lists, q, k) arrays for the oracle
+        assert cand_d.shape == (lists, q, k) and cand_d.stride() == (list_stride, query_stride, 1)
+        assert cand_i.shape == (lists, q, k) and cand_i.stride() == (list_stride, query_stride, 1)
+        d, i = self.oracle.merge(np.ascontiguousarray(cand_d.numpy()), np.ascontiguousarray(cand_i.numpy()))
         return torch.from_numpy(d), torch.from_numpy(i)
 
 
