@@ -201,6 +201,41 @@ def knn_section(bk, dev):
     return result
 
 
+def run_profile_case(name):
+    """Small cases of the k-NN kernels for profiler captures: a few hundred MB on the device,
+    three launches each (inputs larger than L2 where the kernel streams them)."""
+    import torch
+    import __graft_entry__ as entry
+    bk = entry.load_package()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    gen = torch.Generator(device=dev).manual_seed(42)
+    dim, k = 64, 128
+    if name in ("fused_tc", "fused_fp32"):
+        n, q = 1 << 18, 148 * 128                       # one query tile per SM
+        mode = bk.L2_BF16 if name == "fused_tc" else bk.L2_PARTIAL
+        if name == "fused_fp32":
+            q = 148 * 2 * 8
+        points = torch.rand((n, dim), generator=gen, device=dev)
+        queries = torch.rand((q, dim), generator=gen, device=dev)
+        ws = torch.empty(max(bk.fused_workspace_bytes(n, q, dim, k, mode), 256), dtype=torch.uint8, device=dev)
+        out = (torch.empty((q, k), device=dev), torch.empty((q, k), dtype=torch.int32, device=dev))
+        for _ in range(3):
+            bk.fused(points, queries, k, mode=mode, out=out, workspace=ws)
+    else:
+        n, q = 1 << 18, 2048                            # 2 GiB distance matrix
+        mode = bk.L2_BF16 if name == "l2_tc" else bk.L2_PARTIAL
+        points = torch.rand((n, dim), generator=gen, device=dev)
+        queries = torch.rand((q, dim), generator=gen, device=dev)
+        ws = torch.empty(max(bk.l2_workspace_bytes(n, q, dim, mode), 256), dtype=torch.uint8, device=dev)
+        out = torch.empty((q, n), device=dev)
+        for _ in range(3):
+            bk.l2(points, queries, mode=mode, out=out, workspace=ws)
+    torch.cuda.synchronize()
+    bk.device_status()
+    print(json.dumps({"profile_case": name, "n": n, "q": q, "dim": dim, "k": k}))
+
+
 def run_reference_arm(args):
     """The reference's own CPU implementation of the path, timed on the host cores."""
     import numpy as np
@@ -265,11 +300,16 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--rows", type=int, default=Q, help="rows of the matrix (smaller = profiling case)")
+    ap.add_argument("--profile-case", default=None, choices=["fused_tc", "l2_tc", "fused_fp32", "l2_fp32"],
+                    help="run a few launches of one small case of that kernel and exit (for ncu captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "native" else args.warmup
 
     if args.impl == "reference":
         run_reference_arm(args)
+        return
+    if args.profile_case is not None:
+        run_profile_case(args.profile_case)
         return
 
     import torch

@@ -27,10 +27,11 @@ struct tuning_entry
 
 std::mutex g_tuning_mutex;
 tuning_entry g_tuning[] = {
-    {"select.stage_bytes", 16384, 4096, 65536},
-    {"select.stages", 3, 2, 8},
+    {"select.stage_bytes", 0, 0, 65536},
+    {"select.stages", 0, 0, 8},
     {"select.merge_at", 100, 1, 100},
     {"select.auto_split", 1, 0, 1},
+    {"select.wide_block", 1, 0, 1},
     {"fused.query_tile", 8, 8, 16},
 };
 

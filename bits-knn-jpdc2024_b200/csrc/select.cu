@@ -617,16 +617,18 @@ size_t select_smem_bytes(int L, int stage_floats, int stages)
            sizeof(select_ctrl);
 }
 
-template <int IPT>
+template <int THREADS, int IPT>
 int launch_select(select_params p, int64_t vrows, cudaStream_t stream)
 {
-    constexpr int L = SELECT_THREADS * IPT;
+    constexpr int L = THREADS * IPT;
     const int merge_pct = tuning_value("select.merge_at", 100);
     p.merge_at = std::max(1, (L * merge_pct) / 100);
+    // a stage is a whole number of 4-vectors per thread
+    p.stage_floats = std::max(4 * THREADS, (p.stage_floats / (4 * THREADS)) * (4 * THREADS));
     const size_t smem = select_smem_bytes(L, p.stage_floats, p.stages);
-    auto kernel = select_kernel<SELECT_THREADS, IPT>;
+    auto kernel = select_kernel<THREADS, IPT>;
     BITSKNN_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-    kernel<<<static_cast<unsigned>(vrows), SELECT_THREADS, smem, stream>>>(p);
+    kernel<<<static_cast<unsigned>(vrows), THREADS, smem, stream>>>(p);
     BITSKNN_CUDA_TRY(cudaGetLastError());
     return BITSKNN_OK;
 }
@@ -635,19 +637,23 @@ int dispatch_select(const select_params& p, int64_t vrows, cudaStream_t stream)
 {
     // smallest list that holds k: the reference's dynamic_switch_le over K
     // (src/topk/singlepass/bits_knn.cu:44), with the list never shorter than the block
+    // Long lists take 512-thread blocks (the reference's tuned shapes do the same for k = 2048,
+    // scripts/optima.csv:1282): twice the threads fold a list of the same length with half the
+    // pairs, and registers, per thread.
+    const int wide = tuning_value("select.wide_block", 1);
     if (p.k <= 256)
     {
-        return launch_select<1>(p, vrows, stream);
+        return launch_select<256, 1>(p, vrows, stream);
     }
     if (p.k <= 512)
     {
-        return launch_select<2>(p, vrows, stream);
+        return wide != 0 ? launch_select<512, 1>(p, vrows, stream) : launch_select<256, 2>(p, vrows, stream);
     }
     if (p.k <= 1024)
     {
-        return launch_select<4>(p, vrows, stream);
+        return wide != 0 ? launch_select<512, 2>(p, vrows, stream) : launch_select<256, 4>(p, vrows, stream);
     }
-    return launch_select<8>(p, vrows, stream);
+    return wide != 0 ? launch_select<512, 4>(p, vrows, stream) : launch_select<256, 8>(p, vrows, stream);
 }
 
 template <int IPT>
@@ -718,11 +724,22 @@ int check_select_args(const float* d_dist, int64_t ld, int64_t q, int64_t n, int
 
 void fill_stream_config(select_params& p)
 {
-    int stage_bytes = tuning_value("select.stage_bytes", 16384);
-    stage_bytes = (stage_bytes / (16 * SELECT_THREADS)) * (16 * SELECT_THREADS);
-    stage_bytes = std::max(stage_bytes, 16 * SELECT_THREADS);
+    // 0 = automatic: the shapes measured best on B200 -- 3 x 16 KiB for 256-thread blocks
+    // (4 blocks per SM), 3 x 32 KiB for 512-thread blocks, 2 x 64 KiB for the longest lists
+    int stage_bytes = tuning_value("select.stage_bytes", 0);
+    int stages = tuning_value("select.stages", 0);
+    const bool wide = p.k > 256 && tuning_value("select.wide_block", 1) != 0;
+    if (stage_bytes <= 0)
+    {
+        stage_bytes = !wide ? 16384 : (p.k > 1024 ? 65536 : 32768);
+    }
+    if (stages <= 0)
+    {
+        stages = wide && p.k > 1024 ? 2 : 3;
+    }
+    stage_bytes = std::max((stage_bytes / 4096) * 4096, 4096);
     p.stage_floats = stage_bytes / 4;
-    p.stages = std::min(std::max(tuning_value("select.stages", 3), 2), MAX_STAGES);
+    p.stages = std::min(std::max(stages, 2), MAX_STAGES);
 }
 
 } // namespace

@@ -55,10 +55,12 @@ const char* bitsknn_last_error_string(void);
 int bitsknn_device_status(bitsknn_stream_t stream);
 
 /* Tuning knobs (launch shapes).  Unknown keys return BITSKNN_ERR_INVALID_ARGUMENT.
- *   "select.stage_bytes"  bytes per shared-memory stage of the row stream (multiple of 4096)
- *   "select.stages"       stages in the ring (2..8)
+ *   "select.stage_bytes"  bytes per shared-memory stage of the row stream (multiple of 4096;
+ *                         0 = automatic, the default)
+ *   "select.stages"       stages in the ring (2..8; 0 = automatic, the default)
  *   "select.merge_at"     merge the candidate buffer when it holds at least this percentage
  *                         of its capacity (1..100; 100 = only when full, like the reference)
+ *   "select.wide_block"   1 = 512-thread blocks for k > 256 (default), 0 = 256-thread blocks
  * The reference's `--block-size` / `--items-per-thread` flags tune the same things for its
  * kernels (src/topk/singlepass/bits_knn.cu:98-114); here they are hints. */
 int bitsknn_set_tuning(const char* key, int value);

@@ -50,6 +50,7 @@ def test_argument_validation_needs_no_device(bk):
 
 def test_tuning_registry(bk):
     old = bk.get_tuning("select.stages")
+    assert old == 0                                   # automatic by default
     bk.set_tuning("select.stages", 3)
     assert bk.get_tuning("select.stages") == 3
     bk.set_tuning("select.stages", old)
