@@ -31,6 +31,12 @@ int fused_tc_launch(const float* points, const float* queries, int64_t n, int64_
                     int32_t index_base, float* out_dist, int32_t* out_idx, void* workspace, size_t workspace_bytes,
                     cudaStream_t stream);
 
+// FP32 tiled variant (128 queries per block) lives in fused_tiled.cu
+size_t fused_tiled_workspace_bytes(int64_t n, int64_t q, int k);
+int fused_tiled_launch(const float* points, const float* queries, int64_t n, int64_t q, int dim, int k, int mode,
+                       int32_t index_base, float* out_dist, int32_t* out_idx, void* workspace, size_t workspace_bytes,
+                       cudaStream_t stream);
+
 namespace
 {
 
@@ -39,6 +45,7 @@ constexpr int QT = 8;                  // queries per block = warps per block
 constexpr int PPT = 4;                 // points per thread
 constexpr int PT = FUSED_THREADS * PPT; // points per tile
 constexpr int DT = 4;                  // coordinates per staged tile
+constexpr int FUSED_TILED_MIN_DIM = 24; // automatic choice: tiled kernel from this dimension on (measured crossover ~16-32)
 
 struct fused_params
 {
@@ -356,6 +363,11 @@ extern "C" size_t bitsknn_fused_workspace_bytes(int64_t n, int64_t q, int dim, i
     {
         return fused_tc_workspace_bytes(n, q, dim, k, mode);
     }
+    if (mode == BITSKNN_L2_PARTIAL || mode == BITSKNN_L2_EXACT)
+    {
+        // optional for the FP32 modes: with it the tiled kernel (128 queries per block) can be used
+        return fused_tiled_workspace_bytes(n, q, k);
+    }
     return 0;
 }
 
@@ -397,6 +409,16 @@ extern "C" int bitsknn_fused(const float* d_points, const float* d_queries, int6
     {
         return fused_tc_launch(d_points, d_queries, n, q, dim, k, mode, index_base, d_out_dist, d_out_idx, d_workspace,
                                workspace_bytes, static_cast<cudaStream_t>(stream));
+    }
+    // FP32: the tiled kernel needs its list workspace; without one (or when asked through the
+    // "fused.variant" knob: 0 = 8-query blocks, 1 = tiled, 2 = automatic) the 8-query kernel runs
+    const int variant = tuning_value("fused.variant", 2);
+    const bool have_ws = d_workspace != nullptr && workspace_bytes >= fused_tiled_workspace_bytes(n, q, k) &&
+                         (reinterpret_cast<uintptr_t>(d_workspace) & 255U) == 0;
+    if (have_ws && (variant == 1 || (variant == 2 && dim >= FUSED_TILED_MIN_DIM)))
+    {
+        return fused_tiled_launch(d_points, d_queries, n, q, dim, k, mode, index_base, d_out_dist, d_out_idx,
+                                  d_workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
     }
     fused_params p{};
     p.points = d_points;

@@ -31,6 +31,7 @@
 #include "sortnet.cuh"
 #include "tc.cuh"
 #include "tc_host.cuh"
+#include "warpfold.cuh"
 
 namespace bitsknn
 {
@@ -58,59 +59,6 @@ struct ftc_params
     int32_t index_base;
     int* status;
 };
-
-// Sorts a bitonic array of 32 * IPT pairs ascending; entry e lives in lane e % 32, register
-// e / 32.  Strides of 32 and more are exchanges between registers of one lane (M = stride / 32,
-// a compile-time constant so that the arrays stay in registers), smaller ones are shuffles.
-template <int IPT, int M>
-struct striped_reg_steps
-{
-    static __device__ __forceinline__ void run(float (&d)[IPT], int (&x)[IPT])
-    {
-        if constexpr (M >= 1)
-        {
-#pragma unroll
-            for (int r = 0; r < IPT; ++r)
-            {
-                if ((r & M) == 0)
-                {
-                    if (pair_lt(d[r | M], x[r | M], d[r], x[r]))
-                    {
-                        const float td = d[r];
-                        d[r] = d[r | M];
-                        d[r | M] = td;
-                        const int tx = x[r];
-                        x[r] = x[r | M];
-                        x[r | M] = tx;
-                    }
-                }
-            }
-            striped_reg_steps<IPT, M / 2>::run(d, x);
-        }
-    }
-};
-
-template <int IPT>
-__device__ __forceinline__ void merge_striped(float (&d)[IPT], int (&x)[IPT], int lane)
-{
-    striped_reg_steps<IPT, IPT / 2>::run(d, x);
-#pragma unroll
-    for (int J = 16; J >= 1; J >>= 1)
-    {
-        const bool keep_min = (lane & J) == 0;
-#pragma unroll
-        for (int r = 0; r < IPT; ++r)
-        {
-            const float pd = __shfl_xor_sync(FULL_MASK, d[r], J);
-            const int px = __shfl_xor_sync(FULL_MASK, x[r], J);
-            if (pair_lt(pd, px, d[r], x[r]) == keep_min)
-            {
-                d[r] = pd;
-                x[r] = px;
-            }
-        }
-    }
-}
 
 template <bool BF16, int IPT>
 __global__ void __launch_bounds__(FT_THREADS, 1)
@@ -283,46 +231,12 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
                 const int64_t gq_l = qb * TILE_M + w4 * 32 + L;
                 float* gl_d = p.list_d + (list_id * p.q + gq_l) * KL;
                 int32_t* gl_x = p.list_x + (list_id * p.q + gq_l) * KL;
-                // candidates: slot `lane` of query L's buffer, sorted descending over the lanes
-                float cd[1] = {lane < cnt_l ? my_buf_d[lane * 32 + L] : INFINITY};
-                int cx[1] = {lane < cnt_l ? my_buf_x[lane * 32 + L] : PAD_IDX};
-                block_sort<32, 1>(cd, cx, true, nullptr, nullptr, lane);
-                float ld[IPT];
-                int lx[IPT];
-#pragma unroll
-                for (int r = 0; r < IPT; ++r)
-                {
-                    ld[r] = has_l ? gl_d[r * 32 + lane] : INFINITY;
-                    lx[r] = has_l ? gl_x[r * 32 + lane] : PAD_IDX;
-                }
-                // element-wise minimum against the last 32 entries (ascending in the lanes), which
-                // leaves the KL smallest pairs as a bitonic array, then the merge network
-                if (pair_lt(cd[0], cx[0], ld[IPT - 1], lx[IPT - 1]))
-                {
-                    ld[IPT - 1] = cd[0];
-                    lx[IPT - 1] = cx[0];
-                }
-                merge_striped<IPT>(ld, lx, lane);
-#pragma unroll
-                for (int r = 0; r < IPT; ++r)
-                {
-                    gl_d[r * 32 + lane] = ld[r];
-                    gl_x[r * 32 + lane] = lx[r];
-                }
-                // new radius = entry k - 1
-                float nd = ld[0];
-                int nx = lx[0];
-#pragma unroll
-                for (int r = 1; r < IPT; ++r)
-                {
-                    // (opaque selects: a plain ?: chain is turned into an indexed load from a
-                    // stack copy of the list, which costs a local store per list update)
-                    const int pick = r == (p.k - 1) / 32 ? 1 : 0;
-                    asm("{\n.reg .pred p;\nsetp.ne.s32 p, %2, 0;\nselp.f32 %0, %1, %0, p;\n}" : "+f"(nd) : "f"(ld[r]), "r"(pick));
-                    asm("{\n.reg .pred p;\nsetp.ne.s32 p, %2, 0;\nselp.s32 %0, %1, %0, p;\n}" : "+r"(nx) : "r"(lx[r]), "r"(pick));
-                }
-                nd = __shfl_sync(FULL_MASK, nd, (p.k - 1) & 31);
-                nx = __shfl_sync(FULL_MASK, nx, (p.k - 1) & 31);
+                // candidates: slot `lane` of query L's buffer
+                const float cd = lane < cnt_l ? my_buf_d[lane * 32 + L] : INFINITY;
+                const int cx = lane < cnt_l ? my_buf_x[lane * 32 + L] : PAD_IDX;
+                float nd;
+                int nx;
+                warp_fold_global<IPT>(cd, cx, has_l, gl_d, gl_x, p.k, lane, nd, nx);
                 if (lane == L)
                 {
                     r_d = nd;

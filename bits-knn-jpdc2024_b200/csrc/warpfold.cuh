@@ -1,0 +1,113 @@
+// Warp-level fold of up to 32 candidate pairs into a sorted list of 32 * IPT pairs that lives
+// in global memory (L2-resident workspace), shared by the fused kernels.
+#pragma once
+
+#include "common.cuh"
+#include "sortnet.cuh"
+
+namespace bitsknn
+{
+
+// Sorts a bitonic array of 32 * IPT pairs ascending; entry e lives in lane e % 32, register
+// e / 32.  Strides of 32 and more are exchanges between registers of one lane (M = stride / 32,
+// a compile-time constant so that the arrays stay in registers), smaller ones are shuffles.
+template <int IPT, int M>
+struct striped_reg_steps
+{
+    static __device__ __forceinline__ void run(float (&d)[IPT], int (&x)[IPT])
+    {
+        if constexpr (M >= 1)
+        {
+#pragma unroll
+            for (int r = 0; r < IPT; ++r)
+            {
+                if ((r & M) == 0)
+                {
+                    if (pair_lt(d[r | M], x[r | M], d[r], x[r]))
+                    {
+                        const float td = d[r];
+                        d[r] = d[r | M];
+                        d[r | M] = td;
+                        const int tx = x[r];
+                        x[r] = x[r | M];
+                        x[r | M] = tx;
+                    }
+                }
+            }
+            striped_reg_steps<IPT, M / 2>::run(d, x);
+        }
+    }
+};
+
+template <int IPT>
+__device__ __forceinline__ void merge_striped(float (&d)[IPT], int (&x)[IPT], int lane)
+{
+    striped_reg_steps<IPT, IPT / 2>::run(d, x);
+#pragma unroll
+    for (int J = 16; J >= 1; J >>= 1)
+    {
+        const bool keep_min = (lane & J) == 0;
+#pragma unroll
+        for (int r = 0; r < IPT; ++r)
+        {
+            const float pd = __shfl_xor_sync(FULL_MASK, d[r], J);
+            const int px = __shfl_xor_sync(FULL_MASK, x[r], J);
+            if (pair_lt(pd, px, d[r], x[r]) == keep_min)
+            {
+                d[r] = pd;
+                x[r] = px;
+            }
+        }
+    }
+}
+
+// Folds the candidates (one pair per lane, padding = (+inf, PAD_IDX)) into the list at
+// gl_d / gl_x (striped: entry e in lane e % 32, register e / 32; `has_list` false = the list is
+// still empty and is not read).  The candidates are sorted descending with shuffles, the
+// element-wise minimum against the list's last 32 entries leaves the 32 * IPT smallest pairs as
+// a bitonic array (the candidates count as padded with +inf in front), the striped merge sorts
+// it, and the list is written back.  Every lane returns the new radius pair (entry k - 1).
+template <int IPT>
+__device__ __forceinline__ void warp_fold_global(float cand_d, int cand_x, bool has_list, float* gl_d, int32_t* gl_x,
+                                                 int k, int lane, float& radius_d, int& radius_x)
+{
+    float cd[1] = {cand_d};
+    int cx[1] = {cand_x};
+    block_sort<32, 1>(cd, cx, true, nullptr, nullptr, lane);
+    float ld[IPT];
+    int lx[IPT];
+#pragma unroll
+    for (int r = 0; r < IPT; ++r)
+    {
+        ld[r] = has_list ? gl_d[r * 32 + lane] : INFINITY;
+        lx[r] = has_list ? gl_x[r * 32 + lane] : PAD_IDX;
+    }
+    if (pair_lt(cd[0], cx[0], ld[IPT - 1], lx[IPT - 1]))
+    {
+        ld[IPT - 1] = cd[0];
+        lx[IPT - 1] = cx[0];
+    }
+    merge_striped<IPT>(ld, lx, lane);
+#pragma unroll
+    for (int r = 0; r < IPT; ++r)
+    {
+        gl_d[r * 32 + lane] = ld[r];
+        gl_x[r * 32 + lane] = lx[r];
+    }
+    float nd = ld[0];
+    int nx = lx[0];
+#pragma unroll
+    for (int r = 1; r < IPT; ++r)
+    {
+        // (opaque selects: a plain ?: chain is turned into an indexed load from a stack copy of
+        // the list, which costs a local store per list update)
+        const int pick = r == (k - 1) / 32 ? 1 : 0;
+        asm("{\n.reg .pred p;\nsetp.ne.s32 p, %2, 0;\nselp.f32 %0, %1, %0, p;\n}" : "+f"(nd) : "f"(ld[r]), "r"(pick));
+        asm("{\n.reg .pred p;\nsetp.ne.s32 p, %2, 0;\nselp.s32 %0, %1, %0, p;\n}" : "+r"(nx) : "r"(lx[r]), "r"(pick));
+    }
+    radius_d = __shfl_sync(FULL_MASK, nd, (k - 1) & 31);
+    radius_x = __shfl_sync(FULL_MASK, nx, (k - 1) & 31);
+    __syncwarp(); // the list stores are ordered before any later load by this warp
+}
+
+} // namespace bitsknn

@@ -61,6 +61,8 @@ int bitsknn_device_status(bitsknn_stream_t stream);
  *   "select.merge_at"     merge the candidate buffer when it holds at least this percentage
  *                         of its capacity (1..100; 100 = only when full, like the reference)
  *   "select.wide_block"   1 = 512-thread blocks for k > 256 (default), 0 = 256-thread blocks
+ *   "fused.variant"       FP32 fused kernel: 0 = 8 queries per block, 1 = tiled (needs the
+ *                         workspace), 2 = automatic (default)
  * The reference's `--block-size` / `--items-per-thread` flags tune the same things for its
  * kernels (src/topk/singlepass/bits_knn.cu:98-114); here they are hints. */
 int bitsknn_set_tuning(const char* key, int value);
@@ -162,8 +164,10 @@ int bitsknn_l2(const float* d_points, const float* d_queries, int64_t n, int64_t
  *               distance error, not bit-exact)
  *   k           1 <= k <= BITSKNN_FUSED_MAX_K
  *   index_base  added to every reported index (shard base of a sharded database)
- *   d_workspace tensor-core modes only: bitsknn_fused_workspace_bytes() bytes, 256-byte aligned
- *               (input images, norms and the per-block partial lists); FP32 modes pass NULL, 0
+ *   d_workspace bitsknn_fused_workspace_bytes() bytes, 256-byte aligned.  Required by the
+ *               tensor-core modes (input images, norms, partial lists).  Optional for the FP32
+ *               modes: with it the tiled kernel (128 queries per block, lists in the workspace)
+ *               runs, with NULL / 0 the 8-queries-per-block kernel; both give the same bits
  * --------------------------------------------------------------------------------------- */
 size_t bitsknn_fused_workspace_bytes(int64_t n, int64_t q, int dim, int k, int mode);
 int bitsknn_fused(const float* d_points, const float* d_queries, int64_t n, int64_t q, int dim, int k,

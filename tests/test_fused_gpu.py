@@ -9,6 +9,15 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(params=[0, 1], ids=["rows8", "tiled"], autouse=True)
+def fused_variant(request, bk):
+    """Every test runs with both FP32 kernels: 8 queries per block, and 128 x 128 tiles."""
+    old = bk.get_tuning("fused.variant")
+    bk.set_tuning("fused.variant", request.param)
+    yield request.param
+    bk.set_tuning("fused.variant", old)
+
+
 def run_fused(bk, oracle, points, queries, k, partial=True, index_base=0):
     got_d, got_i = bk.fused(torch.from_numpy(points).cuda(), torch.from_numpy(queries).cuda(), k,
                             mode=bk.L2_PARTIAL if partial else bk.L2_EXACT, index_base=index_base)

@@ -70,7 +70,16 @@ def test_many_parts_and_clustered_data(bk, cuda):
 
 def test_workspace_and_dim_limits(bk, cuda):
     x = torch.rand((256, 16), device="cuda")
-    assert bk.fused_workspace_bytes(256, 256, 16, 32, bk.L2_PARTIAL) == 0
+    # FP32: optional workspace (lists of the tiled kernel); without one the 8-query kernel runs
+    d0, i0 = bk.fused(x, x, 32, mode=bk.L2_PARTIAL)
+    lib = bk.lib()
+    import ctypes
+    d1 = torch.empty_like(d0)
+    i1 = torch.empty_like(i0)
+    rc = lib.bitsknn_fused(ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(x.data_ptr()), 256, 256, 16, 32, bk.L2_PARTIAL, 0,
+                           ctypes.c_void_p(d1.data_ptr()), ctypes.c_void_p(i1.data_ptr()), None, 0, None)
+    torch.cuda.synchronize()
+    assert rc == 0 and bool((d0 == d1).all()) and bool((i0 == i1).all())
     need = bk.fused_workspace_bytes(256, 256, 16, 32, bk.L2_TF32)
     assert need > 0
     with pytest.raises(bk.BitsKnnError) as err:
