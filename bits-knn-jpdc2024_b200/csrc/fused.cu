@@ -45,7 +45,7 @@ constexpr int QT = 8;                  // queries per block = warps per block
 constexpr int PPT = 4;                 // points per thread
 constexpr int PT = FUSED_THREADS * PPT; // points per tile
 constexpr int DT = 4;                  // coordinates per staged tile
-constexpr int FUSED_TILED_MIN_DIM = 24; // automatic choice: tiled kernel from this dimension on (measured crossover ~16-32)
+constexpr int FUSED_TILED_MIN_DIM = 16; // automatic choice: tiled kernel from this dimension on (measured crossover)
 
 struct fused_params
 {

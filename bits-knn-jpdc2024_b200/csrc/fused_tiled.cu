@@ -119,8 +119,10 @@ __global__ void __launch_bounds__(FT_THREADS, 2) fused_tiled_kernel(const tiled_
     auto fold_round = [&]() {
         for (int qi = warp; qi < FT_BM; qi += FT_THREADS / 32)
         {
+            // a fold costs a round trip to the list whatever the buffer holds, so nearly empty
+            // buffers wait for a later round (the final flush takes whatever is left)
             const int have = cnt[qi];
-            const bool flush = have > 0;
+            const bool flush = have >= FT_CAP / 4;
             if (flush && m0 + qi < p.q)
             {
                 const int valid = have < FT_CAP ? have : FT_CAP;
@@ -228,31 +230,45 @@ __global__ void __launch_bounds__(FT_THREADS, 2) fused_tiled_kernel(const tiled_
 
         // ---- filter the 8 x 8 distances of this thread -------------------------------------
         unsigned long long pending = 0;
+        const int ncols = p.n - n0 < FT_BN ? static_cast<int>(p.n - n0) : FT_BN; // valid columns of this tile
+        const int c_lo = tx * 4;       // this thread's columns: c_lo .. c_lo + 3 and 64 + c_lo .. + 3
 #pragma unroll
         for (int i = 0; i < 8; ++i)
         {
             const int row = i < 4 ? ty * 4 + i : 64 + ty * 4 + (i - 4);
             const float rd = sr_d[row];
+            // finish the 8 distances of this row and look at their minimum first: once the radius
+            // has settled almost every row is rejected by this one comparison
+            float mn = INFINITY;
 #pragma unroll
             for (int j = 0; j < 8; ++j)
             {
                 const float d = PARTIAL ? (nrm[j] - 2.0F * acc[i][j]) : acc[i][j];
                 acc[i][j] = d;
-                const int64_t col = n0 + (j < 4 ? tx * 4 + j : 64 + tx * 4 + (j - 4));
-                if (d <= rd && col < p.n)
+                mn = fminf(mn, d);
+            }
+            if (mn <= rd)
+            {
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
                 {
-                    const int idx = p.index_base + static_cast<int>(col);
-                    if (pair_lt(d, idx, rd, sr_x[row]))
+                    const float d = acc[i][j];
+                    const int c = j < 4 ? c_lo + j : 64 + c_lo + (j - 4);
+                    if (d <= rd && c < ncols)
                     {
-                        const int pos = atomicAdd(&cnt[row], 1);
-                        if (pos < FT_CAP)
+                        const int idx = p.index_base + static_cast<int>(n0) + c;
+                        if (pair_lt(d, idx, rd, sr_x[row]))
                         {
-                            buf_d[row][pos] = d;
-                            buf_x[row][pos] = idx;
-                        }
-                        else
-                        {
-                            pending |= 1ULL << (i * 8 + j);
+                            const int pos = atomicAdd(&cnt[row], 1);
+                            if (pos < FT_CAP)
+                            {
+                                buf_d[row][pos] = d;
+                                buf_x[row][pos] = idx;
+                            }
+                            else
+                            {
+                                pending |= 1ULL << (i * 8 + j);
+                            }
                         }
                     }
                 }
