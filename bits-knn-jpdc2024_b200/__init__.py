@@ -37,6 +37,7 @@ SIGNATURES = {
     "bitsknn_set_tuning": (_int, [ctypes.c_char_p, _int]),
     "bitsknn_get_tuning": (_int, [ctypes.c_char_p, ctypes.POINTER(_int)]),
     "bitsknn_select": (_int, [_ptr, _i64, _ptr, _i64, _ptr, _i64, _i64, _int, _ptr, _ptr, _ptr]),
+    "bitsknn_select_auto_splits": (_int, [_i64, _i64, _int]),
     "bitsknn_select_split_workspace_bytes": (_sz, [_i64, _int, _int]),
     "bitsknn_select_split": (_int, [_ptr, _i64, _ptr, _i64, _i64, _int, _int, _ptr, _sz, _ptr, _ptr, _ptr]),
     "bitsknn_select_split_static": (_int, [_ptr, _i64, _ptr, _i64, _i64, _int, _int, _ptr, _ptr, _ptr]),
@@ -135,6 +136,10 @@ def select(dist, k, labels=None, label_offsets=None, n=None, out=None):
     _check(lib().bitsknn_select(_p(dist), ld, _p(labels), ldl, _p(label_offsets), q, n, k,
                                 _p(out[0]), _p(out[1]), _stream()))
     return out
+
+
+def select_auto_splits(q, n, k):
+    return int(lib().bitsknn_select_auto_splits(q, n, k))
 
 
 def select_split_workspace_bytes(q, k, splits):

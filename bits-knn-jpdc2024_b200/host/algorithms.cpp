@@ -214,11 +214,35 @@ std::vector<distance_pair> cuda_knn::finish()
     return result;
 }
 
+void bits_knn::initialize(const knn_args& args)
+{
+    cuda_knn::initialize(args);
+    // few, long rows: the library cuts them into slices (what the reference's `bits-sq --deg` does
+    // by hand) so that every SM has a block to run
+    splits_ = bitsknn_select_auto_splits(static_cast<std::int64_t>(query_count()),
+                                         static_cast<std::int64_t>(point_count()), static_cast<int>(k()));
+    workspace_.release();
+    if (splits_ > 1)
+    {
+        workspace_ = device_buffer<unsigned char>{bitsknn_select_split_workspace_bytes(
+            static_cast<std::int64_t>(query_count()), static_cast<int>(k()), splits_)};
+    }
+}
+
 void bits_knn::selection()
 {
     const auto n = static_cast<std::int64_t>(point_count());
-    abi_check(bitsknn_select(in_dist_gpu(), n, nullptr, 0, nullptr, static_cast<std::int64_t>(query_count()), n,
-                             static_cast<int>(k()), out_dist_gpu(), out_label_gpu(), nullptr));
+    if (splits_ > 1)
+    {
+        abi_check(bitsknn_select_split(in_dist_gpu(), n, nullptr, static_cast<std::int64_t>(query_count()), n,
+                                       static_cast<int>(k()), splits_, workspace_.data(), workspace_.size(),
+                                       out_dist_gpu(), out_label_gpu(), nullptr));
+    }
+    else
+    {
+        abi_check(bitsknn_select(in_dist_gpu(), n, nullptr, 0, nullptr, static_cast<std::int64_t>(query_count()), n,
+                                 static_cast<int>(k()), out_dist_gpu(), out_label_gpu(), nullptr));
+    }
     BITS_CUCH(cudaStreamSynchronize(nullptr));
 }
 

@@ -245,10 +245,13 @@ class bits_knn : public cuda_knn
 public:
     explicit bits_knn(std::string id = "bits") : id_(std::move(id)) {}
     std::string id() const override { return id_; }
+    void initialize(const knn_args& args) override;
     void selection() override;
 
 private:
     std::string id_;
+    int splits_ = 1;                         // slices per row chosen by the library for this shape
+    device_buffer<unsigned char> workspace_; // candidates of the slices (only when splits_ > 1)
 };
 
 // `bits-sq`: rows cut into `deg` slices, then merged (reference: single_query_bits).

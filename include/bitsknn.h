@@ -92,6 +92,10 @@ int bitsknn_select(const float* d_dist, int64_t ld, const int32_t* d_labels, int
  * second kernel.  Replaces single_query_bits (src/topk/singlepass/bits_knn.cu:116-186, the
  * `bits-sq --deg` algorithm).  splits == 0 lets the library choose from q and the SM count.
  * Workspace size: bitsknn_select_split_workspace_bytes(q, k, splits). */
+/* The number of slices per row the library would choose (what `splits == 0` resolves to on the
+ * current device; 1 = whole rows are best).  The reference leaves this choice to its `--deg`
+ * flag and tuning tables (scripts/run-bits-sq.sh:25-29). */
+int bitsknn_select_auto_splits(int64_t q, int64_t n, int k);
 size_t bitsknn_select_split_workspace_bytes(int64_t q, int k, int splits);
 int bitsknn_select_split(const float* d_dist, int64_t ld, const int32_t* d_label_offsets, int64_t q,
                          int64_t n, int k, int splits, void* d_workspace, size_t workspace_bytes,

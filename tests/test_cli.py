@@ -71,6 +71,7 @@ def test_published_checksum_end_to_end(knn, cuda):
     ["-a", "bits-prefetch", "-n", "64k", "-q", "128", "-k", "100", "-d", "10", "--seed", "7"],
     ["-a", "bits-sq", "--deg", "8", "-n", "256k", "-q", "4", "-k", "64", "--seed", "7"],
     ["-a", "bits", "-n", "100000", "-q", "8", "-k", "256", "--seed", "24", "-p", "descending"],
+    ["-a", "bits", "-n", "2M", "-q", "4", "-k", "64", "--seed", "7"],          # few long rows: sliced automatically
     ["-a", "bits", "-n", "3000", "-q", "16", "-k", "8", "-d", "6", "--seed", "3", "--point-layout", "column",
      "--query-layout", "column"],
     ["-a", "parallel", "-n", "3000", "-q", "16", "-k", "8", "-d", "6", "--seed", "3"],
