@@ -9,9 +9,10 @@
 //
 // Block = 320 threads on one SM, 128 queries (the TMEM lanes):
 //   warp 8   TMA producer (query image once, point image tiles through a ring of 16 KiB stages)
-//   warp 9   TMEM allocation (2 x 128 columns) and tcgen05.mma issue
-//   warps 0-7  consumers, two groups of four.  Group g takes every other point tile (accumulator
-//            buffer g); thread t of a group is query 32 * (warp % 4) + t and reads its row with
+//   warp 9   TMEM allocation (4 x 128 columns) and tcgen05.mma issue
+//   warps 0-7  consumers, two groups of four.  Group g takes every other point tile (each group
+//            alternates between two accumulator buffers, so the MMAs run two tiles ahead of it);
+//            thread t of a group is query 32 * (warp % 4) + t and reads its row with
 //            tcgen05.ld.  Each (group, query) has a private 32-slot candidate buffer in shared
 //            memory (no atomics: one writer) and a sorted list of KL = 32 * IPT pairs in the
 //            workspace (HBM/L2), touched only when the buffer is folded: the warp sorts the 32
@@ -42,7 +43,8 @@ namespace
 constexpr int FT_THREADS = 320;
 constexpr int FT_PRODUCER_WARP = 8;
 constexpr int FT_MMA_WARP = 9;
-constexpr int FT_TMEM_COLS = 256;
+constexpr int FT_TMEM_COLS = 512; // four 128-column accumulators: each consumer group owns two
+constexpr int FT_ACCS = 4;
 constexpr int CAP = 32; // candidate slots per (group, query)
 
 struct ftc_params
@@ -77,8 +79,8 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
     uint64_t* full_b = bars + 1;
     uint64_t* empty_b = full_b + 16;
     uint64_t* acc_full = empty_b + 16;
-    uint64_t* acc_empty = acc_full + 2;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    uint64_t* acc_empty = acc_full + FT_ACCS;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + FT_ACCS);
     float* rad = reinterpret_cast<float*>(bars + 64);     // [2][128] radius distance per group and query
     float* buf_d = rad + 2 * TILE_M;                      // [8 warps][CAP][32 lanes]
     int* buf_x = reinterpret_cast<int*>(buf_d + 8 * CAP * 32);
@@ -101,7 +103,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
             ptx::mbar_init(&full_b[s], 1);
             ptx::mbar_init(&empty_b[s], 1);
         }
-        for (int a = 0; a < 2; ++a)
+        for (int a = 0; a < FT_ACCS; ++a)
         {
             ptx::mbar_init(&acc_full[a], 1);
             ptx::mbar_init(&acc_empty[a], 128);
@@ -166,8 +168,9 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
             int64_t lt = 0;
             for (int64_t t = t_begin; t < t_end && ok; ++t, ++lt)
             {
-                const int a = static_cast<int>(lt & 1);
-                const uint32_t aph = static_cast<uint32_t>((lt >> 1) & 1);
+                // tile lt goes to accumulator lt % 4 (consumer group lt % 2), used for the (lt / 4)-th time
+                const int a = static_cast<int>(lt & (FT_ACCS - 1));
+                const uint32_t aph = static_cast<uint32_t>((lt >> 2) & 1);
                 if (!ptx::mbar_wait_bounded(&acc_empty[a], aph ^ 1U))
                 {
                     ok = false;
@@ -211,7 +214,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
         float* my_buf_d = buf_d + warp * (CAP * 32);  // slot s of lane l at [s * 32 + l]
         int* my_buf_x = buf_x + warp * (CAP * 32);
         const int64_t list_id = static_cast<int64_t>(part) * 2 + group;
-        const uint32_t lane_base = (static_cast<uint32_t>(w4 * 32) << 16) + static_cast<uint32_t>(group * TILE_N);
+        const uint32_t lane_base = static_cast<uint32_t>(w4 * 32) << 16;
 
         // radius pair of this (group, query); a dead row (query beyond q) never accepts anything
         float r_d = live ? INFINITY : -INFINITY;
@@ -249,8 +252,57 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
             }
         };
 
-        int64_t use = 0;
-        for (int64_t t = t_begin + group; t < t_end && ok; t += 2, ++use)
+        // One half chunk (16 columns) of this thread's row: max-tree, warp vote, pushes, folds.
+        // A buffer holds at most 16 pairs when a half starts, so its at most 16 pushes always fit.
+        auto scan_half = [&](const uint32_t(&v)[16], int64_t col0) {
+            float mx = __uint_as_float(v[0]);
+#pragma unroll
+            for (int j = 1; j < 16; ++j)
+            {
+                mx = fmaxf(mx, __uint_as_float(v[j]));
+            }
+            if (!__any_sync(FULL_MASK, mx >= thr))
+            {
+                return;
+            }
+            const int ncols = p.n - col0 < 16 ? static_cast<int>(p.n - col0) : 16; // valid columns
+            const float r_part = -2.0F * thr; // the tighter of the two groups' radii
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+            {
+                const float s = __uint_as_float(v[j]);
+                const bool cand = s >= thr && j < ncols;
+                if (__any_sync(FULL_MASK, cand))
+                {
+                    if (cand)
+                    {
+                        const float d = -2.0F * s;
+                        const int idx = p.index_base + static_cast<int>(col0 + j);
+                        if (d <= r_part && pair_lt(d, idx, r_d, r_x))
+                        {
+                            my_buf_d[cnt * 32 + lane] = d;
+                            my_buf_x[cnt * 32 + lane] = idx;
+                            ++cnt;
+                        }
+                    }
+                }
+            }
+            const unsigned need = __ballot_sync(FULL_MASK, cnt > CAP / 2);
+            if (need != 0)
+            {
+                __syncwarp();
+                fold_queries(need);
+                if (live)
+                {
+                    thr = fmaxf(thr, -0.5F * r_d);
+                }
+            }
+        };
+
+        // this group's tiles are the local tiles lt = group, group + 2, ...; tile lt sits in
+        // accumulator lt % 4, so the group alternates between its two accumulators
+        int64_t lt = group;
+        for (int64_t t = t_begin + group; t < t_end && ok; t += 2, lt += 2)
         {
             if (live)
             {
@@ -258,74 +310,38 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
                 const float r_eff = fminf(r_d, rad[(group ^ 1) * TILE_M + qrow]);
                 thr = -0.5F * r_eff;
             }
-            // (the verdict is made warp-uniform: the lanes poll independently)
-            if (!__all_sync(FULL_MASK, ptx::mbar_wait_bounded(&acc_full[group], static_cast<uint32_t>(use & 1))))
+            const int a = static_cast<int>(lt & (FT_ACCS - 1));
+            // (made warp-uniform: the lanes poll independently)
+            if (!__all_sync(FULL_MASK, ptx::mbar_wait_bounded(&acc_full[a], static_cast<uint32_t>((lt >> 2) & 1))))
             {
                 ok = false;
                 break;
             }
             tc::fence_after_sync();
+            const uint32_t acc_addr = tmem_base + lane_base + static_cast<uint32_t>(a * TILE_N);
+            // 16 columns at a time, the next 16 in flight from tensor memory while these are scanned
+            uint32_t lo[16];
+            uint32_t hi[16];
+            tc::tmem_ld_32x16(acc_addr, lo);
 #pragma unroll 1
             for (int c = 0; c < TILE_N / 32; ++c)
             {
-                uint32_t v[32];
-                tc::tmem_ld_32x32(tmem_base + lane_base + static_cast<uint32_t>(c * 32), v);
+                const int64_t col0 = t * TILE_N + c * 32;
                 tc::tmem_ld_wait();
-                if (c == TILE_N / 32 - 1)
+                tc::tmem_ld_32x16(acc_addr + static_cast<uint32_t>(c * 32 + 16), hi);
+                scan_half(lo, col0);
+                tc::tmem_ld_wait();
+                if (c + 1 < TILE_N / 32)
+                {
+                    tc::tmem_ld_32x16(acc_addr + static_cast<uint32_t>(c * 32 + 32), lo);
+                }
+                else
                 {
                     // every accumulator of this thread is in registers: the buffer may be reused
                     tc::fence_before_sync();
-                    tc::mbar_arrive(&acc_empty[group]);
+                    tc::mbar_arrive(&acc_empty[a]);
                 }
-                const int64_t col0 = t * TILE_N + c * 32;
-                const int ncols = p.n - col0 < 32 ? static_cast<int>(p.n - col0) : 32; // valid columns
-                // two halves of 16 columns; a buffer holds at most 16 pairs when a half starts,
-                // so the at most 16 pushes of a half always fit its 32 slots
-#pragma unroll
-                for (int half = 0; half < 2; ++half)
-                {
-                    float mx = __uint_as_float(v[half * 16]);
-#pragma unroll
-                    for (int j = 1; j < 16; ++j)
-                    {
-                        mx = fmaxf(mx, __uint_as_float(v[half * 16 + j]));
-                    }
-                    if (!__any_sync(FULL_MASK, mx >= thr))
-                    {
-                        continue;
-                    }
-                    const float r_part = -2.0F * thr; // the tighter of the two groups' radii
-#pragma unroll
-                    for (int j = half * 16; j < half * 16 + 16; ++j)
-                    {
-                        const float s = __uint_as_float(v[j]);
-                        const bool cand = s >= thr && j < ncols;
-                        if (__any_sync(FULL_MASK, cand))
-                        {
-                            if (cand)
-                            {
-                                const float d = -2.0F * s;
-                                const int idx = p.index_base + static_cast<int>(col0 + j);
-                                if (d <= r_part && pair_lt(d, idx, r_d, r_x))
-                                {
-                                    my_buf_d[cnt * 32 + lane] = d;
-                                    my_buf_x[cnt * 32 + lane] = idx;
-                                    ++cnt;
-                                }
-                            }
-                        }
-                    }
-                    const unsigned need = __ballot_sync(FULL_MASK, cnt > CAP / 2);
-                    if (need != 0)
-                    {
-                        __syncwarp();
-                        fold_queries(need);
-                        if (live)
-                        {
-                            thr = fmaxf(thr, -0.5F * r_d);
-                        }
-                    }
-                }
+                scan_half(hi, col0 + 16);
             }
         }
         // flush: every live (group, query) leaves a complete list behind, padding included

@@ -14,14 +14,14 @@
 //   main       320 threads per block, one block per SM:
 //              warp 8  TMA producer: query tile once, then point tiles through a ring of
 //                      16 KiB stages (128 rows x 128 bytes, 128-byte swizzle)
-//              warp 9  allocates 256 TMEM columns, issues tcgen05.mma (M = 128 queries,
+//              warp 9  allocates 512 TMEM columns (four accumulators), issues tcgen05.mma (M = 128 queries,
 //                      N = 128 points, K = 8 TF32 / 16 BF16 per instruction), commits stage and
 //                      accumulator barriers
 //              warps 0-7  epilogue, two groups of four: group g drains accumulator buffer g
 //                      (every other tile) with tcgen05.ld 32 lanes x 32 columns, transposes
 //                      through a shared-memory staging tile so that every 128-byte row segment
-//                      is written by 8 lanes, adds the norms, streaming 128-bit stores; the two
-//                      buffers let the epilogue of tile t overlap the MMAs of tile t + 1
+//                      is written by 8 lanes, adds the norms, streaming 128-bit stores; each group
+//                      alternates between two accumulators, so the MMAs run two tiles ahead of it
 // Every mbarrier wait is bounded; on expiry the role stops, the block reaches its final barrier,
 // frees its TMEM and sets the device status word.
 #include <algorithm>
@@ -45,7 +45,8 @@ namespace
 constexpr int TC_THREADS = 320;     // 8 epilogue warps + TMA producer warp + MMA warp
 constexpr int PRODUCER_WARP = 8;
 constexpr int MMA_WARP = 9;
-constexpr int TMEM_COLS = 256;
+constexpr int TMEM_COLS = 512;      // four 128-column accumulators: each epilogue group owns two
+constexpr int ACCS = 4;
 constexpr int STAGE_LD = 36;       // row stride (floats) of the epilogue staging tiles
 
 struct tc_params
@@ -77,8 +78,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     uint64_t* full_b = bars + 1;
     uint64_t* empty_b = full_b + 16;
     uint64_t* acc_full = empty_b + 16;
-    uint64_t* acc_empty = acc_full + 2;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    uint64_t* acc_empty = acc_full + ACCS;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + ACCS);
     float* staging = reinterpret_cast<float*>(bars + 64); // 8 warps x 32 rows x STAGE_LD floats
 
     const int tid = threadIdx.x;
@@ -101,7 +102,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
             ptx::mbar_init(&full_b[s], 1);
             ptx::mbar_init(&empty_b[s], 1);
         }
-        for (int a = 0; a < 2; ++a)
+        for (int a = 0; a < ACCS; ++a)
         {
             ptx::mbar_init(&acc_full[a], 1);
             ptx::mbar_init(&acc_empty[a], 128);
@@ -163,8 +164,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
             int64_t lt = 0;
             for (int64_t t = t_begin; t < t_end && ok; ++t, ++lt)
             {
-                const int a = static_cast<int>(lt & 1);
-                const uint32_t aph = static_cast<uint32_t>((lt >> 1) & 1);
+                // tile lt goes to accumulator lt % 4 (epilogue group lt % 2), used for the (lt / 4)-th time
+                const int a = static_cast<int>(lt & (ACCS - 1));
+                const uint32_t aph = static_cast<uint32_t>((lt >> 2) & 1);
                 if (!ptx::mbar_wait_bounded(&acc_empty[a], aph ^ 1U))
                 {
                     ok = false;
@@ -217,9 +219,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
             const int64_t r = qb * TILE_M + w4 * 32 + i * 4 + sub;
             qn[i] = r < p.q ? __ldg(p.qn + r) : 0.0F;
         }
-        const uint32_t lane_base = (static_cast<uint32_t>(w4 * 32) << 16) + static_cast<uint32_t>(group * TILE_N);
-        int64_t use = 0; // how many times this group has used its buffer
-        for (int64_t t = t_begin + group; t < t_end && ok; t += 2, ++use)
+        const uint32_t lane_row = static_cast<uint32_t>(w4 * 32) << 16;
+        int64_t lt = group; // this group's tiles are the local tiles group, group + 2, ...
+        for (int64_t t = t_begin + group; t < t_end && ok; t += 2, lt += 2)
         {
             // point norms of this lane's four column quads, fetched before the wait so that their
             // latency hides behind it
@@ -245,8 +247,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                     }
                 }
             }
-            // (the verdict is made warp-uniform: the lanes poll independently)
-            if (!__all_sync(FULL_MASK, ptx::mbar_wait_bounded(&acc_full[group], static_cast<uint32_t>(use & 1))))
+            // (made warp-uniform: the lanes poll independently)
+            const int a = static_cast<int>(lt & (ACCS - 1));
+            const uint32_t lane_base = lane_row + static_cast<uint32_t>(a * TILE_N);
+            if (!__all_sync(FULL_MASK, ptx::mbar_wait_bounded(&acc_full[a], static_cast<uint32_t>((lt >> 2) & 1))))
             {
                 ok = false;
                 break;
@@ -314,7 +318,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                 {
                     // every accumulator of this thread has been read: the MMA warp may reuse the buffer
                     tc::fence_before_sync();
-                    tc::mbar_arrive(&acc_empty[group]);
+                    tc::mbar_arrive(&acc_empty[a]);
                 }
             }
         }
