@@ -201,6 +201,42 @@ def knn_section(bk, dev):
     return result
 
 
+def sharded_knn_section(bk, search, dev, rank, world, barrier, max_over_ranks):
+    """The sharded search of the largest configuration, one shard per GPU: every rank holds 2^24
+    points of dimension 64 (4 GiB; 8 ranks = the 2^27-point database), all 16384 queries, k = 128;
+    fused tensor-core search of the shard (bf16 split images), one all-gather of the candidates,
+    merge.  Queries per second of the whole job, device time, max over ranks."""
+    import torch
+    n_shard, q, dim, k = 1 << 24, 1 << 14, 64, 128
+    gen = torch.Generator(device=dev).manual_seed(1000 + rank)
+    points = torch.rand((n_shard, dim), generator=gen, device=dev)
+    gen_q = torch.Generator(device=dev).manual_seed(7)          # the same queries on every rank
+    queries = torch.rand((q, dim), generator=gen_q, device=dev)
+    mode = bk.L2_BF16
+    ws = torch.empty(max(bk.fused_workspace_bytes(n_shard, q, dim, k, mode), 256), dtype=torch.uint8, device=dev)
+    fin = (torch.empty((q, k), device=dev), torch.empty((q, k), dtype=torch.int32, device=dev))
+
+    def step():
+        search.knn(points, queries, k, rank * n_shard, out=None if world == 1 else fin, mode=mode, workspace=ws)
+
+    step()
+    barrier()
+    steps = 3
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    barrier()
+    ms = max_over_ranks(e0.elapsed_time(e1)) / steps
+    bk.device_status()
+    del points, ws
+    torch.cuda.empty_cache()
+    return {"n_total": n_shard * world, "n_per_gpu": n_shard, "q": q, "dim": dim, "k": k, "mode": "bf16 (tcgen05)",
+            "ms_per_step": ms, "queries_per_s": q / (ms * 1e-3), "distances_per_s": q * n_shard * world / (ms * 1e-3),
+            "steps": steps}
+
+
 def run_profile_case(name):
     """Small cases of the k-NN kernels for profiler captures: a few hundred MB on the device,
     three launches each (inputs larger than L2 where the kernel streams them)."""
@@ -495,6 +531,14 @@ def main():
         torch.cuda.empty_cache()
         knn = knn_section(bk, dev)
 
+    # ---- database-sharded fused k-NN: 2^24 points of dim 64 per GPU, 16384 queries, k = 128 ----
+    knn_sharded = None
+    if not args.no_sweep:
+        if "matrix" in dir():
+            del matrix
+        torch.cuda.empty_cache()
+        knn_sharded = sharded_knn_section(bk, search, dev, rank, world, barrier, max_over_ranks)
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
         if host is None:
@@ -518,6 +562,8 @@ def main():
             line["reference_gpu"] = reference_gpu
         if knn is not None:
             line["knn"] = knn
+        if knn_sharded is not None:
+            line["knn_sharded"] = knn_sharded
         print(json.dumps(line), flush=True)
     if world > 1:
         dist_pg.destroy_process_group()
