@@ -474,6 +474,24 @@ def main():
             del src
         del desc
         torch.cuda.empty_cache()
+        # ablation: the same kernel without its radius filter (the reference's partial-bitonic-regs):
+        # what the buffer + filter buy on uniform rows
+        bk.set_tuning("select.filter", 0)
+        try:
+            od = torch.empty((q, 32), dtype=torch.float32, device=dev)
+            oi = torch.empty((q, 32), dtype=torch.int32, device=dev)
+            bk.select(matrix, 32, out=(od, oi))
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            bk.select(matrix, 32, out=(od, oi))
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1)
+            sweep["uniform_k32_without_filter"] = {"ms": ms, "distances_per_s": q * n / (ms * 1e-3),
+                                                   "frac_of_hbm_peak": (4.0 * q * n + 8.0 * q * 32) / (ms * 1e-3) / 1e9 / peak_gbs}
+        finally:
+            bk.set_tuning("select.filter", 1)
 
     # ---- end to end through the C ABI from host buffers (`e2e`) ----------------------------
     e2e = None

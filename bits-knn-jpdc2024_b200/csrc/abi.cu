@@ -32,6 +32,7 @@ tuning_entry g_tuning[] = {
     {"select.merge_at", 100, 1, 100},
     {"select.auto_split", 1, 0, 1},
     {"select.wide_block", 1, 0, 1},
+    {"select.filter", 1, 0, 1},
     {"fused.variant", 2, 0, 2},
 };
 

@@ -52,6 +52,7 @@ struct select_params
     float* out_dist;  // [rows * splits][k]
     int32_t* out_idx; // [rows * splits][k]
     int raw_pad;      // 1: leave padding as (+inf, PAD_IDX) (candidate lists for a later merge)
+    int no_filter;    // 1: never tighten the radius: every value is buffered, sorted and merged (ablation)
     int stage_floats; // floats per stage, a multiple of 4 * SELECT_THREADS
     int stages;
     int merge_at;     // fold the buffer as soon as it holds this many candidates (<= L)
@@ -81,6 +82,7 @@ struct select_block
     const int32_t* labp; // explicit labels of this slice or nullptr
     int lab0;            // implicit label of slice element 0
     int k;
+    bool keep_radius;    // the un-buffered ablation: the filter radius stays at +inf
 
     __device__ __forceinline__ int label_of(int e) const { return labp != nullptr ? labp[e] : lab0 + e; }
 
@@ -115,8 +117,11 @@ struct select_block
             ctrl->count = 0;
         }
         __syncthreads();
-        r_d = ctrl->r_d;
-        r_x = ctrl->r_x;
+        if (!keep_radius)
+        {
+            r_d = ctrl->r_d;
+            r_x = ctrl->r_x;
+        }
     }
 
     // Evaluates the filter on one 4-vector; returns the number of survivors of this lane.
@@ -305,6 +310,7 @@ __global__ void __launch_bounds__(THREADS) select_kernel(const select_params p)
     uint64_t* bars = reinterpret_cast<uint64_t*>(blk.buf_x + L);
     blk.ctrl = reinterpret_cast<select_ctrl*>(bars + MAX_STAGES);
     blk.k = p.k;
+    blk.keep_radius = p.no_filter != 0;
 
     // which slice of which row
     const int64_t vrow = blockIdx.x;
@@ -782,6 +788,9 @@ extern "C" int bitsknn_select(const float* d_dist, int64_t ld, const int32_t* d_
     {
         return fail(BITSKNN_ERR_CUDA, "CUDA error. cannot resolve the device status word");
     }
+    // "select.filter" = 0 turns the radius filter off: the un-buffered partial bitonic sort the
+    // reference keeps as an ablation (partial-bitonic-regs, src/topk/singlepass/partial_bitonic.cu:217-294)
+    p.no_filter = tuning_value("select.filter", 1) == 0 ? 1 : 0;
     fill_stream_config(p);
     return dispatch_select(p, q, static_cast<cudaStream_t>(stream));
 }

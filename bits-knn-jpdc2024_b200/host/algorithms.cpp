@@ -246,6 +246,17 @@ void bits_knn::selection()
     BITS_CUCH(cudaStreamSynchronize(nullptr));
 }
 
+void partial_bitonic_regs_knn::selection()
+{
+    const auto n = static_cast<std::int64_t>(point_count());
+    abi_check(bitsknn_set_tuning("select.filter", 0));
+    const int status = bitsknn_select(in_dist_gpu(), n, nullptr, 0, nullptr, static_cast<std::int64_t>(query_count()), n,
+                                      static_cast<int>(k()), out_dist_gpu(), out_label_gpu(), nullptr);
+    bitsknn_set_tuning("select.filter", 1);
+    abi_check(status);
+    BITS_CUCH(cudaStreamSynchronize(nullptr));
+}
+
 void bits_sq_knn::initialize(const knn_args& args)
 {
     cuda_knn::initialize(args);
@@ -362,6 +373,7 @@ std::vector<std::unique_ptr<knn>> make_registry()
     std::vector<std::unique_ptr<knn>> algorithms;
     algorithms.push_back(std::make_unique<serial_knn>());
     algorithms.push_back(std::make_unique<parallel_knn>());
+    algorithms.push_back(std::make_unique<partial_bitonic_regs_knn>());
     algorithms.push_back(std::make_unique<bits_knn>("bits"));
     algorithms.push_back(std::make_unique<bits_knn>("bits-prefetch"));
     algorithms.push_back(std::make_unique<bits_sq_knn>());

@@ -254,6 +254,16 @@ private:
     device_buffer<unsigned char> workspace_; // candidates of the slices (only when splits_ > 1)
 };
 
+// `partial-bitonic-regs`: the same kernel with the radius filter switched off -- every value is
+// buffered, sorted and merged.  Kept, like in the reference (partial_bitonic.cu:217-294), to show
+// what the buffer and the filter buy.
+class partial_bitonic_regs_knn : public cuda_knn
+{
+public:
+    std::string id() const override { return "partial-bitonic-regs"; }
+    void selection() override;
+};
+
 // `bits-sq`: rows cut into `deg` slices, then merged (reference: single_query_bits).
 class bits_sq_knn : public cuda_knn
 {

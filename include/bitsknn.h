@@ -61,6 +61,8 @@ int bitsknn_device_status(bitsknn_stream_t stream);
  *   "select.merge_at"     merge the candidate buffer when it holds at least this percentage
  *                         of its capacity (1..100; 100 = only when full, like the reference)
  *   "select.wide_block"   1 = 512-thread blocks for k > 256 (default), 0 = 256-thread blocks
+ *   "select.filter"       0 = bitsknn_select buffers, sorts and merges every value (no radius
+ *                         filter): the reference's un-buffered ablation `partial-bitonic-regs`
  *   "fused.variant"       FP32 fused kernel: 0 = 8 queries per block, 1 = tiled (needs the
  *                         workspace), 2 = automatic (default)
  * The reference's `--block-size` / `--items-per-thread` flags tune the same things for its

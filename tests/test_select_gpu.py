@@ -136,6 +136,18 @@ def test_launch_shapes_do_not_change_results(bk, oracle, cuda, stage_bytes, stag
             bk.set_tuning(key, value)
 
 
+def test_unfiltered_ablation_gives_the_same_result(bk, oracle, cuda):
+    # "select.filter" = 0: every value is buffered, sorted and merged (partial-bitonic-regs)
+    bk.set_tuning("select.filter", 0)
+    try:
+        rng = np.random.default_rng(12)
+        for k in (16, 256, 600):
+            run_select(bk, oracle, rng.random((5, 30001), dtype=np.float32), k)
+            run_select(bk, oracle, rng.integers(0, 40, size=(3, 9000)).astype(np.float32), k)
+    finally:
+        bk.set_tuning("select.filter", 1)
+
+
 def test_config_c1_full_parity(bk, oracle, cuda):
     # q=1024 x n=32768 Uniform[0,1) (numpy Philox stand-in for the seeded matrix), k=32
     rng = np.random.default_rng(42)
