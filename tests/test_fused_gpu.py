@@ -52,6 +52,13 @@ def test_many_tiles_and_index_base(bk, oracle, cuda):
     run_fused(bk, oracle, points, queries, 128, index_base=1 << 20)
 
 
+def test_few_queries_long_database(bk, oracle, cuda):
+    # the tiled kernel cuts the database into parts when the query tiles cannot fill the SMs
+    points, queries = oracle.generate("uniform", 11, 300000, 5, 16)
+    run_fused(bk, oracle, points, queries, 64)
+    run_fused(bk, oracle, points, queries, 7, partial=False, index_base=12345)
+
+
 def test_ties_take_lowest_index(bk, oracle, cuda):
     rng = np.random.default_rng(5)
     points = rng.integers(0, 4, size=(20000, 4)).astype(np.float32)   # many identical points

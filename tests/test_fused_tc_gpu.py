@@ -56,6 +56,16 @@ def test_ragged_shapes(bk, cuda, n, q, k):
     check_against_fp32(bk, points, queries, k, bk.L2_TF32, index_base=1000)
 
 
+def test_few_queries_long_database_is_cut_into_parts(bk, cuda):
+    # 3 queries, 2^19 points: one query tile, so the database is split over many blocks and the
+    # per-part lists are merged
+    gen = torch.Generator(device="cuda").manual_seed(77)
+    points = torch.rand(((1 << 19) + 5, 24), generator=gen, device="cuda")
+    queries = torch.rand((3, 24), generator=gen, device="cuda")
+    check_against_fp32(bk, points, queries, 32, bk.L2_BF16)
+    check_against_fp32(bk, points, queries, 200, bk.L2_TF32)
+
+
 def test_many_parts_and_clustered_data(bk, cuda):
     # 2^18 points: several blocks per query tile; clustered data (256 centres, sigma 0.05)
     gen = torch.Generator(device="cuda").manual_seed(5)
