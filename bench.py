@@ -251,7 +251,7 @@ def run_profile_case(name):
         n, q = 1 << 18, 148 * 128                       # one query tile per SM
         mode = bk.L2_BF16 if name == "fused_tc" else bk.L2_PARTIAL
         if name == "fused_fp32":
-            q = 148 * 2 * 8
+            q = 148 * 2 * 128                           # two 128-query blocks per SM
         points = torch.rand((n, dim), generator=gen, device=dev)
         queries = torch.rand((q, dim), generator=gen, device=dev)
         ws = torch.empty(max(bk.fused_workspace_bytes(n, q, dim, k, mode), 256), dtype=torch.uint8, device=dev)

@@ -34,6 +34,7 @@ SIGNATURES = {
     "bitsknn_version": (_int, []),
     "bitsknn_last_error_string": (ctypes.c_char_p, []),
     "bitsknn_device_status": (_int, [_ptr]),
+    "bitsknn_selftest_bounded_wait": (_int, [_ptr]),
     "bitsknn_set_tuning": (_int, [ctypes.c_char_p, _int]),
     "bitsknn_get_tuning": (_int, [ctypes.c_char_p, ctypes.POINTER(_int)]),
     "bitsknn_select": (_int, [_ptr, _i64, _ptr, _i64, _ptr, _i64, _i64, _int, _ptr, _ptr, _ptr]),
@@ -106,6 +107,10 @@ def get_tuning(key):
 
 def device_status():
     _check(lib().bitsknn_device_status(_stream()))
+
+
+def selftest_bounded_wait():
+    _check(lib().bitsknn_selftest_bounded_wait(_stream()))
 
 
 def _device_check(t, dtype, name):

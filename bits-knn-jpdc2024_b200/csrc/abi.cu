@@ -6,6 +6,7 @@
 #include <string>
 
 #include "common.cuh"
+#include "ptx.cuh"
 
 namespace bitsknn
 {
@@ -93,6 +94,46 @@ int device_sm_count()
 }
 
 } // namespace bitsknn
+
+namespace bitsknn
+{
+
+namespace
+{
+
+// Waits, with a small poll limit, on a barrier phase that nothing will ever complete, and reports
+// the expiry exactly like the production kernels do: status bit, normal return.
+__global__ void selftest_wait_kernel(int* status, uint32_t limit)
+{
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0)
+    {
+        ptx::mbar_init(&bar, 1);
+        ptx::mbar_init_fence();
+    }
+    __syncthreads();
+    if (!ptx::mbar_wait_bounded(&bar, 0, limit) && threadIdx.x == 0)
+    {
+        atomicOr(status, DEVICE_STATUS_TIMEOUT);
+    }
+}
+
+} // namespace
+
+} // namespace bitsknn
+
+extern "C" int bitsknn_selftest_bounded_wait(bitsknn_stream_t stream)
+{
+    using namespace bitsknn;
+    int* word = device_status_word();
+    if (word == nullptr)
+    {
+        return fail(BITSKNN_ERR_CUDA, "CUDA error. cannot resolve the device status word");
+    }
+    selftest_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(word, 1024U);
+    BITSKNN_CUDA_TRY(cudaGetLastError());
+    return BITSKNN_OK;
+}
 
 extern "C" int bitsknn_version(void) { return 100; }
 

@@ -54,6 +54,13 @@ const char* bitsknn_last_error_string(void);
  * waits gives up.  Synchronises `stream`.  Returns BITSKNN_OK or BITSKNN_ERR_DEVICE_TIMEOUT. */
 int bitsknn_device_status(bitsknn_stream_t stream);
 
+/* Diagnostic: launches a one-warp kernel that waits on a barrier nothing ever completes, with a
+ * poll limit of about a thousand tries (well under a millisecond), and reports the expiry the way
+ * the production kernels do.  After it, bitsknn_device_status() returns
+ * BITSKNN_ERR_DEVICE_TIMEOUT once and the context stays usable.  The reference has no device-side
+ * waits and no such check (its only failure path is the CUCH macro, include/bits/cuch.hpp:9-19). */
+int bitsknn_selftest_bounded_wait(bitsknn_stream_t stream);
+
 /* Tuning knobs (launch shapes).  Unknown keys return BITSKNN_ERR_INVALID_ARGUMENT.
  *   "select.stage_bytes"  bytes per shared-memory stage of the row stream (multiple of 4096;
  *                         0 = automatic, the default)

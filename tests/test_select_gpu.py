@@ -148,6 +148,18 @@ def test_unfiltered_ablation_gives_the_same_result(bk, oracle, cuda):
         bk.set_tuning("select.filter", 1)
 
 
+def test_expired_device_wait_is_reported_and_the_context_survives(bk, oracle, cuda):
+    # a bounded wait that nothing satisfies: the kernel gives up, sets the status word, returns
+    bk.device_status()
+    bk.selftest_bounded_wait()
+    with pytest.raises(bk.BitsKnnError) as err:
+        bk.device_status()
+    assert err.value.status == bk.ERR_DEVICE_TIMEOUT
+    bk.device_status()                                   # reported once, then cleared
+    rng = np.random.default_rng(1)
+    run_select(bk, oracle, rng.random((4, 5000), dtype=np.float32), 16)   # the context is still fine
+
+
 def test_config_c1_full_parity(bk, oracle, cuda):
     # q=1024 x n=32768 Uniform[0,1) (numpy Philox stand-in for the seeded matrix), k=32
     rng = np.random.default_rng(42)
