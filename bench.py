@@ -121,20 +121,32 @@ def cpu_selection_baseline(host_matrix, k, budget_s=20.0):
     cores = oracle.num_threads()
     rows = min(host_matrix.shape[0], max(cores, 64))
     sample = np.ascontiguousarray(host_matrix[:rows])
-    oracle.select_heap(sample[:cores], k)  # warm the thread pool and the pages
+    kind, what = "port", "port of parallel_knn::selection"
+    run = lambda m: (oracle.select_heap(m, k), None)[1]
+    try:
+        # the reference's own parallel_knn::selection when it was compiled (it reports the time of
+        # selection() alone, like the reference's main loop)
+        from oracle import ref_select
+        if ref_select.available():
+            ref_select.select("parallel", sample[:cores], k)
+            kind, what = "reference", "the reference's parallel_knn::selection compiled from its sources"
+            run = lambda m: ref_select.select("parallel", m, k)[2]
+    except Exception:
+        kind, what = "port", "port of parallel_knn::selection"
+        run = lambda m: (oracle.select_heap(m, k), None)[1]
+    run(sample[:cores])  # warm the thread pool and the pages
     times = []
     spent = 0.0
     while len(times) < 5 and spent < budget_s:
         t0 = time.perf_counter()
-        oracle.select_heap(sample, k)
+        inner = run(sample)
         dt = time.perf_counter() - t0
-        times.append(dt)
+        times.append(inner if inner is not None else dt)
         spent += dt
     best = statistics.median(times)
-    return {"value": rows * host_matrix.shape[1] / best, "unit": UNIT, "cores": cores, "kind": "port",
+    return {"value": rows * host_matrix.shape[1] / best, "unit": UNIT, "cores": cores, "kind": kind,
             "sample": f"first {rows} of {host_matrix.shape[0]} rows x {host_matrix.shape[1]} columns of the same "
-                      f"matrix, k={k}, OpenMP heap selection (port of parallel_knn::selection), "
-                      f"median of {len(times)} runs"}
+                      f"matrix, k={k}, OpenMP heap selection ({what}), median of {len(times)} runs"}
 
 
 def knn_section(bk, dev):
