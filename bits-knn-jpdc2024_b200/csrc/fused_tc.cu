@@ -237,9 +237,9 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
                 // candidates: slot `lane` of query L's buffer
                 const float cd = lane < cnt_l ? my_buf_d[lane * 32 + L] : INFINITY;
                 const int cx = lane < cnt_l ? my_buf_x[lane * 32 + L] : PAD_IDX;
-                float nd;
-                int nx;
-                warp_fold_global<IPT>(cd, cx, has_l, gl_d, gl_x, p.k, lane, nd, nx);
+                const radius_pair nr = warp_fold_global_call<IPT>(cd, cx, has_l, gl_d, gl_x, p.k, lane);
+                const float nd = nr.d;
+                const int nx = nr.x;
                 if (lane == L)
                 {
                     r_d = nd;

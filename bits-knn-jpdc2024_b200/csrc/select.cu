@@ -290,12 +290,11 @@ struct select_block
     }
 };
 
-template <int THREADS, int IPT>
+template <int THREADS, int IPT, int UNROLL>
 __global__ void __launch_bounds__(THREADS) select_kernel(const select_params p)
 {
     using block_t = select_block<THREADS, IPT>;
     constexpr int L = block_t::L;
-    constexpr int UNROLL = 4;
     constexpr int SPARSE_LANES = 6; // up to this many lanes with a candidate: per-lane insertion
 
     extern __shared__ __align__(128) unsigned char smem[];
@@ -421,7 +420,12 @@ __global__ void __launch_bounds__(THREADS) select_kernel(const select_params p)
                 {
                     mn[u] = fminf(fminf(val[u].x, val[u].y), fminf(val[u].z, val[u].w));
                 }
-                const float mall = fminf(fminf(mn[0], mn[1]), fminf(mn[2], mn[3]));
+                float mall = mn[0];
+#pragma unroll
+                for (int u = 1; u < UNROLL; ++u)
+                {
+                    mall = fminf(mall, mn[u]);
+                }
                 const unsigned hitters = __ballot_sync(FULL_MASK, mall <= blk.r_d);
                 if (hitters == 0)
                 {
@@ -627,12 +631,16 @@ template <int THREADS, int IPT>
 int launch_select(select_params p, int64_t vrows, cudaStream_t stream)
 {
     constexpr int L = THREADS * IPT;
-    const int merge_pct = tuning_value("select.merge_at", 100);
+    const int merge_pct = tuning_value("select.merge_at", 50);
     p.merge_at = std::max(1, (L * merge_pct) / 100);
     // a stage is a whole number of 4-vectors per thread
     p.stage_floats = std::max(4 * THREADS, (p.stage_floats / (4 * THREADS)) * (4 * THREADS));
     const size_t smem = select_smem_bytes(L, p.stage_floats, p.stages);
-    auto kernel = select_kernel<THREADS, IPT>;
+    // 128-bit vectors per thread examined under one warp vote
+    // (0 = automatic: 2 for 256-thread blocks -- no register spills at 4 blocks per SM --, 4 for 512)
+    int unroll = tuning_value("select.unroll", 0);
+    unroll = unroll != 0 ? unroll : (THREADS == 256 ? 2 : 4);
+    auto kernel = unroll == 2 ? select_kernel<THREADS, IPT, 2> : select_kernel<THREADS, IPT, 4>;
     BITSKNN_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     kernel<<<static_cast<unsigned>(vrows), THREADS, smem, stream>>>(p);
     BITSKNN_CUDA_TRY(cudaGetLastError());

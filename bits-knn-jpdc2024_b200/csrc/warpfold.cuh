@@ -110,4 +110,21 @@ __device__ __forceinline__ void warp_fold_global(float cand_d, int cand_x, bool 
     __syncwarp(); // the list stores are ordered before any later load by this warp
 }
 
+// The same fold as a real function call: the kernels that fold from several places in their
+// scan loops keep ONE copy of the sorting networks in their instruction stream this way.
+struct radius_pair
+{
+    float d;
+    int x;
+};
+
+template <int IPT>
+__device__ __noinline__ radius_pair warp_fold_global_call(float cand_d, int cand_x, bool has_list, float* gl_d,
+                                                          int32_t* gl_x, int k, int lane)
+{
+    radius_pair r;
+    warp_fold_global<IPT>(cand_d, cand_x, has_list, gl_d, gl_x, k, lane, r.d, r.x);
+    return r;
+}
+
 } // namespace bitsknn
