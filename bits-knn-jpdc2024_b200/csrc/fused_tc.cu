@@ -62,6 +62,13 @@ struct ftc_params
     int* status;
 };
 
+__device__ __forceinline__ float max3(float a, float b, float c)
+{
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
 template <bool BF16, int IPT>
 __global__ void __launch_bounds__(FT_THREADS, 1)
     fused_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_p, const ftc_params p)
@@ -82,7 +89,8 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
     uint64_t* acc_empty = acc_full + FT_ACCS;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + FT_ACCS);
     float* rad = reinterpret_cast<float*>(bars + 64);     // [2][128] radius distance per group and query
-    float* buf_d = rad + 2 * TILE_M;                      // [8 warps][CAP][32 lanes]
+    float* hlf = rad + 2 * TILE_M;                        // [2][128] distance of list entry ceil(k / 2) - 1
+    float* buf_d = hlf + 2 * TILE_M;                      // [8 warps][CAP][32 lanes]
     int* buf_x = reinterpret_cast<int*>(buf_d + 8 * CAP * 32);
 
     const int tid = threadIdx.x;
@@ -113,6 +121,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
     if (tid < 2 * TILE_M)
     {
         rad[tid] = INFINITY;
+        hlf[tid] = INFINITY;
     }
     if (warp == FT_MMA_WARP)
     {
@@ -220,8 +229,17 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
         float r_d = live ? INFINITY : -INFINITY;
         int r_x = PAD_IDX;
         float thr = live ? -INFINITY : INFINITY; // accumulators >= thr are candidates
+        float h_d = INFINITY; // distance of entry ceil(k / 2) - 1 of this (group, query)'s list
         int cnt = 0;
         bool has_list = false;
+
+        // Upper bound of the query's true k-th distance: each group's own radius, and the larger
+        // of the two groups' entries ceil(k / 2) - 1 (the two lists cover different points, so at
+        // least k pairs lie at or below it).
+        auto bound = [&]() {
+            const int other = (group ^ 1) * TILE_M + qrow;
+            return fminf(fminf(r_d, rad[other]), fmaxf(h_d, hlf[other]));
+        };
 
         // Folds the buffers of the queries whose lanes are set in `mask` into their lists.
         auto fold_queries = [&](unsigned mask) {
@@ -246,7 +264,9 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
                     r_x = nx;
                     cnt = 0;
                     has_list = true;
+                    h_d = nr.half_d;
                     rad[group * TILE_M + qrow] = nd;
+                    hlf[group * TILE_M + qrow] = nr.half_d;
                 }
                 __syncwarp(); // the list stores are ordered before any later load by this warp
             }
@@ -255,26 +275,26 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
         // One half chunk (16 columns) of this thread's row: max-tree, warp vote, pushes, folds.
         // A buffer holds at most 16 pairs when a half starts, so its at most 16 pushes always fit.
         auto scan_half = [&](const uint32_t(&v)[16], int64_t col0) {
-            float mx = __uint_as_float(v[0]);
+            {
+                // maxima of the four groups of four columns, then of the half
+                float g[4];
 #pragma unroll
-            for (int j = 1; j < 16; ++j)
-            {
-                mx = fmaxf(mx, __uint_as_float(v[j]));
-            }
-            if (!__any_sync(FULL_MASK, mx >= thr))
-            {
-                return;
-            }
-            const int ncols = p.n - col0 < 16 ? static_cast<int>(p.n - col0) : 16; // valid columns
-            const float r_part = -2.0F * thr; // the tighter of the two groups' radii
-#pragma unroll
-            for (int j = 0; j < 16; ++j)
-            {
-                const float s = __uint_as_float(v[j]);
-                const bool cand = s >= thr && j < ncols;
-                if (__any_sync(FULL_MASK, cand))
+                for (int i = 0; i < 4; ++i)
                 {
-                    if (cand)
+                    g[i] = fmaxf(max3(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
+                                      __uint_as_float(v[4 * i + 2])),
+                                 __uint_as_float(v[4 * i + 3]));
+                }
+                const float mx = fmaxf(max3(g[0], g[1], g[2]), g[3]);
+                if (!__any_sync(FULL_MASK, mx >= thr))
+                {
+                    return;
+                }
+                const int ncols = p.n - col0 < 16 ? static_cast<int>(p.n - col0) : 16; // valid columns
+                const float r_part = -2.0F * thr; // the bound as a distance
+                auto push = [&](int j) {
+                    const float s = __uint_as_float(v[j]);
+                    if (s >= thr && j < ncols)
                     {
                         const float d = -2.0F * s;
                         const int idx = p.index_base + static_cast<int>(col0 + j);
@@ -283,6 +303,19 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
                             my_buf_d[cnt * 32 + lane] = d;
                             my_buf_x[cnt * 32 + lane] = idx;
                             ++cnt;
+                        }
+                    }
+                };
+                // warp votes per group of four, then per column
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                {
+                    if (__any_sync(FULL_MASK, g[i] >= thr))
+                    {
+#pragma unroll
+                        for (int j = 4 * i; j < 4 * i + 4; ++j)
+                        {
+                            push(j);
                         }
                     }
                 }
@@ -294,7 +327,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
                 fold_queries(need);
                 if (live)
                 {
-                    thr = fmaxf(thr, -0.5F * r_d);
+                    thr = fmaxf(thr, -0.5F * bound());
                 }
             }
         };
@@ -306,9 +339,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
         {
             if (live)
             {
-                // both groups' radii bound the true k-th distance from above
-                const float r_eff = fminf(r_d, rad[(group ^ 1) * TILE_M + qrow]);
-                thr = -0.5F * r_eff;
+                thr = -0.5F * bound();
             }
             const int a = static_cast<int>(lt & (FT_ACCS - 1));
             // (made warp-uniform: the lanes poll independently)
@@ -452,7 +483,7 @@ int run_ftc(const float* points, const float* queries, int64_t n, int64_t q, int
         return fail(BITSKNN_ERR_CUDA, "CUDA error. cannot resolve the device status word");
     }
     // shared memory: query image + ring + barriers + radii + candidate buffers
-    const size_t fixed = 1024 + 64 * 8 + 2 * TILE_M * 4 + 2 * (8 * CAP * 32 * 4);
+    const size_t fixed = 1024 + 64 * 8 + 4 * TILE_M * 4 + 2 * (8 * CAP * 32 * 4);
     const int room = static_cast<int>((227 * 1024 - fixed) / STAGE_BYTES) - p.nkb;
     if (room < 2)
     {

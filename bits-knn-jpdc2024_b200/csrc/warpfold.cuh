@@ -61,15 +61,46 @@ __device__ __forceinline__ void merge_striped(float (&d)[IPT], int (&x)[IPT], in
     }
 }
 
+// Entry `pos` of a striped list (register pos / 32 of lane pos % 32), delivered to every lane.
+// (Opaque selects: a plain ?: chain is turned into an indexed load from a stack copy of the
+// list, which costs a local store per list update.)
+template <int IPT>
+__device__ __forceinline__ float striped_entry_d(const float (&ld)[IPT], int pos)
+{
+    float nd = ld[0];
+#pragma unroll
+    for (int r = 1; r < IPT; ++r)
+    {
+        const int pick = r == pos / 32 ? 1 : 0;
+        asm("{\n.reg .pred p;\nsetp.ne.s32 p, %2, 0;\nselp.f32 %0, %1, %0, p;\n}" : "+f"(nd) : "f"(ld[r]), "r"(pick));
+    }
+    return __shfl_sync(FULL_MASK, nd, pos & 31);
+}
+
+template <int IPT>
+__device__ __forceinline__ int striped_entry_x(const int (&lx)[IPT], int pos)
+{
+    int nx = lx[0];
+#pragma unroll
+    for (int r = 1; r < IPT; ++r)
+    {
+        const int pick = r == pos / 32 ? 1 : 0;
+        asm("{\n.reg .pred p;\nsetp.ne.s32 p, %2, 0;\nselp.s32 %0, %1, %0, p;\n}" : "+r"(nx) : "r"(lx[r]), "r"(pick));
+    }
+    return __shfl_sync(FULL_MASK, nx, pos & 31);
+}
+
 // Folds the candidates (one pair per lane, padding = (+inf, PAD_IDX)) into the list at
 // gl_d / gl_x (striped: entry e in lane e % 32, register e / 32; `has_list` false = the list is
 // still empty and is not read).  The candidates are sorted descending with shuffles, the
 // element-wise minimum against the list's last 32 entries leaves the 32 * IPT smallest pairs as
 // a bitonic array (the candidates count as padded with +inf in front), the striped merge sorts
-// it, and the list is written back.  Every lane returns the new radius pair (entry k - 1).
+// it, and the list is written back.  Every lane returns the new radius pair (entry k - 1) and,
+// when `half_d` is given, the distance of entry ceil(k / 2) - 1.
 template <int IPT>
 __device__ __forceinline__ void warp_fold_global(float cand_d, int cand_x, bool has_list, float* gl_d, int32_t* gl_x,
-                                                 int k, int lane, float& radius_d, int& radius_x)
+                                                 int k, int lane, float& radius_d, int& radius_x,
+                                                 float* half_d = nullptr)
 {
     float cd[1] = {cand_d};
     int cx[1] = {cand_x};
@@ -94,19 +125,14 @@ __device__ __forceinline__ void warp_fold_global(float cand_d, int cand_x, bool 
         gl_d[r * 32 + lane] = ld[r];
         gl_x[r * 32 + lane] = lx[r];
     }
-    float nd = ld[0];
-    int nx = lx[0];
-#pragma unroll
-    for (int r = 1; r < IPT; ++r)
+    radius_d = striped_entry_d<IPT>(ld, k - 1);
+    radius_x = striped_entry_x<IPT>(lx, k - 1);
+    if (half_d != nullptr)
     {
-        // (opaque selects: a plain ?: chain is turned into an indexed load from a stack copy of
-        // the list, which costs a local store per list update)
-        const int pick = r == (k - 1) / 32 ? 1 : 0;
-        asm("{\n.reg .pred p;\nsetp.ne.s32 p, %2, 0;\nselp.f32 %0, %1, %0, p;\n}" : "+f"(nd) : "f"(ld[r]), "r"(pick));
-        asm("{\n.reg .pred p;\nsetp.ne.s32 p, %2, 0;\nselp.s32 %0, %1, %0, p;\n}" : "+r"(nx) : "r"(lx[r]), "r"(pick));
+        // entry ceil(k / 2) - 1: with a second list over other points, the larger of the two
+        // lists' entries at this position has at least k pairs below or at it
+        *half_d = striped_entry_d<IPT>(ld, (k + 1) / 2 - 1);
     }
-    radius_d = __shfl_sync(FULL_MASK, nd, (k - 1) & 31);
-    radius_x = __shfl_sync(FULL_MASK, nx, (k - 1) & 31);
     __syncwarp(); // the list stores are ordered before any later load by this warp
 }
 
@@ -116,6 +142,7 @@ struct radius_pair
 {
     float d;
     int x;
+    float half_d; // distance of entry ceil(k / 2) - 1
 };
 
 template <int IPT>
@@ -123,7 +150,7 @@ __device__ __noinline__ radius_pair warp_fold_global_call(float cand_d, int cand
                                                           int32_t* gl_x, int k, int lane)
 {
     radius_pair r;
-    warp_fold_global<IPT>(cand_d, cand_x, has_list, gl_d, gl_x, k, lane, r.d, r.x);
+    warp_fold_global<IPT>(cand_d, cand_x, has_list, gl_d, gl_x, k, lane, r.d, r.x, &r.half_d);
     return r;
 }
 
