@@ -36,6 +36,7 @@ tuning_entry g_tuning[] = {
     {"select.filter", 1, 0, 1},
     {"select.unroll", 0, 0, 4},
     {"fused.variant", 2, 0, 2},
+    {"fused.tc_mma_n", 0, 0, 256},
 };
 
 } // namespace

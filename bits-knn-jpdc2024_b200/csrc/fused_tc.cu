@@ -1,25 +1,30 @@
 // `bits-fused` on the tensor cores: the partial distance tile is produced by tcgen05.mma in
 // tensor memory and consumed from there by the top-k -- no distance ever reaches HBM.
 //
-// The contraction runs over the pre-pass image of tc_host.cuh with the norm columns enabled,
-// so an accumulator holds  s = x.y - |x|^2 / 2  and the partial distance is d = -2 s
-// (= |x|^2 - 2 x.y, the quantity the reference's fused kernel ranks by,
+// The contraction runs over the compact split image of tc_host.cuh ([hi | lo | norm columns]; the
+// MMA warp pairs the K steps: points.hi with queries.hi and queries.lo, points.lo with
+// queries.hi, norm step with norm step), so an accumulator holds  s = x.y - |x|^2 / 2  and the
+// partial distance is d = -2 s (= |x|^2 - 2 x.y, the quantity the reference's fused kernel ranks by,
 // include/bits/topk/singlepass/fused_cache_kernel_structs.cuh:622-630).  The consumer compares
-// raw accumulators against  -radius / 2: one max-tree and one compare per 32 columns.
+// raw accumulators against  -bound / 2: one max-tree and one vote per 16 columns.
 //
 // Block = 320 threads on one SM, 128 queries (the TMEM lanes):
-//   warp 8   TMA producer (query image once, point image tiles through a ring of 16 KiB stages)
-//   warp 9   TMEM allocation (4 x 128 columns) and tcgen05.mma issue
-//   warps 0-7  consumers, two groups of four.  Group g takes every other point tile (each group
-//            alternates between two accumulator buffers, so the MMAs run two tiles ahead of it);
+//   warp 8   TMA producer (query image once, point image K blocks through a ring of stages)
+//   warp 9   TMEM allocation (4 accumulators of 128 columns) and tcgen05.mma issue.  One MMA
+//            instruction costs about the same time for 128 and for 256 points, so whenever the
+//            ring fits, an MMA covers 256 points and fills two neighbouring accumulators, one per
+//            consumer group (NMMA = 256); long vectors fall back to 128 points per MMA.
+//   warps 0-7  consumers, two groups of four.  Group g takes every other 128-point tile (each
+//            group alternates between two accumulators, so the MMAs run ahead of it);
 //            thread t of a group is query 32 * (warp % 4) + t and reads its row with
 //            tcgen05.ld.  Each (group, query) has a private 32-slot candidate buffer in shared
 //            memory (no atomics: one writer) and a sorted list of KL = 32 * IPT pairs in the
 //            workspace (HBM/L2), touched only when the buffer is folded: the warp sorts the 32
 //            candidates with shuffles, takes the element-wise minimum against the list's last 32
 //            entries and finishes with a bitonic merge (striped arrangement: entry e in lane
-//            e % 32).  A group's radius is tightened by its partner group's (both are upper
-//            bounds of the true k-th distance).
+//            e % 32).  The acceptance bound of a query is the smallest of: its group's radius,
+//            the partner group's radius, and the larger of the two lists' entries
+//            ceil(k / 2) - 1 (the lists cover different points, so k pairs lie at or below it).
 // After the scan the 2 * parts lists of every query are merged by merge_lists(), which also adds
 // the query norm so that the reported distance is |x|^2 + |y|^2 - 2 x.y.
 // Role of the reference's fused_tc_kernel (detail/fused_tc_kernel.cuh:177-445, wmma based and
@@ -53,7 +58,9 @@ struct ftc_params
     int32_t* list_x; // [parts * 2][q][KL]
     int64_t n;
     int64_t q;
-    int nkb;
+    int nkb;    // 128-byte K blocks per row of the images
+    int nsteps; // MMA K steps (32 bytes) per row that hold data
+    int hs;     // steps of the hi part of a compact split image (0: plain image)
     int stages;
     int parts;
     int64_t tiles;
@@ -69,19 +76,21 @@ __device__ __forceinline__ float max3(float a, float b, float c)
     return d;
 }
 
-template <bool BF16, int IPT>
+template <bool BF16, int IPT, int NMMA>
 __global__ void __launch_bounds__(FT_THREADS, 1)
     fused_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_p, const ftc_params p)
 {
     constexpr int KL = 32 * IPT;
     constexpr int KB_ELEMS = BF16 ? 64 : 32;
     constexpr int K_STEP_BYTES = 32;
+    constexpr int NT = NMMA / TILE_N;            // 128-column tiles per MMA (1 or 2)
+    constexpr int STAGE_B = NT * STAGE_BYTES;    // one K block of NMMA points
 
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     unsigned char* a_tiles = smem;
     unsigned char* b_ring = a_tiles + static_cast<size_t>(p.nkb) * STAGE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(b_ring + static_cast<size_t>(p.stages) * STAGE_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(b_ring + static_cast<size_t>(p.stages) * STAGE_B);
     uint64_t* a_full = bars;
     uint64_t* full_b = bars + 1;
     uint64_t* empty_b = full_b + 16;
@@ -93,15 +102,19 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
     float* buf_d = hlf + 2 * TILE_M;                      // [8 warps][CAP][32 lanes]
     int* buf_x = reinterpret_cast<int*>(buf_d + 8 * CAP * 32);
 
+    __shared__ uint2 a_tab[MAX_KB * 4]; // written and read by the MMA-issuing thread alone
+
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
 
     const int64_t qb = blockIdx.x / p.parts;
     const int part = static_cast<int>(blockIdx.x - qb * p.parts);
-    const int64_t per = (p.tiles + p.parts - 1) / p.parts;
+    // tiles of 128 points; a part is a whole number of MMAs (a tile beyond n holds no valid column)
+    const int64_t per = ((p.tiles + p.parts - 1) / p.parts + NT - 1) / NT * NT;
+    const int64_t tiles_up = (p.tiles + NT - 1) / NT * NT;
     const int64_t t_begin = part * per;
-    const int64_t t_end = t_begin + per < p.tiles ? t_begin + per : p.tiles;
+    const int64_t t_end = t_begin + per < tiles_up ? t_begin + per : tiles_up;
 
     if (tid == 0)
     {
@@ -145,7 +158,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
             }
             int s = 0;
             uint32_t ph = 0;
-            for (int64_t t = t_begin; t < t_end && ok; ++t)
+            for (int64_t t = t_begin; t < t_end && ok; t += NT)
             {
                 for (int kb = 0; kb < p.nkb; ++kb)
                 {
@@ -154,8 +167,8 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
                         ok = false;
                         break;
                     }
-                    ptx::mbar_expect_tx(&full_b[s], STAGE_BYTES);
-                    tc::tma_load_2d(b_ring + static_cast<size_t>(s) * STAGE_BYTES, &map_p, kb * KB_ELEMS,
+                    ptx::mbar_expect_tx(&full_b[s], STAGE_B);
+                    tc::tma_load_2d(b_ring + static_cast<size_t>(s) * STAGE_B, &map_p, kb * KB_ELEMS,
                                     static_cast<int>(t * TILE_N), &full_b[s]);
                     if (++s == p.stages)
                     {
@@ -170,22 +183,56 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
     {
         if (lane == 0 && t_begin < t_end)
         {
-            constexpr uint32_t idesc = tc::instr_desc(BF16 ? 1U : 2U, TILE_M, TILE_N);
+            constexpr uint32_t idesc = tc::instr_desc(BF16 ? 1U : 2U, TILE_M, NMMA);
+            // Low descriptor words of the query steps that meet step st of the point image (0: none).
+            // Plain image and norm step: step st itself.  Compact split image: a hi step of the
+            // points meets the queries' hi and lo steps, a lo step the queries' hi step.
+            const uint64_t a_desc0 = tc::smem_desc_sw128(a_tiles);
+            const uint32_t desc_hi = static_cast<uint32_t>(a_desc0 >> 32);
+            const uint32_t b_lo0 = static_cast<uint32_t>(tc::smem_desc_sw128(b_ring));
+            auto a_step = [&](int st) {
+                return static_cast<uint32_t>(a_desc0) + static_cast<uint32_t>(st >> 2) * (STAGE_BYTES >> 4) +
+                       static_cast<uint32_t>((st & 3) * (K_STEP_BYTES >> 4));
+            };
+            for (int st = 0; st < MAX_KB * 4; ++st)
+            {
+                uint2 e = make_uint2(0U, 0U);
+                if (st < p.nsteps)
+                {
+                    if (p.hs == 0 || st >= 2 * p.hs)
+                    {
+                        e.x = a_step(st);
+                    }
+                    else if (st < p.hs)
+                    {
+                        e.x = a_step(st);
+                        e.y = a_step(p.hs + st);
+                    }
+                    else
+                    {
+                        e.x = a_step(st - p.hs);
+                    }
+                }
+                a_tab[st] = e;
+            }
             ok = ptx::mbar_wait_bounded(a_full, 0);
             int s = 0;
             uint32_t ph = 0;
             int64_t lt = 0;
-            for (int64_t t = t_begin; t < t_end && ok; ++t, ++lt)
+            for (int64_t t = t_begin; t < t_end && ok; t += NT, lt += NT)
             {
-                // tile lt goes to accumulator lt % 4 (consumer group lt % 2), used for the (lt / 4)-th time
+                // tile lt goes to accumulator lt % 4 (consumer group lt % 2), used for the (lt / 4)-th
+                // time; a 256-column MMA fills two neighbouring accumulators (one per group) at once
                 const int a = static_cast<int>(lt & (FT_ACCS - 1));
                 const uint32_t aph = static_cast<uint32_t>((lt >> 2) & 1);
-                if (!ptx::mbar_wait_bounded(&acc_empty[a], aph ^ 1U))
+                if (!ptx::mbar_wait_bounded(&acc_empty[a], aph ^ 1U) ||
+                    (NT == 2 && !ptx::mbar_wait_bounded(&acc_empty[a + 1], aph ^ 1U)))
                 {
                     ok = false;
                     break;
                 }
                 tc::fence_after_sync();
+                const uint32_t acc = tmem_base + static_cast<uint32_t>(a * TILE_N);
                 for (int kb = 0; kb < p.nkb && ok; ++kb)
                 {
                     if (!ptx::mbar_wait_bounded(&full_b[s], ph))
@@ -194,13 +241,15 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
                         break;
                     }
                     tc::fence_after_sync();
-                    const uint64_t adesc = tc::smem_desc_sw128(a_tiles + static_cast<size_t>(kb) * STAGE_BYTES);
-                    const uint64_t bdesc = tc::smem_desc_sw128(b_ring + static_cast<size_t>(s) * STAGE_BYTES);
+                    const uint32_t b_lo = b_lo0 + static_cast<uint32_t>(s) * (STAGE_B >> 4);
 #pragma unroll
                     for (int ks = 0; ks < 128 / K_STEP_BYTES; ++ks)
                     {
-                        tc::mma<BF16>(tmem_base + static_cast<uint32_t>(a * TILE_N), adesc + (ks * K_STEP_BYTES >> 4),
-                                      bdesc + (ks * K_STEP_BYTES >> 4), idesc, kb > 0 || ks > 0);
+                        // the one or two query steps that meet this step of the point image
+                        const uint2 a_lo = a_tab[kb * 4 + ks];
+                        const uint32_t b_st = b_lo + static_cast<uint32_t>(ks * (K_STEP_BYTES >> 4));
+                        tc::mma_words<BF16>(acc, a_lo.x, b_st, desc_hi, idesc, (kb | ks) != 0 ? 1U : 0U, a_lo.x);
+                        tc::mma_words<BF16>(acc, a_lo.y, b_st, desc_hi, idesc, 1U, a_lo.y);
                     }
                     tc::mma_commit(&empty_b[s]);
                     if (++s == p.stages)
@@ -210,6 +259,10 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
                     }
                 }
                 tc::mma_commit(&acc_full[a]);
+                if constexpr (NT == 2)
+                {
+                    tc::mma_commit(&acc_full[a + 1]);
+                }
             }
         }
     }
@@ -395,8 +448,11 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
 
 struct ftc_layout
 {
-    int dim_pad;
-    int split;
+    int dim_pad; // row pitch of the images in elements
+    int split;   // image kind for the pre-pass (2: compact split, 0: plain)
+    int hs;      // K steps of the hi part (0: plain image)
+    int nsteps;  // K steps that hold data
+    int nkb;     // 128-byte K blocks per row
     int kl;
     int parts;
     size_t off_pn, off_qn, off_p, off_q, off_ld, off_lx, total;
@@ -405,10 +461,26 @@ struct ftc_layout
 ftc_layout ftc_layout_of(int64_t n, int64_t q, int dim, int k, bool bf16)
 {
     ftc_layout l{};
-    const int unit = bf16 ? 64 : 32;
-    l.split = 3 * dim + 3 <= MAX_KB * unit ? 1 : 0;
-    const int ext = (l.split != 0 ? 3 : 1) * dim + 3;
-    l.dim_pad = ((ext + unit - 1) / unit) * unit;
+    const int unit = bf16 ? 64 : 32; // elements per 128-byte K block
+    const int step = unit / 4;       // elements per MMA K step
+    const int dp = (dim + step - 1) / step * step;
+    if (2 * (dp / step) + 1 <= MAX_KB * 4)
+    {
+        // compact split image: [hi (dp) | lo (dp) | norm columns, padded to one step]
+        l.split = 2;
+        l.hs = dp / step;
+        l.nsteps = 2 * l.hs + 1;
+        l.dim_pad = 2 * dp + step;
+    }
+    else
+    {
+        // plain image: [row | norm columns], padded to whole K blocks
+        l.split = 0;
+        l.hs = 0;
+        l.dim_pad = ((dim + 3 + unit - 1) / unit) * unit;
+        l.nsteps = l.dim_pad / step;
+    }
+    l.nkb = (l.nsteps + 3) / 4;
     l.kl = k <= 32 ? 32 : (k <= 64 ? 64 : (k <= 128 ? 128 : 256));
     const int64_t nqb = (q + TILE_M - 1) / TILE_M;
     const int64_t tiles = (n + TILE_N - 1) / TILE_N;
@@ -430,11 +502,11 @@ ftc_layout ftc_layout_of(int64_t n, int64_t q, int dim, int k, bool bf16)
     return l;
 }
 
-template <bool BF16, int IPT>
+template <bool BF16, int IPT, int NMMA>
 int launch_ftc(const CUtensorMap& map_q, const CUtensorMap& map_p, const ftc_params& p, size_t smem, int64_t grid,
                cudaStream_t stream)
 {
-    auto kernel = fused_tc_kernel<BF16, IPT>;
+    auto kernel = fused_tc_kernel<BF16, IPT, NMMA>;
     BITSKNN_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     kernel<<<static_cast<unsigned>(grid), FT_THREADS, smem, stream>>>(map_q, map_p, p);
     BITSKNN_CUDA_TRY(cudaGetLastError());
@@ -456,23 +528,14 @@ int run_ftc(const float* points, const float* queries, int64_t n, int64_t q, int
         <<<static_cast<unsigned>((q + 7) / 8), 256, 0, stream>>>(queries, q, dim, l.dim_pad, l.split, 0, 1, cq, qn);
     BITSKNN_CUDA_TRY(cudaGetLastError());
 
-    CUtensorMap map_q;
-    CUtensorMap map_p;
-    if (const int rc = make_map(&map_q, cq, q, l.dim_pad, BF16); rc != BITSKNN_OK)
-    {
-        return rc;
-    }
-    if (const int rc = make_map(&map_p, cp, n, l.dim_pad, BF16); rc != BITSKNN_OK)
-    {
-        return rc;
-    }
-
     ftc_params p{};
     p.list_d = reinterpret_cast<float*>(ws + l.off_ld);
     p.list_x = reinterpret_cast<int32_t*>(ws + l.off_lx);
     p.n = n;
     p.q = q;
-    p.nkb = l.dim_pad / (BF16 ? 64 : 32);
+    p.nkb = l.nkb;
+    p.nsteps = l.nsteps;
+    p.hs = l.hs;
     p.parts = l.parts;
     p.tiles = (n + TILE_N - 1) / TILE_N;
     p.k = k;
@@ -482,31 +545,54 @@ int run_ftc(const float* points, const float* queries, int64_t n, int64_t q, int
     {
         return fail(BITSKNN_ERR_CUDA, "CUDA error. cannot resolve the device status word");
     }
-    // shared memory: query image + ring + barriers + radii + candidate buffers
+    // shared memory: query image + ring + barriers + radii + candidate buffers.  The MMA covers 256
+    // points (two tiles, one per consumer group) when at least two of its 32 KiB stages fit beside
+    // the query image, else 128 points.
     const size_t fixed = 1024 + 64 * 8 + 4 * TILE_M * 4 + 2 * (8 * CAP * 32 * 4);
-    const int room = static_cast<int>((227 * 1024 - fixed) / STAGE_BYTES) - p.nkb;
-    if (room < 2)
+    const int room128 = static_cast<int>((227 * 1024 - fixed) / STAGE_BYTES) - p.nkb;
+    if (room128 < 2)
     {
         return fail(BITSKNN_ERR_UNSUPPORTED_DIM, "Unsupported dimension: %d (query image does not fit shared memory)", dim);
     }
-    p.stages = std::min(8, room);
-    const size_t smem = fixed + static_cast<size_t>(p.nkb + p.stages) * STAGE_BYTES;
+    const int want_n = tuning_value("fused.tc_mma_n", 0);
+    const bool wide = want_n == 128 ? false : room128 >= 4;
+    const int nt = wide ? 2 : 1;
+    p.stages = std::min(wide ? 4 : 8, room128 / nt);
+    const size_t smem = fixed + (static_cast<size_t>(p.nkb) + static_cast<size_t>(p.stages) * nt) * STAGE_BYTES;
+
+    CUtensorMap map_q;
+    CUtensorMap map_p;
+    if (const int rc = make_map(&map_q, cq, q, l.dim_pad, BF16); rc != BITSKNN_OK)
+    {
+        return rc;
+    }
+    if (const int rc = make_map(&map_p, cp, n, l.dim_pad, BF16, wide ? 256U : 128U); rc != BITSKNN_OK)
+    {
+        return rc;
+    }
+
     const int64_t nqb = (q + TILE_M - 1) / TILE_M;
     const int64_t grid = nqb * p.parts;
     int rc;
-    switch (l.kl)
+    switch (l.kl * nt)
     {
     case 32:
-        rc = launch_ftc<BF16, 1>(map_q, map_p, p, smem, grid, stream);
+        rc = launch_ftc<BF16, 1, 128>(map_q, map_p, p, smem, grid, stream);
         break;
     case 64:
-        rc = launch_ftc<BF16, 2>(map_q, map_p, p, smem, grid, stream);
+        rc = wide ? launch_ftc<BF16, 1, 256>(map_q, map_p, p, smem, grid, stream)
+                  : launch_ftc<BF16, 2, 128>(map_q, map_p, p, smem, grid, stream);
         break;
     case 128:
-        rc = launch_ftc<BF16, 4>(map_q, map_p, p, smem, grid, stream);
+        rc = wide ? launch_ftc<BF16, 2, 256>(map_q, map_p, p, smem, grid, stream)
+                  : launch_ftc<BF16, 4, 128>(map_q, map_p, p, smem, grid, stream);
+        break;
+    case 256:
+        rc = wide ? launch_ftc<BF16, 4, 256>(map_q, map_p, p, smem, grid, stream)
+                  : launch_ftc<BF16, 8, 128>(map_q, map_p, p, smem, grid, stream);
         break;
     default:
-        rc = launch_ftc<BF16, 8>(map_q, map_p, p, smem, grid, stream);
+        rc = launch_ftc<BF16, 8, 256>(map_q, map_p, p, smem, grid, stream);
         break;
     }
     if (rc != BITSKNN_OK)

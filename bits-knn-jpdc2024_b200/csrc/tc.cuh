@@ -134,6 +134,43 @@ __device__ __forceinline__ void mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b
     }
 }
 
+// The same with the descriptors given as their low words (start address and leading byte offset:
+// the part that differs between tiles and K steps) plus the shared high word; `enable` == 0
+// skips the instruction.  Keeps the issuing thread's 64-bit arithmetic out of its loop.
+template <bool BF16>
+__device__ __forceinline__ void mma_words(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi, uint32_t idesc,
+                                          uint32_t accumulate, uint32_t enable)
+{
+    if constexpr (BF16)
+    {
+        asm volatile("{\n"
+                     ".reg .pred p, q;\n"
+                     ".reg .b64 da, db;\n"
+                     "setp.ne.b32 p, %5, 0;\n"
+                     "setp.ne.b32 q, %6, 0;\n"
+                     "mov.b64 da, {%1, %3};\n"
+                     "mov.b64 db, {%2, %3};\n"
+                     "@q tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n"
+                     "}\n" ::"r"(d_tmem),
+                     "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate), "r"(enable)
+                     : "memory");
+    }
+    else
+    {
+        asm volatile("{\n"
+                     ".reg .pred p, q;\n"
+                     ".reg .b64 da, db;\n"
+                     "setp.ne.b32 p, %5, 0;\n"
+                     "setp.ne.b32 q, %6, 0;\n"
+                     "mov.b64 da, {%1, %3};\n"
+                     "mov.b64 db, {%2, %3};\n"
+                     "@q tcgen05.mma.cta_group::1.kind::tf32 [%0], da, db, %4, p;\n"
+                     "}\n" ::"r"(d_tmem),
+                     "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate), "r"(enable)
+                     : "memory");
+    }
+}
+
 // Makes `bar` complete one arrival when every MMA issued so far by this thread has finished.
 __device__ __forceinline__ void mma_commit(uint64_t* bar)
 {

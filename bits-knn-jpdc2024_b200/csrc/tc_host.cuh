@@ -29,6 +29,11 @@ constexpr int MAX_KB = 8;          // K blocks of 128 bytes in the resident quer
 //     queries  [hi | hi | lo]      points  [hi | lo | hi]
 // so that ONE contraction over 3 * dim yields hi.hi + hi.lo + lo.hi -- the product with the
 // rounding error of both inputs compensated to first order (only lo.lo is dropped).
+// Compact split image (`split` == 2): hi and lo are stored once each, both zero padded to a
+// whole number of MMA K steps (dp = dim rounded up to 16 BF16 / 8 TF32 elements):
+//     [hi (dp) | lo (dp) | norm columns]
+// and the kernel that reads it pairs the steps itself (hi.hi, lo.hi, hi.lo), which saves the
+// memory traffic of the duplicated hi part.
 //
 // With `norm_cols` != 0 three more coordinates follow the vector part: for points the three-way
 // split of -|x|^2 / 2 in the input type (together exact to FP32), for queries 1, 1, 1.  The
@@ -68,7 +73,20 @@ __global__ void tc_prepare_kernel(const float* __restrict__ src, int64_t rows, i
     };
     const float* in = src + row * dim;
     float nrm = 0.0F;
-    for (int d = lane; d < dim; d += 32)
+    constexpr int STEP = BF16 ? 16 : 8;
+    const int dp = (dim + STEP - 1) / STEP * STEP;
+    if (split == 2)
+    {
+        for (int d = lane; d < dp; d += 32)
+        {
+            const float v = d < dim ? in[d] : 0.0F;
+            nrm = fmaf(v, v, nrm);
+            const float hi = round_in(v);
+            store(d, hi);
+            store(dp + d, round_in(v - hi));
+        }
+    }
+    for (int d = lane; d < dim && split != 2; d += 32)
     {
         const float v = in[d];
         nrm = fmaf(v, v, nrm);
@@ -90,7 +108,7 @@ __global__ void tc_prepare_kernel(const float* __restrict__ src, int64_t rows, i
     {
         nrm += __shfl_xor_sync(FULL_MASK, nrm, o);
     }
-    int tail = (split != 0 ? 3 : 1) * dim;
+    int tail = split == 2 ? 2 * dp : (split != 0 ? 3 : 1) * dim;
     if (norm_cols != 0)
     {
         if (lane == 0)
@@ -144,8 +162,10 @@ encode_fn_t tensor_map_encoder()
     return fn;
 }
 
-// rows x dim_pad matrix of 4-byte (TF32) or 2-byte (BF16) elements, box = 128 bytes x 128 rows
-int make_map(CUtensorMap* map, void* base, int64_t rows, int dim_pad, bool bf16)
+// rows x dim_pad matrix of 4-byte (TF32) or 2-byte (BF16) elements, box = 128 bytes x `box_rows` rows
+// (a row pitch that is not a whole number of boxes is fine: the last box is zero filled past the
+// row's end); the pitch in bytes must be a multiple of 16
+int make_map(CUtensorMap* map, void* base, int64_t rows, int dim_pad, bool bf16, unsigned box_rows = 128U)
 {
     encode_fn_t encode = tensor_map_encoder();
     if (encode == nullptr)
@@ -154,7 +174,7 @@ int make_map(CUtensorMap* map, void* base, int64_t rows, int dim_pad, bool bf16)
     }
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(dim_pad), static_cast<cuuint64_t>(rows)};
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(dim_pad) * (bf16 ? 2U : 4U)};
-    const cuuint32_t box[2] = {bf16 ? 64U : 32U, 128U};
+    const cuuint32_t box[2] = {bf16 ? 64U : 32U, box_rows};
     const cuuint32_t elem[2] = {1U, 1U};
     const CUresult rc = encode(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, base,
                                dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
