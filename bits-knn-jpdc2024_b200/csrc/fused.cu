@@ -32,7 +32,8 @@ int fused_tc_launch(const float* points, const float* queries, int64_t n, int64_
                     cudaStream_t stream);
 
 // FP32 tiled variant (128 queries per block) lives in fused_tiled.cu
-size_t fused_tiled_workspace_bytes(int64_t n, int64_t q, int k);
+bool fused_tiled_supports(int dim);
+size_t fused_tiled_workspace_bytes(int64_t n, int64_t q, int dim, int k);
 int fused_tiled_launch(const float* points, const float* queries, int64_t n, int64_t q, int dim, int k, int mode,
                        int32_t index_base, float* out_dist, int32_t* out_idx, void* workspace, size_t workspace_bytes,
                        cudaStream_t stream);
@@ -366,7 +367,7 @@ extern "C" size_t bitsknn_fused_workspace_bytes(int64_t n, int64_t q, int dim, i
     if (mode == BITSKNN_L2_PARTIAL || mode == BITSKNN_L2_EXACT)
     {
         // optional for the FP32 modes: with it the tiled kernel (128 queries per block) can be used
-        return fused_tiled_workspace_bytes(n, q, k);
+        return fused_tiled_workspace_bytes(n, q, dim, k);
     }
     return 0;
 }
@@ -413,7 +414,8 @@ extern "C" int bitsknn_fused(const float* d_points, const float* d_queries, int6
     // FP32: the tiled kernel needs its list workspace; without one (or when asked through the
     // "fused.variant" knob: 0 = 8-query blocks, 1 = tiled, 2 = automatic) the 8-query kernel runs
     const int variant = tuning_value("fused.variant", 2);
-    const bool have_ws = d_workspace != nullptr && workspace_bytes >= fused_tiled_workspace_bytes(n, q, k) &&
+    const bool have_ws = fused_tiled_supports(dim) && d_workspace != nullptr &&
+                         workspace_bytes >= fused_tiled_workspace_bytes(n, q, dim, k) &&
                          (reinterpret_cast<uintptr_t>(d_workspace) & 255U) == 0;
     if (have_ws && (variant == 1 || (variant == 2 && dim >= FUSED_TILED_MIN_DIM)))
     {

@@ -235,6 +235,14 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
                 const uint32_t acc = tmem_base + static_cast<uint32_t>(a * TILE_N);
                 for (int kb = 0; kb < p.nkb && ok; ++kb)
                 {
+                    // the one or two query steps that meet each of the four steps of this K block
+                    // (read before the wait: the MMA statements below order memory accesses)
+                    uint2 a_words[4];
+#pragma unroll
+                    for (int ks = 0; ks < 4; ++ks)
+                    {
+                        a_words[ks] = a_tab[kb * 4 + ks];
+                    }
                     if (!ptx::mbar_wait_bounded(&full_b[s], ph))
                     {
                         ok = false;
@@ -245,8 +253,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
 #pragma unroll
                     for (int ks = 0; ks < 128 / K_STEP_BYTES; ++ks)
                     {
-                        // the one or two query steps that meet this step of the point image
-                        const uint2 a_lo = a_tab[kb * 4 + ks];
+                        const uint2 a_lo = a_words[ks];
                         const uint32_t b_st = b_lo + static_cast<uint32_t>(ks * (K_STEP_BYTES >> 4));
                         tc::mma_words<BF16>(acc, a_lo.x, b_st, desc_hi, idesc, (kb | ks) != 0 ? 1U : 0U, a_lo.x);
                         tc::mma_words<BF16>(acc, a_lo.y, b_st, desc_hi, idesc, 1U, a_lo.y);
@@ -325,50 +332,42 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
             }
         };
 
-        // One half chunk (16 columns) of this thread's row: max-tree, warp vote, pushes, folds.
-        // A buffer holds at most 16 pairs when a half starts, so its at most 16 pushes always fit.
-        auto scan_half = [&](const uint32_t(&v)[16], int64_t col0) {
+        // Maxima of the four groups of four columns of a half chunk.
+        auto group_maxima = [](const uint32_t(&v)[16], float(&g)[4]) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
             {
-                // maxima of the four groups of four columns, then of the half
-                float g[4];
+                g[i] = fmaxf(max3(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]), __uint_as_float(v[4 * i + 2])),
+                             __uint_as_float(v[4 * i + 3]));
+            }
+        };
+
+        // The candidates of one half chunk (16 columns) of this thread's row go to its buffer; full
+        // buffers are folded.  A buffer holds at most 16 pairs when a half starts, so its at most
+        // 16 pushes always fit.
+        auto push_half = [&](const uint32_t(&v)[16], const float(&g)[4], int64_t col0) {
+            const int ncols = p.n - col0 < 16 ? static_cast<int>(p.n - col0) : 16; // valid columns
+            const float r_part = -2.0F * thr; // the bound as a distance
+            // warp votes per group of four, then per column
 #pragma unroll
-                for (int i = 0; i < 4; ++i)
+            for (int i = 0; i < 4; ++i)
+            {
+                if (__any_sync(FULL_MASK, g[i] >= thr))
                 {
-                    g[i] = fmaxf(max3(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
-                                      __uint_as_float(v[4 * i + 2])),
-                                 __uint_as_float(v[4 * i + 3]));
-                }
-                const float mx = fmaxf(max3(g[0], g[1], g[2]), g[3]);
-                if (!__any_sync(FULL_MASK, mx >= thr))
-                {
-                    return;
-                }
-                const int ncols = p.n - col0 < 16 ? static_cast<int>(p.n - col0) : 16; // valid columns
-                const float r_part = -2.0F * thr; // the bound as a distance
-                auto push = [&](int j) {
-                    const float s = __uint_as_float(v[j]);
-                    if (s >= thr && j < ncols)
+#pragma unroll
+                    for (int j = 4 * i; j < 4 * i + 4; ++j)
                     {
-                        const float d = -2.0F * s;
-                        const int idx = p.index_base + static_cast<int>(col0 + j);
-                        if (d <= r_part && pair_lt(d, idx, r_d, r_x))
+                        const float s = __uint_as_float(v[j]);
+                        if (s >= thr && j < ncols)
                         {
-                            my_buf_d[cnt * 32 + lane] = d;
-                            my_buf_x[cnt * 32 + lane] = idx;
-                            ++cnt;
-                        }
-                    }
-                };
-                // warp votes per group of four, then per column
-#pragma unroll
-                for (int i = 0; i < 4; ++i)
-                {
-                    if (__any_sync(FULL_MASK, g[i] >= thr))
-                    {
-#pragma unroll
-                        for (int j = 4 * i; j < 4 * i + 4; ++j)
-                        {
-                            push(j);
+                            const float d = -2.0F * s;
+                            const int idx = p.index_base + static_cast<int>(col0 + j);
+                            if (d <= r_part && pair_lt(d, idx, r_d, r_x))
+                            {
+                                my_buf_d[cnt * 32 + lane] = d;
+                                my_buf_x[cnt * 32 + lane] = idx;
+                                ++cnt;
+                            }
                         }
                     }
                 }
@@ -403,29 +402,38 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
             }
             tc::fence_after_sync();
             const uint32_t acc_addr = tmem_base + lane_base + static_cast<uint32_t>(a * TILE_N);
-            // 16 columns at a time, the next 16 in flight from tensor memory while these are scanned
+            // 32 columns per step: both halves' max-trees run side by side and one vote rejects the
+            // step; the registers are free for the next load as soon as the step is decided (the
+            // other warp of this scheduler covers the load's latency)
             uint32_t lo[16];
             uint32_t hi[16];
-            tc::tmem_ld_32x16(acc_addr, lo);
+            tc::tmem_ld_32x32_halves(acc_addr, lo, hi);
 #pragma unroll 1
             for (int c = 0; c < TILE_N / 32; ++c)
             {
-                const int64_t col0 = t * TILE_N + c * 32;
+                float g_lo[4];
+                float g_hi[4];
                 tc::tmem_ld_wait();
-                tc::tmem_ld_32x16(acc_addr + static_cast<uint32_t>(c * 32 + 16), hi);
-                scan_half(lo, col0);
-                tc::tmem_ld_wait();
+                group_maxima(lo, g_lo);
+                group_maxima(hi, g_hi);
+                const float mx = max3(max3(g_lo[0], g_lo[1], g_lo[2]), max3(g_hi[0], g_hi[1], g_hi[2]),
+                                      fmaxf(g_lo[3], g_hi[3]));
+                if (__any_sync(FULL_MASK, mx >= thr))
+                {
+                    const int64_t col0 = t * TILE_N + c * 32;
+                    push_half(lo, g_lo, col0);
+                    push_half(hi, g_hi, col0 + 16);
+                }
                 if (c + 1 < TILE_N / 32)
                 {
-                    tc::tmem_ld_32x16(acc_addr + static_cast<uint32_t>(c * 32 + 32), lo);
+                    tc::tmem_ld_32x32_halves(acc_addr + static_cast<uint32_t>(c * 32 + 32), lo, hi);
                 }
                 else
                 {
-                    // every accumulator of this thread is in registers: the buffer may be reused
+                    // every accumulator of this thread has been looked at: the buffer may be reused
                     tc::fence_before_sync();
                     tc::mbar_arrive(&acc_empty[a]);
                 }
-                scan_half(hi, col0 + 16);
             }
         }
         // flush: every live (group, query) leaves a complete list behind, padding included

@@ -3,21 +3,27 @@
 // arithmetic as l2.cu, hence bit-identical with the reference's fused kernel and its
 // abstract_gemm) is filtered in registers instead of being stored.
 //
-// Against the 8-queries-per-block kernel of fused.cu every database coordinate fetched from L2
-// now feeds 128 queries instead of 8, and the inner loop is the distance kernel's (64 FMAs per
-// four 128-bit shared-memory loads).  Per query the block keeps a 32-slot candidate buffer in
-// shared memory (slots handed out by shared atomics) and the radius; the sorted lists
-// (32 * IPT pairs) live in the workspace and are only touched by folds, which the warps do with
-// the shuffle networks of warpfold.cuh (warp w folds queries w, w + 8, ...).  A fold round runs
-// when some buffer is at least half full or a candidate found no slot; candidates left over are
-// filtered again by the tightened radius.  The database may be cut into `parts` ranges scanned by
-// different blocks (small q); merge_lists() merges the per-part lists.
+// A pre-pass writes both inputs as tile images: for every 128 rows the coordinates transposed,
+// [coordinate][row] (coordinates zero padded to a multiple of four, which changes no FP32 sum),
+// followed by one row of squared norms (accumulated in coordinate order like the reference does).
+// The block keeps its query image resident in shared memory and streams the point image through a
+// ring of 16-coordinate slabs with 1-D bulk copies (cp.async.bulk + mbarrier): the compute warps
+// issue no global loads at all, their inner loop is four 128-bit shared-memory loads per 64 FMAs.
+//
+// Per query the block keeps a 32-slot candidate buffer in shared memory (slots handed out by
+// shared atomics) and the radius; the sorted lists (32 * IPT pairs) live in the workspace and are
+// only touched by folds, which the warps do with the shuffle networks of warpfold.cuh (warp w folds
+// queries w, w + 8, ...).  A fold round runs when some buffer is at least half full or a candidate
+// found no slot; candidates left over are filtered again by the tightened radius.  The database
+// may be cut into `parts` ranges scanned by different blocks (small q); merge_lists() merges the
+// per-part lists.
 // Reference counterpart: fused_cache_kernel::run + multi_buffer
 // (include/bits/topk/singlepass/fused_cache_kernel_structs.cuh:25-305,716-799).
 #include <algorithm>
 #include <cstdint>
 
 #include "common.cuh"
+#include "ptx.cuh"
 #include "sortnet.cuh"
 #include "warpfold.cuh"
 
@@ -29,61 +35,59 @@ namespace
 
 constexpr int FT_BM = 128;
 constexpr int FT_BN = 128;
-constexpr int FT_BK = 16;
-constexpr int FT_PAD = FT_BM + 4;
+constexpr int FT_BK = 16;      // coordinates per slab
+constexpr int FT_STAGES = 4;   // slabs in flight
 constexpr int FT_THREADS = 256;
 constexpr int FT_CAP = 32;
+constexpr int FT_SLAB_FLOATS = (FT_BK + 1) * FT_BN; // 16 coordinate rows + room for the norm row
+constexpr int FT_MAX_DIM = 320;                     // query image + ring + buffers within 227 KiB
 
 struct tiled_params
 {
-    const float* points;
-    const float* queries;
+    const float* pimg; // [tiles][dp + 1][128]: point coordinates transposed per tile, then |x|^2
+    const float* qimg; // [query tiles][dp + 1][128]
     int64_t n;
     int64_t q;
-    int dim;
+    int dp; // coordinates padded to a multiple of 4
     int k;
     int32_t index_base;
     int parts;
     int64_t tiles; // point tiles of 128
     float* list_d; // [parts][q][KL]
     int32_t* list_x;
-    int vec_in;
+    int* status;
 };
 
-__device__ __forceinline__ void ft_load8(const float* __restrict__ base, int64_t rows, int dim, int64_t row, int k0,
-                                         bool vec, float (&v)[8])
+// Pre-pass: one block per 128 rows, thread r owns row r of the tile.
+__global__ void __launch_bounds__(FT_BN) ft_image_kernel(const float* __restrict__ src, int64_t rows, int dim, int dp,
+                                                         float* __restrict__ dst)
 {
-    if (row < rows && vec && k0 + 8 <= dim)
+    const int r = threadIdx.x;
+    const int64_t row = static_cast<int64_t>(blockIdx.x) * FT_BN + r;
+    float* out = dst + static_cast<int64_t>(blockIdx.x) * (dp + 1) * FT_BN;
+    const float* in = src + row * dim;
+    float nrm = 0.0F;
+    for (int d = 0; d < dp; ++d)
     {
-        const float4* p = reinterpret_cast<const float4*>(base + row * dim + k0);
-        const float4 a = __ldg(p);
-        const float4 b = __ldg(p + 1);
-        v[0] = a.x;
-        v[1] = a.y;
-        v[2] = a.z;
-        v[3] = a.w;
-        v[4] = b.x;
-        v[5] = b.y;
-        v[6] = b.z;
-        v[7] = b.w;
-        return;
+        const float v = (row < rows && d < dim) ? __ldg(in + d) : 0.0F;
+        nrm = fmaf(v, v, nrm);
+        out[d * FT_BN + r] = v;
     }
-#pragma unroll
-    for (int j = 0; j < 8; ++j)
-    {
-        v[j] = (row < rows && k0 + j < dim) ? __ldg(base + row * dim + k0 + j) : 0.0F;
-    }
+    out[dp * FT_BN + r] = nrm;
 }
 
 template <int IPT, bool PARTIAL>
 __global__ void __launch_bounds__(FT_THREADS, 2) fused_tiled_kernel(const tiled_params p)
 {
     constexpr int KL = 32 * IPT;
-    extern __shared__ __align__(16) unsigned char ft_smem[];
-    auto As = reinterpret_cast<float(*)[FT_BK][FT_PAD]>(ft_smem);                        // [2][16][132]
-    auto Bs = reinterpret_cast<float(*)[FT_BK][FT_PAD]>(ft_smem + sizeof(float) * 2 * FT_BK * FT_PAD);
-    auto buf_d = reinterpret_cast<float(*)[FT_CAP]>(ft_smem + sizeof(float) * 4 * FT_BK * FT_PAD); // [128][32]
-    auto buf_x = reinterpret_cast<int(*)[FT_CAP]>(ft_smem + sizeof(float) * (4 * FT_BK * FT_PAD + FT_BM * FT_CAP));
+    // ring [FT_STAGES][17][128] | query image [dp][128] | candidate buffers [128][32] x 2
+    extern __shared__ __align__(128) unsigned char ft_smem[];
+    float* Bs = reinterpret_cast<float*>(ft_smem);
+    float* As = Bs + FT_STAGES * FT_SLAB_FLOATS;
+    auto buf_d = reinterpret_cast<float(*)[FT_CAP]>(As + p.dp * FT_BM);
+    auto buf_x = reinterpret_cast<int(*)[FT_CAP]>(As + p.dp * FT_BM + FT_BM * FT_CAP);
+    __shared__ uint64_t full[FT_STAGES];
+    __shared__ uint64_t a_full;
     __shared__ int cnt[FT_BM];
     __shared__ float sr_d[FT_BM];
     __shared__ int sr_x[FT_BM];
@@ -94,16 +98,16 @@ __global__ void __launch_bounds__(FT_THREADS, 2) fused_tiled_kernel(const tiled_
     const int warp = tid >> 5;
     const int tx = tid & 15;
     const int ty = tid >> 4;
-    const int64_t qb = blockIdx.x / p.parts;
-    const int part = static_cast<int>(blockIdx.x - qb * p.parts);
-    const int64_t m0 = qb * FT_BM;
-    const int64_t per = (p.tiles + p.parts - 1) / p.parts;
-    const int64_t t_begin = part * per;
-    const int64_t t_end = t_begin + per < p.tiles ? t_begin + per : p.tiles;
-
-    const int lrow = tid >> 1;
-    const int lk = (tid & 1) * 8;
-    const int ntk = (p.dim + FT_BK - 1) / FT_BK;
+    // (32-bit tile and slab counters: fewer registers; the host checks that they fit)
+    const int qb = static_cast<int>(blockIdx.x) / p.parts;
+    const int part = static_cast<int>(blockIdx.x) - qb * p.parts;
+    const int64_t m0 = static_cast<int64_t>(qb) * FT_BM;
+    const int tiles = static_cast<int>(p.tiles);
+    const int per = (tiles + p.parts - 1) / p.parts;
+    const int t_begin = part * per;
+    const int t_end = t_begin + per < tiles ? t_begin + per : tiles;
+    const int nslab = (p.dp + FT_BK - 1) / FT_BK;
+    const int total = (t_end > t_begin ? t_end - t_begin : 0) * nslab; // slabs this block consumes
 
     if (tid < FT_BM)
     {
@@ -113,7 +117,56 @@ __global__ void __launch_bounds__(FT_THREADS, 2) fused_tiled_kernel(const tiled_
         sr_d[tid] = m0 + tid < p.q ? INFINITY : -INFINITY;
         sr_x[tid] = PAD_IDX;
     }
+    if (tid == 0)
+    {
+        ptx::mbar_init(&a_full, 1);
+        for (int s = 0; s < FT_STAGES; ++s)
+        {
+            ptx::mbar_init(&full[s], 1);
+        }
+        ptx::mbar_init_fence();
+    }
     __syncthreads();
+
+    // Producer state (thread 0 alone): the next slab to request, as (tile, slab) and as a count.
+    int issue_t = t_begin;
+    int issue_s = 0;
+    int issued = 0;
+    auto issue_slab = [&](int stage) {
+        const int rows = p.dp - issue_s * FT_BK < FT_BK ? p.dp - issue_s * FT_BK : FT_BK;
+        // the norm row follows the last coordinate row and travels with the last slab
+        const uint32_t bytes = static_cast<uint32_t>(rows + (issue_s == nslab - 1 ? 1 : 0)) * FT_BN * 4U;
+        const float* src = p.pimg + (static_cast<int64_t>(issue_t) * (p.dp + 1) + issue_s * FT_BK) * FT_BN;
+        ptx::mbar_expect_tx(&full[stage], bytes);
+        ptx::bulk_g2s(Bs + stage * FT_SLAB_FLOATS, src, bytes, &full[stage]);
+        ++issued;
+        if (++issue_s == nslab)
+        {
+            issue_s = 0;
+            ++issue_t;
+        }
+    };
+    if (tid == 0 && total > 0)
+    {
+        const uint32_t a_bytes = static_cast<uint32_t>(p.dp) * FT_BM * 4U;
+        ptx::mbar_expect_tx(&a_full, a_bytes);
+        const float* qsrc = p.qimg + static_cast<int64_t>(qb) * (p.dp + 1) * FT_BM;
+        for (int s = 0; s < nslab; ++s)
+        {
+            const int rows = p.dp - s * FT_BK < FT_BK ? p.dp - s * FT_BK : FT_BK;
+            ptx::bulk_g2s(As + s * FT_BK * FT_BM, qsrc + s * FT_BK * FT_BM, static_cast<uint32_t>(rows) * FT_BM * 4U,
+                          &a_full);
+        }
+        for (int s = 0; s < FT_STAGES && issued < total; ++s)
+        {
+            issue_slab(s);
+        }
+    }
+    bool ok = true;
+    if (total > 0)
+    {
+        ok = ptx::mbar_wait_bounded(&a_full, 0);
+    }
 
     // folds the buffers of this warp's queries (w, w + 8, ...) that hold candidates
     auto fold_round = [&]() {
@@ -130,13 +183,11 @@ __global__ void __launch_bounds__(FT_THREADS, 2) fused_tiled_kernel(const tiled_
                 const int cx = lane < valid ? buf_x[qi][lane] : PAD_IDX;
                 float* gl_d = p.list_d + (static_cast<int64_t>(part) * p.q + m0 + qi) * KL;
                 int32_t* gl_x = p.list_x + (static_cast<int64_t>(part) * p.q + m0 + qi) * KL;
-                float nd;
-                int nx;
-                warp_fold_global<IPT>(cd, cx, has_list[qi] != 0, gl_d, gl_x, p.k, lane, nd, nx);
+                const radius_pair nr = warp_fold_global_call<IPT>(cd, cx, has_list[qi] != 0, gl_d, gl_x, p.k, lane);
                 if (lane == 0)
                 {
-                    sr_d[qi] = nd;
-                    sr_x[qi] = nx;
+                    sr_d[qi] = nr.d;
+                    sr_x[qi] = nr.x;
                     has_list[qi] = 1;
                     cnt[qi] = 0;
                 }
@@ -145,9 +196,11 @@ __global__ void __launch_bounds__(FT_THREADS, 2) fused_tiled_kernel(const tiled_
         }
     };
 
-    for (int64_t t = t_begin; t < t_end; ++t)
+    int stage = 0;
+    uint32_t parity = 0;
+    for (int t = t_begin; t < t_end; ++t)
     {
-        const int64_t n0 = t * FT_BN;
+        const int64_t n0 = static_cast<int64_t>(t) * FT_BN;
         float acc[8][8];
         float nrm[8];
 #pragma unroll
@@ -160,75 +213,74 @@ __global__ void __launch_bounds__(FT_THREADS, 2) fused_tiled_kernel(const tiled_
                 acc[i][j] = 0.0F;
             }
         }
-        float ra[8];
-        float rb[8];
-        ft_load8(p.queries, p.q, p.dim, m0 + lrow, lk, p.vec_in != 0, ra);
-        ft_load8(p.points, p.n, p.dim, n0 + lrow, lk, p.vec_in != 0, rb);
-        __syncthreads(); // the previous tile's readers of buffer 0 are done
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
+        for (int s = 0; s < nslab; ++s)
         {
-            As[0][lk + j][lrow] = ra[j];
-            Bs[0][lk + j][lrow] = rb[j];
-        }
-        __syncthreads();
-        int buf = 0;
-        for (int kt = 0; kt < ntk; ++kt)
-        {
-            if (kt + 1 < ntk)
+            // (a wait that runs out is reported through the status word; the block carries on
+            // so that every thread still reaches every barrier)
+            ok = ptx::mbar_wait_bounded(&full[stage], parity) && ok;
+            const float* Bsl = Bs + stage * FT_SLAB_FLOATS;
+            const float* Asl = As + s * FT_BK * FT_BM;
+            const int rows = p.dp - s * FT_BK < FT_BK ? p.dp - s * FT_BK : FT_BK;
+            for (int k4 = 0; k4 < rows; k4 += 4)
             {
-                ft_load8(p.queries, p.q, p.dim, m0 + lrow, (kt + 1) * FT_BK + lk, p.vec_in != 0, ra);
-                ft_load8(p.points, p.n, p.dim, n0 + lrow, (kt + 1) * FT_BK + lk, p.vec_in != 0, rb);
-            }
 #pragma unroll
-            for (int kk = 0; kk < FT_BK; ++kk)
-            {
-                const float4 a0 = *reinterpret_cast<const float4*>(&As[buf][kk][ty * 4]);
-                const float4 a1 = *reinterpret_cast<const float4*>(&As[buf][kk][64 + ty * 4]);
-                const float4 b0 = *reinterpret_cast<const float4*>(&Bs[buf][kk][tx * 4]);
-                const float4 b1 = *reinterpret_cast<const float4*>(&Bs[buf][kk][64 + tx * 4]);
-                const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-                const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
-                if constexpr (PARTIAL)
+                for (int kk = 0; kk < 4; ++kk)
                 {
+                    const float* ar = Asl + (k4 + kk) * FT_BM;
+                    const float* br = Bsl + (k4 + kk) * FT_BN;
+                    const float4 a0 = *reinterpret_cast<const float4*>(ar + ty * 4);
+                    const float4 a1 = *reinterpret_cast<const float4*>(ar + 64 + ty * 4);
+                    const float4 b0 = *reinterpret_cast<const float4*>(br + tx * 4);
+                    const float4 b1 = *reinterpret_cast<const float4*>(br + 64 + tx * 4);
+                    const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+                    const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
 #pragma unroll
-                    for (int j = 0; j < 8; ++j)
+                    for (int i = 0; i < 8; ++i)
                     {
-                        nrm[j] = fmaf(b[j], b[j], nrm[j]);
-                    }
-                }
 #pragma unroll
-                for (int i = 0; i < 8; ++i)
-                {
-#pragma unroll
-                    for (int j = 0; j < 8; ++j)
-                    {
-                        if constexpr (PARTIAL)
+                        for (int j = 0; j < 8; ++j)
                         {
-                            acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
-                        }
-                        else
-                        {
-                            const float diff = a[i] - b[j];
-                            acc[i][j] = fmaf(diff, diff, acc[i][j]);
+                            if constexpr (PARTIAL)
+                            {
+                                acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+                            }
+                            else
+                            {
+                                const float diff = a[i] - b[j];
+                                acc[i][j] = fmaf(diff, diff, acc[i][j]);
+                            }
                         }
                     }
                 }
             }
-            if (kt + 1 < ntk)
+            if (PARTIAL && s == nslab - 1)
             {
-#pragma unroll
-                for (int j = 0; j < 8; ++j)
-                {
-                    As[buf ^ 1][lk + j][lrow] = ra[j];
-                    Bs[buf ^ 1][lk + j][lrow] = rb[j];
-                }
+                // squared norms of this thread's eight points: the row after the coordinates
+                const float* nr = Bsl + rows * FT_BN;
+                const float4 n0v = *reinterpret_cast<const float4*>(nr + tx * 4);
+                const float4 n1v = *reinterpret_cast<const float4*>(nr + 64 + tx * 4);
+                nrm[0] = n0v.x;
+                nrm[1] = n0v.y;
+                nrm[2] = n0v.z;
+                nrm[3] = n0v.w;
+                nrm[4] = n1v.x;
+                nrm[5] = n1v.y;
+                nrm[6] = n1v.z;
+                nrm[7] = n1v.w;
             }
-            __syncthreads();
-            buf ^= 1;
+            __syncthreads(); // every thread is done with this stage: it can be refilled
+            if (tid == 0 && issued < total)
+            {
+                issue_slab(stage);
+            }
+            if (++stage == FT_STAGES)
+            {
+                stage = 0;
+                parity ^= 1U;
+            }
         }
 
-        // ---- filter the 8 x 8 distances of this thread -------------------------------------
+    // ---- filter the 8 x 8 distances of this thread -------------------------------------
         unsigned long long pending = 0;
         const int ncols = p.n - n0 < FT_BN ? static_cast<int>(p.n - n0) : FT_BN; // valid columns of this tile
         const int c_lo = tx * 4;       // this thread's columns: c_lo .. c_lo + 3 and 64 + c_lo .. + 3
@@ -334,25 +386,30 @@ __global__ void __launch_bounds__(FT_THREADS, 2) fused_tiled_kernel(const tiled_
             const int cx = lane < valid ? buf_x[qi][lane] : PAD_IDX;
             float* gl_d = p.list_d + (static_cast<int64_t>(part) * p.q + m0 + qi) * KL;
             int32_t* gl_x = p.list_x + (static_cast<int64_t>(part) * p.q + m0 + qi) * KL;
-            float nd;
-            int nx;
-            warp_fold_global<IPT>(cd, cx, has_list[qi] != 0, gl_d, gl_x, p.k, lane, nd, nx);
+            warp_fold_global_call<IPT>(cd, cx, has_list[qi] != 0, gl_d, gl_x, p.k, lane);
         }
         __syncwarp();
     }
+    if (!ok)
+    {
+        atomicOr(p.status, DEVICE_STATUS_TIMEOUT);
+    }
 }
+
 
 struct tiled_layout
 {
     int kl;
     int parts;
-    size_t off_ld, off_lx, total;
+    int dp;
+    size_t off_pimg, off_qimg, off_ld, off_lx, total;
 };
 
-tiled_layout tiled_layout_of(int64_t n, int64_t q, int k)
+tiled_layout tiled_layout_of(int64_t n, int64_t q, int dim, int k)
 {
     tiled_layout l{};
     l.kl = k <= 32 ? 32 : (k <= 64 ? 64 : (k <= 128 ? 128 : 256));
+    l.dp = (dim + 3) / 4 * 4;
     const int64_t nqb = (q + FT_BM - 1) / FT_BM;
     const int64_t tiles = (n + FT_BN - 1) / FT_BN;
     // two blocks fit an SM; split the database only when the query tiles cannot fill them
@@ -360,16 +417,25 @@ tiled_layout tiled_layout_of(int64_t n, int64_t q, int k)
     const int64_t want = 4 * nqb >= 3 * slots ? 1 : (slots + nqb - 1) / nqb;
     l.parts = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(want, std::max<int64_t>(1, tiles / 32))));
     const size_t lists = static_cast<size_t>(l.parts) * static_cast<size_t>(q) * l.kl;
-    l.off_ld = 0;
-    l.off_lx = (lists * 4 + 255) & ~static_cast<size_t>(255);
-    l.total = l.off_lx + ((lists * 4 + 255) & ~static_cast<size_t>(255));
+    auto align256 = [](size_t v) { return (v + 255) & ~static_cast<size_t>(255); };
+    l.off_pimg = 0;
+    l.off_qimg = align256(static_cast<size_t>(tiles) * (l.dp + 1) * FT_BN * 4);
+    l.off_ld = l.off_qimg + align256(static_cast<size_t>(nqb) * (l.dp + 1) * FT_BM * 4);
+    l.off_lx = l.off_ld + align256(lists * 4);
+    l.total = l.off_lx + align256(lists * 4);
     return l;
+}
+
+size_t tiled_smem_bytes(int dp)
+{
+    return sizeof(float) * (static_cast<size_t>(FT_STAGES) * FT_SLAB_FLOATS + static_cast<size_t>(dp) * FT_BM +
+                            2 * FT_BM * FT_CAP);
 }
 
 template <int IPT>
 int launch_tiled(const tiled_params& p, int mode, int64_t grid, cudaStream_t stream)
 {
-    constexpr size_t smem = sizeof(float) * (4 * FT_BK * FT_PAD + 2 * FT_BM * FT_CAP);
+    const size_t smem = tiled_smem_bytes(p.dp);
     if (mode == BITSKNN_L2_PARTIAL)
     {
         auto kernel = fused_tiled_kernel<IPT, true>;
@@ -388,41 +454,63 @@ int launch_tiled(const tiled_params& p, int mode, int64_t grid, cudaStream_t str
 
 } // namespace
 
-size_t fused_tiled_workspace_bytes(int64_t n, int64_t q, int k)
+bool fused_tiled_supports(int dim) { return dim >= 1 && dim <= FT_MAX_DIM; }
+
+size_t fused_tiled_workspace_bytes(int64_t n, int64_t q, int dim, int k)
 {
-    if (n <= 0 || q <= 0 || k <= 0)
+    if (n <= 0 || q <= 0 || k <= 0 || !fused_tiled_supports(dim))
     {
         return 0;
     }
-    return tiled_layout_of(n, q, k).total;
+    return tiled_layout_of(n, q, dim, k).total;
 }
 
 int fused_tiled_launch(const float* points, const float* queries, int64_t n, int64_t q, int dim, int k, int mode,
                        int32_t index_base, float* out_dist, int32_t* out_idx, void* workspace, size_t workspace_bytes,
                        cudaStream_t stream)
 {
-    const tiled_layout l = tiled_layout_of(n, q, k);
+    if (!fused_tiled_supports(dim))
+    {
+        return fail(BITSKNN_ERR_UNSUPPORTED_DIM, "Unsupported dimension: %d (the tiled fused kernel takes up to %d)", dim,
+                    FT_MAX_DIM);
+    }
+    if (n / FT_BN * ((dim + FT_BK - 1) / FT_BK) >= (int64_t{1} << 31) - FT_BN)
+    {
+        return fail(BITSKNN_ERR_INVALID_ARGUMENT, "the tiled fused kernel counts up to 2^31 slabs of 16 coordinates x 128 points");
+    }
+    const tiled_layout l = tiled_layout_of(n, q, dim, k);
     if (workspace == nullptr || workspace_bytes < l.total || (reinterpret_cast<uintptr_t>(workspace) & 255U) != 0)
     {
         return fail(BITSKNN_ERR_WORKSPACE, "workspace of %zu bytes (256-byte aligned) needed, %zu given", l.total,
                     workspace_bytes);
     }
     auto* ws = static_cast<unsigned char*>(workspace);
+    float* pimg = reinterpret_cast<float*>(ws + l.off_pimg);
+    float* qimg = reinterpret_cast<float*>(ws + l.off_qimg);
+    const int64_t tiles = (n + FT_BN - 1) / FT_BN;
+    const int64_t nqb = (q + FT_BM - 1) / FT_BM;
+    ft_image_kernel<<<static_cast<unsigned>(tiles), FT_BN, 0, stream>>>(points, n, dim, l.dp, pimg);
+    ft_image_kernel<<<static_cast<unsigned>(nqb), FT_BM, 0, stream>>>(queries, q, dim, l.dp, qimg);
+    BITSKNN_CUDA_TRY(cudaGetLastError());
+
     tiled_params p{};
-    p.points = points;
-    p.queries = queries;
+    p.pimg = pimg;
+    p.qimg = qimg;
     p.n = n;
     p.q = q;
-    p.dim = dim;
+    p.dp = l.dp;
     p.k = k;
     p.index_base = index_base;
     p.parts = l.parts;
-    p.tiles = (n + FT_BN - 1) / FT_BN;
+    p.tiles = tiles;
     p.list_d = reinterpret_cast<float*>(ws + l.off_ld);
     p.list_x = reinterpret_cast<int32_t*>(ws + l.off_lx);
-    p.vec_in = (dim % 4 == 0) && ((reinterpret_cast<uintptr_t>(points) & 15U) == 0) &&
-               ((reinterpret_cast<uintptr_t>(queries) & 15U) == 0);
-    const int64_t grid = ((q + FT_BM - 1) / FT_BM) * l.parts;
+    p.status = device_status_word();
+    if (p.status == nullptr)
+    {
+        return fail(BITSKNN_ERR_CUDA, "CUDA error. cannot resolve the device status word");
+    }
+    const int64_t grid = nqb * l.parts;
     int rc;
     switch (l.kl)
     {
