@@ -8,10 +8,12 @@
 // include/bits/topk/singlepass/fused_cache_kernel_structs.cuh:622-630).  The consumer compares
 // raw accumulators against  -bound / 2: one max-tree and one vote per 16 columns.
 //
-// Block = 320 threads on one SM, 128 queries (the TMEM lanes):
+// Block = 352 threads on one SM, 128 queries (the TMEM lanes):
 //   warp 8   TMA producer (query image once, point image K blocks through a ring of stages)
-//   warp 9   TMEM allocation (4 accumulators of 128 columns) and tcgen05.mma issue.  One MMA
-//            instruction costs about the same time for 128 and for 256 points, so whenever the
+//   warps 9, 10  tcgen05.mma issue, the two taking MMAs in turn (warp 9 also allocates the
+//            tensor memory: 4 accumulators of 128 columns).  The tensor pipe needs about 64
+//            clocks for a 128 x 128 x 16 MMA and 128 for 128 x 256 x 16, but the issuing thread
+//            spends more than 64 on one instruction with its barrier traffic, so whenever the
 //            ring fits, an MMA covers 256 points and fills two neighbouring accumulators, one per
 //            consumer group (NMMA = 256); long vectors fall back to 128 points per MMA.
 //   warps 0-7  consumers, two groups of four.  Group g takes every other 128-point tile (each
@@ -45,7 +47,7 @@ namespace bitsknn
 namespace
 {
 
-constexpr int FT_THREADS = 320;
+constexpr int FT_THREADS = 352;
 constexpr int FT_PRODUCER_WARP = 8;
 constexpr int FT_MMA_WARP = 9;
 constexpr int FT_TMEM_COLS = 512; // four 128-column accumulators: each consumer group owns two
@@ -102,7 +104,8 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
     float* buf_d = hlf + 2 * TILE_M;                      // [8 warps][CAP][32 lanes]
     int* buf_x = reinterpret_cast<int*>(buf_d + 8 * CAP * 32);
 
-    __shared__ uint2 a_tab[MAX_KB * 4]; // written and read by the MMA-issuing thread alone
+    __shared__ uint2 a_tab_both[2][MAX_KB * 4]; // one table per MMA-issuing thread
+    __shared__ volatile int fills_seen[2];      // ring fills each issuing thread has seen complete
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
@@ -130,6 +133,10 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
             ptx::mbar_init(&acc_empty[a], 128);
         }
         ptx::mbar_init_fence();
+    }
+    if (tid < 2)
+    {
+        fills_seen[tid] = 0;
     }
     if (tid < 2 * TILE_M)
     {
@@ -162,7 +169,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
             {
                 for (int kb = 0; kb < p.nkb; ++kb)
                 {
-                    if (!ptx::mbar_wait_bounded(&empty_b[s], ph ^ 1U))
+                    if (!ptx::mbar_wait_bounded_spin(&empty_b[s], ph ^ 1U))
                     {
                         ok = false;
                         break;
@@ -179,8 +186,13 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
             }
         }
     }
-    else if (warp == FT_MMA_WARP)
+    else if (warp == FT_MMA_WARP || warp == FT_MMA_WARP + 1)
     {
+        // Two issuing threads take the MMAs (tiles, or pairs of tiles) in turn: tcgen05.mma holds
+        // its issuing thread for about the time the tensor pipe needs, so one thread's barrier
+        // waits and commits would leave the pipe idle; with two, the other one's MMAs fill it.
+        const int issuer = warp - FT_MMA_WARP;
+        uint2* a_tab = a_tab_both[issuer];
         if (lane == 0 && t_begin < t_end)
         {
             constexpr uint32_t idesc = tc::instr_desc(BF16 ? 1U : 2U, TILE_M, NMMA);
@@ -215,18 +227,53 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
                 }
                 a_tab[st] = e;
             }
-            ok = ptx::mbar_wait_bounded(a_full, 0);
+            ok = ptx::mbar_wait_bounded_spin(a_full, 0);
             int s = 0;
             uint32_t ph = 0;
             int64_t lt = 0;
-            for (int64_t t = t_begin; t < t_end && ok; t += NT, lt += NT)
+            int turn = 0;
+            int fills_before = 0; // ring fills that belong to earlier MMAs
+            for (int64_t t = t_begin; t < t_end && ok; t += NT, lt += NT, turn ^= 1, fills_before += p.nkb)
             {
+                if (turn != issuer)
+                {
+                    // the other thread's MMA: step over its stages of the ring
+                    for (int kb = 0; kb < p.nkb; ++kb)
+                    {
+                        if (++s == p.stages)
+                        {
+                            s = 0;
+                            ph ^= 1U;
+                        }
+                    }
+                    continue;
+                }
+                // A parity wait on a ring stage is only meaningful once the stage's previous fill
+                // has completed.  This thread has not watched the fills of the other thread's
+                // MMAs, so it first lets the other thread report them (they were requested
+                // before this MMA's fills, so this hardly ever spins).
+                if (fills_before > 0)
+                {
+                    uint32_t polls = 0;
+                    while (fills_seen[issuer ^ 1] < fills_before)
+                    {
+                        if (++polls > (1U << 26))
+                        {
+                            ok = false;
+                            break;
+                        }
+                    }
+                    if (!ok)
+                    {
+                        break;
+                    }
+                }
                 // tile lt goes to accumulator lt % 4 (consumer group lt % 2), used for the (lt / 4)-th
                 // time; a 256-column MMA fills two neighbouring accumulators (one per group) at once
                 const int a = static_cast<int>(lt & (FT_ACCS - 1));
                 const uint32_t aph = static_cast<uint32_t>((lt >> 2) & 1);
-                if (!ptx::mbar_wait_bounded(&acc_empty[a], aph ^ 1U) ||
-                    (NT == 2 && !ptx::mbar_wait_bounded(&acc_empty[a + 1], aph ^ 1U)))
+                if (!ptx::mbar_wait_bounded_spin(&acc_empty[a], aph ^ 1U) ||
+                    (NT == 2 && !ptx::mbar_wait_bounded_spin(&acc_empty[a + 1], aph ^ 1U)))
                 {
                     ok = false;
                     break;
@@ -243,7 +290,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
                     {
                         a_words[ks] = a_tab[kb * 4 + ks];
                     }
-                    if (!ptx::mbar_wait_bounded(&full_b[s], ph))
+                    if (!ptx::mbar_wait_bounded_spin(&full_b[s], ph))
                     {
                         ok = false;
                         break;
@@ -263,6 +310,10 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
                     {
                         s = 0;
                         ph ^= 1U;
+                    }
+                    if (kb == p.nkb - 1)
+                    {
+                        fills_seen[issuer] = fills_before + p.nkb;
                     }
                 }
                 tc::mma_commit(&acc_full[a]);
@@ -395,7 +446,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
             }
             const int a = static_cast<int>(lt & (FT_ACCS - 1));
             // (made warp-uniform: the lanes poll independently)
-            if (!__all_sync(FULL_MASK, ptx::mbar_wait_bounded(&acc_full[a], static_cast<uint32_t>((lt >> 2) & 1))))
+            if (!__all_sync(FULL_MASK, ptx::mbar_wait_bounded_spin(&acc_full[a], static_cast<uint32_t>((lt >> 2) & 1))))
             {
                 ok = false;
                 break;

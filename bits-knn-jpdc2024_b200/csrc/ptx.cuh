@@ -62,6 +62,20 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     return false;
 }
 
+// The same without the back-off, for waits on a pipeline's critical path (a sleeping waiter
+// notices a completed phase late, which a short ring cannot absorb).
+__device__ __forceinline__ bool mbar_wait_bounded_spin(uint64_t* bar, uint32_t parity, uint32_t limit = (1U << 26))
+{
+    for (uint32_t i = 0; i < limit; ++i)
+    {
+        if (mbar_try_wait(bar, parity))
+        {
+            return true;
+        }
+    }
+    return false;
+}
+
 // 1-D bulk copy global -> shared, completion counted in bytes on `bar`.
 // dst, src 16-byte aligned; bytes a multiple of 16.  No multicast.
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar)
