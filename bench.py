@@ -12,6 +12,8 @@ its local top-k, the candidates are all-gathered over NCCL and merged on every r
 The JSON line carries: `value` (distances/s with the matrix resident in HBM), `e2e` (same
 metric through the C ABI with HOST buffers: pinned host -> device copy of the matrix, the
 selection, and the device -> host copy of the result, all inside the timed region),
+`e2e_knn` (the reference binary's own flow: host points and queries -> device, distance matrix
+made on the device, selection, result -> host),
 `roofline` (algorithmic bytes / CUDA-event kernel time against the measured HBM peak),
 `cpu_baseline` (the CPU port of the reference's OpenMP heap selection, timed on this host)
 and `sweep` (other k and the adversarial descending-row input, kernel time only).
@@ -259,9 +261,11 @@ def run_profile_case(name):
     torch.cuda.set_device(dev)
     gen = torch.Generator(device=dev).manual_seed(42)
     dim, k = 64, 128
-    if name in ("fused_tc", "fused_fp32"):
+    if name == "fused_tc_small":
+        dim, k = 16, 16                                 # the consumer-bound end: few MMAs, few candidates
+    if name in ("fused_tc", "fused_tc_small", "fused_fp32"):
         n, q = 1 << 18, 148 * 128                       # one query tile per SM
-        mode = bk.L2_BF16 if name == "fused_tc" else bk.L2_PARTIAL
+        mode = bk.L2_PARTIAL if name == "fused_fp32" else bk.L2_BF16
         if name == "fused_fp32":
             q = 148 * 2 * 128                           # two 128-query blocks per SM
         points = torch.rand((n, dim), generator=gen, device=dev)
@@ -348,7 +352,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--rows", type=int, default=Q, help="rows of the matrix (smaller = profiling case)")
-    ap.add_argument("--profile-case", default=None, choices=["fused_tc", "l2_tc", "fused_fp32", "l2_fp32"],
+    ap.add_argument("--profile-case", default=None, choices=["fused_tc", "fused_tc_small", "l2_tc", "fused_fp32", "l2_fp32"],
                     help="run a few launches of one small case of that kernel and exit (for ncu captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "native" else args.warmup
@@ -459,6 +463,7 @@ def main():
 
     # ---- sweep: other k, and the adversarial descending rows (kernel time only) -------------
     sweep = None
+    desc_host = None
     if not args.no_sweep and world == 1:
         sweep = {}
         desc = None
@@ -484,6 +489,8 @@ def main():
                 sweep[f"{order}_k{kk}"] = {"ms": ms, "distances_per_s": q * n / (ms * 1e-3),
                                            "frac_of_hbm_peak": (4.0 * q * n + 8.0 * q * kk) / (ms * 1e-3) / 1e9 / peak_gbs}
             del src
+        # kept on the host for the same-box run of the reference's kernel on the adversarial rows
+        desc_host = desc.cpu().numpy() if (desc is not None and not args.no_cpu and not args.no_e2e) else None
         del desc
         torch.cuda.empty_cache()
         # ablation: the same kernel without its radius filter (the reference's partial-bitonic-regs):
@@ -507,6 +514,7 @@ def main():
 
     # ---- end to end through the C ABI from host buffers (`e2e`) ----------------------------
     e2e = None
+    e2e_knn = None
     host = None
     if not args.no_e2e:
         host = torch.empty((q, n), dtype=torch.float32).pin_memory()
@@ -534,8 +542,42 @@ def main():
         barrier()
         e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / e2e_steps
         e2e = {"value": q * n * world / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms, "steps": e2e_steps,
-               "h2d_bytes_per_step": 4 * q * n, "d2h_bytes_per_step": 8 * q * k}
-        del staging
+               "h2d_bytes_per_step": 4 * q * n, "d2h_bytes_per_step": 8 * q * k,
+               "what": "pinned host distance matrix -> device, selection, result -> host (PCIe-bound: the matrix "
+                       "is 4 GiB per step)"}
+
+        # The flow of the reference's `knn` binary (prepare / distances / selection / finish,
+        # src/main.cpp): the VECTORS come from the host every step, the distance matrix is made on
+        # the device (exact FP32 kernel) and never crosses PCIe.
+        e2e_dim = 32
+        hp = torch.rand((n, e2e_dim), dtype=torch.float32).pin_memory()
+        hq = torch.rand((q, e2e_dim), dtype=torch.float32).pin_memory()
+        dp = torch.empty((n, e2e_dim), dtype=torch.float32, device=dev)
+        dq = torch.empty((q, e2e_dim), dtype=torch.float32, device=dev)
+
+        def knn_step():
+            dp.copy_(hp, non_blocking=True)
+            dq.copy_(hq, non_blocking=True)
+            bk.l2(dp, dq, mode=bk.L2_EXACT, out=staging)
+            step(staging)
+            host_d.copy_(res_d, non_blocking=True)
+            host_i.copy_(res_i, non_blocking=True)
+
+        for _ in range(2):
+            knn_step()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(e2e_steps):
+            knn_step()
+        e1.record()
+        barrier()
+        knn_ms = max_over_ranks(e0.elapsed_time(e1)) / e2e_steps
+        e2e_knn = {"value": q * n * world / (knn_ms * 1e-3), "unit": UNIT, "ms_per_step": knn_ms, "steps": e2e_steps,
+                   "h2d_bytes_per_step": 4 * e2e_dim * (n + q), "d2h_bytes_per_step": 8 * q * k, "dim": e2e_dim,
+                   "what": "pinned host points and queries -> device, exact FP32 distance matrix on the device, "
+                           "selection, result -> host: the reference's own end-to-end flow"}
+        del staging, dp, dq, hp, hq
 
     # ---- same-box comparator: the reference's own `bits-prefetch` kernel, recompiled ---------
     reference_gpu = None
@@ -552,6 +594,10 @@ def main():
                                          "(block 256, batch 13: its tuned H100 shape), same matrix, host-timed "
                                          "selection() like its main loop, fastest of 3",
                                  "uniform": ref_sel}
+                if desc_host is not None:
+                    _, _, sec = ref_select.select("bits-prefetch", desc_host, k, block_size=256, batch=13, repeats=2)
+                    reference_gpu["descending"] = {f"k{k}": {"ms": sec * 1e3, "distances_per_s": q * n / sec}}
+                    desc_host = None
         except Exception as err:  # the comparator is optional
             reference_gpu = {"unavailable": str(err)}
 
@@ -584,7 +630,7 @@ def main():
                 "config": {"workload": f"k-selection sweep shape: q={q} x n=2^20 float32 Uniform[0,1) per GPU, k={k}",
                            "q": q, "n": n, "k": k, "sharding": "database columns" if world > 1 else "none",
                            "l2_policy": "input (4 GiB per GPU) is larger than L2; no flush needed"},
-                "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
+                "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "e2e_knn": e2e_knn,
                 "gpu_launches": launches_per_step * args.steps, "clocks": clocks}
         if sweep is not None:
             line["sweep"] = sweep

@@ -255,9 +255,10 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
                 if (fills_before > 0)
                 {
                     uint32_t polls = 0;
+                    const long long deadline = clock64() + ptx::WAIT_CLOCK_LIMIT;
                     while (fills_seen[issuer ^ 1] < fills_before)
                     {
-                        if (++polls > (1U << 26))
+                        if ((++polls & 1023U) == 0 && clock64() > deadline)
                         {
                             ok = false;
                             break;
