@@ -332,7 +332,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
         const int qrow = w4 * 32 + lane;              // query of this thread inside the tile
         const int64_t gq = qb * TILE_M + qrow;        // global query
         const bool live = gq < p.q;
-        float* my_buf_d = buf_d + warp * (CAP * 32);  // slot s of lane l at [s * 32 + l]
+        float* my_buf_d = buf_d + warp * (CAP * 32);  // slot s of lane l at [s * 32 + (l + s) % 32]
         int* my_buf_x = buf_x + warp * (CAP * 32);
         const int64_t list_id = static_cast<int64_t>(part) * 2 + group;
         const uint32_t lane_base = static_cast<uint32_t>(w4 * 32) << 16;
@@ -365,8 +365,9 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
                 float* gl_d = p.list_d + (list_id * p.q + gq_l) * KL;
                 int32_t* gl_x = p.list_x + (list_id * p.q + gq_l) * KL;
                 // candidates: slot `lane` of query L's buffer
-                const float cd = lane < cnt_l ? my_buf_d[lane * 32 + L] : INFINITY;
-                const int cx = lane < cnt_l ? my_buf_x[lane * 32 + L] : PAD_IDX;
+                // (slot s of query L sits in bank (L + s) % 32: the 32 slots come from 32 banks)
+                const float cd = lane < cnt_l ? my_buf_d[lane * 32 + ((L + lane) & 31)] : INFINITY;
+                const int cx = lane < cnt_l ? my_buf_x[lane * 32 + ((L + lane) & 31)] : PAD_IDX;
                 const radius_pair nr = warp_fold_global_call<IPT>(cd, cx, has_l, gl_d, gl_x, p.k, lane);
                 const float nd = nr.d;
                 const int nx = nr.x;
@@ -416,8 +417,8 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
                             const int idx = p.index_base + static_cast<int>(col0 + j);
                             if (d <= r_part && pair_lt(d, idx, r_d, r_x))
                             {
-                                my_buf_d[cnt * 32 + lane] = d;
-                                my_buf_x[cnt * 32 + lane] = idx;
+                                my_buf_d[cnt * 32 + ((lane + cnt) & 31)] = d;
+                                my_buf_x[cnt * 32 + ((lane + cnt) & 31)] = idx;
                                 ++cnt;
                             }
                         }
