@@ -30,7 +30,7 @@ std::mutex g_tuning_mutex;
 tuning_entry g_tuning[] = {
     {"select.stage_bytes", 0, 0, 65536},
     {"select.stages", 0, 0, 8},
-    {"select.merge_at", 50, 1, 100},
+    {"select.merge_at", 0, 0, 100},
     {"select.auto_split", 1, 0, 1},
     {"select.wide_block", 1, 0, 1},
     {"select.filter", 1, 0, 1},

@@ -631,7 +631,13 @@ template <int THREADS, int IPT>
 int launch_select(select_params p, int64_t vrows, cudaStream_t stream)
 {
     constexpr int L = THREADS * IPT;
-    const int merge_pct = tuning_value("select.merge_at", 50);
+    // 0 = automatic: half-full buffers for lists of up to 256 pairs, three-quarter-full ones for
+    // longer lists, whose folds cost more against what an earlier tightening of the radius saves
+    int merge_pct = tuning_value("select.merge_at", 0);
+    if (merge_pct <= 0)
+    {
+        merge_pct = L <= 256 ? 50 : 75;
+    }
     p.merge_at = std::max(1, (L * merge_pct) / 100);
     // a stage is a whole number of 4-vectors per thread
     p.stage_floats = std::max(4 * THREADS, (p.stage_floats / (4 * THREADS)) * (4 * THREADS));

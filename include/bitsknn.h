@@ -66,8 +66,8 @@ int bitsknn_selftest_bounded_wait(bitsknn_stream_t stream);
  *                         0 = automatic, the default)
  *   "select.stages"       stages in the ring (2..8; 0 = automatic, the default)
  *   "select.merge_at"     merge the candidate buffer when it holds at least this percentage
- *                         of its capacity (1..100; default 50; 100 = only when full, like the
- *                         reference)
+ *                         of its capacity (1..100; 100 = only when full, like the reference;
+ *                         0 = automatic, the default: 50 for lists of up to 256 pairs, else 75)
  *   "select.unroll"       128-bit vectors per thread examined under one warp vote (0 = automatic,
  *                         2 or 4)
  *   "select.wide_block"   1 = 512-thread blocks for k > 256 (default), 0 = 256-thread blocks
