@@ -10,12 +10,10 @@
 //
 // Block = 352 threads on one SM, 128 queries (the TMEM lanes):
 //   warp 8   TMA producer (query image once, point image K blocks through a ring of stages)
-//   warps 9, 10  tcgen05.mma issue, the two taking MMAs in turn (warp 9 also allocates the
-//            tensor memory: 4 accumulators of 128 columns).  The tensor pipe needs about 64
-//            clocks for a 128 x 128 x 16 MMA and 128 for 128 x 256 x 16, but the issuing thread
-//            spends more than 64 on one instruction with its barrier traffic, so whenever the
-//            ring fits, an MMA covers 256 points and fills two neighbouring accumulators, one per
-//            consumer group (NMMA = 256); long vectors fall back to 128 points per MMA.
+//   warps 9, 10  tcgen05.mma issue, the two taking MMAs in turn (tc_pipeline.cuh; warp 9 also
+//            allocates the tensor memory: 4 accumulators of 128 columns).  Whenever the ring fits,
+//            an MMA covers 256 points and fills two neighbouring accumulators, one per consumer
+//            group (NMMA = 256); long vectors fall back to 128 points per MMA.
 //   warps 0-7  consumers, two groups of four.  Group g takes every other 128-point tile (each
 //            group alternates between two accumulators, so the MMAs run ahead of it);
 //            thread t of a group is query 32 * (warp % 4) + t and reads its row with
@@ -39,6 +37,7 @@
 #include "sortnet.cuh"
 #include "tc.cuh"
 #include "tc_host.cuh"
+#include "tc_pipeline.cuh"
 #include "warpfold.cuh"
 
 namespace bitsknn
@@ -50,8 +49,7 @@ namespace
 constexpr int FT_THREADS = 352;
 constexpr int FT_PRODUCER_WARP = 8;
 constexpr int FT_MMA_WARP = 9;
-constexpr int FT_TMEM_COLS = 512; // four 128-column accumulators: each consumer group owns two
-constexpr int FT_ACCS = 4;
+constexpr int FT_ACCS = tcpipe::ACCS; // four 128-column accumulators: each consumer group owns two
 constexpr int CAP = 32; // candidate slots per (group, query)
 
 struct ftc_params
@@ -83,29 +81,32 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
     fused_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_p, const ftc_params p)
 {
     constexpr int KL = 32 * IPT;
-    constexpr int KB_ELEMS = BF16 ? 64 : 32;
-    constexpr int K_STEP_BYTES = 32;
     constexpr int NT = NMMA / TILE_N;            // 128-column tiles per MMA (1 or 2)
     constexpr int STAGE_B = NT * STAGE_BYTES;    // one K block of NMMA points
 
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    unsigned char* a_tiles = smem;
-    unsigned char* b_ring = a_tiles + static_cast<size_t>(p.nkb) * STAGE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(b_ring + static_cast<size_t>(p.stages) * STAGE_B);
-    uint64_t* a_full = bars;
-    uint64_t* full_b = bars + 1;
-    uint64_t* empty_b = full_b + 16;
-    uint64_t* acc_full = empty_b + 16;
-    uint64_t* acc_empty = acc_full + FT_ACCS;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + FT_ACCS);
+    __shared__ uint2 a_tab_both[2][MAX_KB * 4]; // one descriptor table per MMA-issuing thread
+    __shared__ volatile int fills_seen[2];      // ring fills each issuing thread has seen complete
+    tcpipe::state pipe;
+    pipe.a_tiles = smem;
+    pipe.b_ring = pipe.a_tiles + static_cast<size_t>(p.nkb) * STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(pipe.b_ring + static_cast<size_t>(p.stages) * STAGE_B);
+    pipe.a_full = bars;
+    pipe.full_b = bars + 1;
+    pipe.empty_b = pipe.full_b + 16;
+    pipe.acc_full = pipe.empty_b + 16;
+    pipe.acc_empty = pipe.acc_full + FT_ACCS;
+    pipe.a_tab = &a_tab_both[0][0];
+    pipe.fills_seen = fills_seen;
+    uint64_t* acc_full = pipe.acc_full;
+    uint64_t* acc_empty = pipe.acc_empty;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pipe.acc_empty + FT_ACCS);
     float* rad = reinterpret_cast<float*>(bars + 64);     // [2][128] radius distance per group and query
     float* hlf = rad + 2 * TILE_M;                        // [2][128] distance of list entry ceil(k / 2) - 1
     float* buf_d = hlf + 2 * TILE_M;                      // [8 warps][CAP][32 lanes]
     int* buf_x = reinterpret_cast<int*>(buf_d + 8 * CAP * 32);
-
-    __shared__ uint2 a_tab_both[2][MAX_KB * 4]; // one table per MMA-issuing thread
-    __shared__ volatile int fills_seen[2];      // ring fills each issuing thread has seen complete
+    const tcpipe::shape shape{p.nkb, p.nsteps, p.hs, p.stages};
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
@@ -121,22 +122,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
 
     if (tid == 0)
     {
-        ptx::mbar_init(a_full, 1);
-        for (int s = 0; s < p.stages; ++s)
-        {
-            ptx::mbar_init(&full_b[s], 1);
-            ptx::mbar_init(&empty_b[s], 1);
-        }
-        for (int a = 0; a < FT_ACCS; ++a)
-        {
-            ptx::mbar_init(&acc_full[a], 1);
-            ptx::mbar_init(&acc_empty[a], 128);
-        }
-        ptx::mbar_init_fence();
-    }
-    if (tid < 2)
-    {
-        fills_seen[tid] = 0;
+        tcpipe::init_barriers(pipe, p.stages);
     }
     if (tid < 2 * TILE_M)
     {
@@ -145,7 +131,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
     }
     if (warp == FT_MMA_WARP)
     {
-        tc::tmem_alloc(tmem_slot, FT_TMEM_COLS);
+        tc::tmem_alloc(tmem_slot, tcpipe::TMEM_COLS);
     }
     tc::fence_before_sync();
     __syncthreads();
@@ -157,172 +143,14 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
     {
         if (lane == 0 && t_begin < t_end)
         {
-            ptx::mbar_expect_tx(a_full, static_cast<uint32_t>(p.nkb) * STAGE_BYTES);
-            for (int kb = 0; kb < p.nkb; ++kb)
-            {
-                tc::tma_load_2d(a_tiles + static_cast<size_t>(kb) * STAGE_BYTES, &map_q, kb * KB_ELEMS,
-                                static_cast<int>(qb * TILE_M), a_full);
-            }
-            int s = 0;
-            uint32_t ph = 0;
-            for (int64_t t = t_begin; t < t_end && ok; t += NT)
-            {
-                for (int kb = 0; kb < p.nkb; ++kb)
-                {
-                    if (!ptx::mbar_wait_bounded_spin(&empty_b[s], ph ^ 1U))
-                    {
-                        ok = false;
-                        break;
-                    }
-                    ptx::mbar_expect_tx(&full_b[s], STAGE_B);
-                    tc::tma_load_2d(b_ring + static_cast<size_t>(s) * STAGE_B, &map_p, kb * KB_ELEMS,
-                                    static_cast<int>(t * TILE_N), &full_b[s]);
-                    if (++s == p.stages)
-                    {
-                        s = 0;
-                        ph ^= 1U;
-                    }
-                }
-            }
+            ok = tcpipe::producer<BF16, NMMA>(pipe, shape, &map_q, &map_p, qb * TILE_M, t_begin, t_end);
         }
     }
     else if (warp == FT_MMA_WARP || warp == FT_MMA_WARP + 1)
     {
-        // Two issuing threads take the MMAs (tiles, or pairs of tiles) in turn: tcgen05.mma holds
-        // its issuing thread for about the time the tensor pipe needs, so one thread's barrier
-        // waits and commits would leave the pipe idle; with two, the other one's MMAs fill it.
-        const int issuer = warp - FT_MMA_WARP;
-        uint2* a_tab = a_tab_both[issuer];
         if (lane == 0 && t_begin < t_end)
         {
-            constexpr uint32_t idesc = tc::instr_desc(BF16 ? 1U : 2U, TILE_M, NMMA);
-            // Low descriptor words of the query steps that meet step st of the point image (0: none).
-            // Plain image and norm step: step st itself.  Compact split image: a hi step of the
-            // points meets the queries' hi and lo steps, a lo step the queries' hi step.
-            const uint64_t a_desc0 = tc::smem_desc_sw128(a_tiles);
-            const uint32_t desc_hi = static_cast<uint32_t>(a_desc0 >> 32);
-            const uint32_t b_lo0 = static_cast<uint32_t>(tc::smem_desc_sw128(b_ring));
-            auto a_step = [&](int st) {
-                return static_cast<uint32_t>(a_desc0) + static_cast<uint32_t>(st >> 2) * (STAGE_BYTES >> 4) +
-                       static_cast<uint32_t>((st & 3) * (K_STEP_BYTES >> 4));
-            };
-            for (int st = 0; st < MAX_KB * 4; ++st)
-            {
-                uint2 e = make_uint2(0U, 0U);
-                if (st < p.nsteps)
-                {
-                    if (p.hs == 0 || st >= 2 * p.hs)
-                    {
-                        e.x = a_step(st);
-                    }
-                    else if (st < p.hs)
-                    {
-                        e.x = a_step(st);
-                        e.y = a_step(p.hs + st);
-                    }
-                    else
-                    {
-                        e.x = a_step(st - p.hs);
-                    }
-                }
-                a_tab[st] = e;
-            }
-            ok = ptx::mbar_wait_bounded_spin(a_full, 0);
-            int s = 0;
-            uint32_t ph = 0;
-            int64_t lt = 0;
-            int turn = 0;
-            int fills_before = 0; // ring fills that belong to earlier MMAs
-            for (int64_t t = t_begin; t < t_end && ok; t += NT, lt += NT, turn ^= 1, fills_before += p.nkb)
-            {
-                if (turn != issuer)
-                {
-                    // the other thread's MMA: step over its stages of the ring
-                    for (int kb = 0; kb < p.nkb; ++kb)
-                    {
-                        if (++s == p.stages)
-                        {
-                            s = 0;
-                            ph ^= 1U;
-                        }
-                    }
-                    continue;
-                }
-                // A parity wait on a ring stage is only meaningful once the stage's previous fill
-                // has completed.  This thread has not watched the fills of the other thread's
-                // MMAs, so it first lets the other thread report them (they were requested
-                // before this MMA's fills, so this hardly ever spins).
-                if (fills_before > 0)
-                {
-                    uint32_t polls = 0;
-                    const long long deadline = clock64() + ptx::WAIT_CLOCK_LIMIT;
-                    while (fills_seen[issuer ^ 1] < fills_before)
-                    {
-                        if ((++polls & 1023U) == 0 && clock64() > deadline)
-                        {
-                            ok = false;
-                            break;
-                        }
-                    }
-                    if (!ok)
-                    {
-                        break;
-                    }
-                }
-                // tile lt goes to accumulator lt % 4 (consumer group lt % 2), used for the (lt / 4)-th
-                // time; a 256-column MMA fills two neighbouring accumulators (one per group) at once
-                const int a = static_cast<int>(lt & (FT_ACCS - 1));
-                const uint32_t aph = static_cast<uint32_t>((lt >> 2) & 1);
-                if (!ptx::mbar_wait_bounded_spin(&acc_empty[a], aph ^ 1U) ||
-                    (NT == 2 && !ptx::mbar_wait_bounded_spin(&acc_empty[a + 1], aph ^ 1U)))
-                {
-                    ok = false;
-                    break;
-                }
-                tc::fence_after_sync();
-                const uint32_t acc = tmem_base + static_cast<uint32_t>(a * TILE_N);
-                for (int kb = 0; kb < p.nkb && ok; ++kb)
-                {
-                    // the one or two query steps that meet each of the four steps of this K block
-                    // (read before the wait: the MMA statements below order memory accesses)
-                    uint2 a_words[4];
-#pragma unroll
-                    for (int ks = 0; ks < 4; ++ks)
-                    {
-                        a_words[ks] = a_tab[kb * 4 + ks];
-                    }
-                    if (!ptx::mbar_wait_bounded_spin(&full_b[s], ph))
-                    {
-                        ok = false;
-                        break;
-                    }
-                    tc::fence_after_sync();
-                    const uint32_t b_lo = b_lo0 + static_cast<uint32_t>(s) * (STAGE_B >> 4);
-#pragma unroll
-                    for (int ks = 0; ks < 128 / K_STEP_BYTES; ++ks)
-                    {
-                        const uint2 a_lo = a_words[ks];
-                        const uint32_t b_st = b_lo + static_cast<uint32_t>(ks * (K_STEP_BYTES >> 4));
-                        tc::mma_words<BF16>(acc, a_lo.x, b_st, desc_hi, idesc, (kb | ks) != 0 ? 1U : 0U, a_lo.x);
-                        tc::mma_words<BF16>(acc, a_lo.y, b_st, desc_hi, idesc, 1U, a_lo.y);
-                    }
-                    tc::mma_commit(&empty_b[s]);
-                    if (++s == p.stages)
-                    {
-                        s = 0;
-                        ph ^= 1U;
-                    }
-                    if (kb == p.nkb - 1)
-                    {
-                        fills_seen[issuer] = fills_before + p.nkb;
-                    }
-                }
-                tc::mma_commit(&acc_full[a]);
-                if constexpr (NT == 2)
-                {
-                    tc::mma_commit(&acc_full[a + 1]);
-                }
-            }
+            ok = tcpipe::mma_issuer<BF16, NMMA>(pipe, shape, tmem_base, warp - FT_MMA_WARP, t_begin, t_end);
         }
     }
     else
@@ -503,7 +331,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
     if (warp == FT_MMA_WARP)
     {
         tc::fence_after_sync();
-        tc::tmem_dealloc(tmem_base, FT_TMEM_COLS);
+        tc::tmem_dealloc(tmem_base, tcpipe::TMEM_COLS);
     }
 }
 
@@ -522,26 +350,12 @@ struct ftc_layout
 ftc_layout ftc_layout_of(int64_t n, int64_t q, int dim, int k, bool bf16)
 {
     ftc_layout l{};
-    const int unit = bf16 ? 64 : 32; // elements per 128-byte K block
-    const int step = unit / 4;       // elements per MMA K step
-    const int dp = (dim + step - 1) / step * step;
-    if (2 * (dp / step) + 1 <= MAX_KB * 4)
-    {
-        // compact split image: [hi (dp) | lo (dp) | norm columns, padded to one step]
-        l.split = 2;
-        l.hs = dp / step;
-        l.nsteps = 2 * l.hs + 1;
-        l.dim_pad = 2 * dp + step;
-    }
-    else
-    {
-        // plain image: [row | norm columns], padded to whole K blocks
-        l.split = 0;
-        l.hs = 0;
-        l.dim_pad = ((dim + 3 + unit - 1) / unit) * unit;
-        l.nsteps = l.dim_pad / step;
-    }
-    l.nkb = (l.nsteps + 3) / 4;
+    const tcpipe::image_shape img = tcpipe::image_shape_of(dim, bf16, true);
+    l.dim_pad = img.dim_pad;
+    l.split = img.split;
+    l.hs = img.hs;
+    l.nsteps = img.nsteps;
+    l.nkb = img.nkb;
     l.kl = k <= 32 ? 32 : (k <= 64 ? 64 : (k <= 128 ? 128 : 256));
     const int64_t nqb = (q + TILE_M - 1) / TILE_M;
     const int64_t tiles = (n + TILE_N - 1) / TILE_N;

@@ -6,22 +6,21 @@
 // of its tensor-core experiment fused_tc_kernel.cuh:109-158,346,440: a pre-pass that converts
 // the inputs and computes the norms, then `fmaf(-2, dot, |x|^2) + |y|^2`).
 //
-//   pre-pass   rounds the inputs to the MMA input type (round-to-nearest) into a padded image
-//              in the caller's workspace and writes the FP32 norms of the ORIGINAL vectors;
-//              for dim <= 85 (TF32) / 170 (BF16) the image carries a hi/lo split along K that
-//              compensates the input rounding (see tc_prepare_kernel), which is what keeps
+//   pre-pass   rounds the inputs to the MMA input type (round-to-nearest) into an image in the
+//              caller's workspace and writes the FP32 norms of the ORIGINAL vectors; whenever it
+//              fits the resident query tile (dim <= 128 TF32 / 256 BF16) the image is the compact
+//              hi/lo split of tc_host.cuh, which compensates the input rounding and is what keeps
 //              recall@k >= 0.999 against the FP32 path
-//   main       320 threads per block, one block per SM:
-//              warp 8  TMA producer: query tile once, then point tiles through a ring of
-//                      16 KiB stages (128 rows x 128 bytes, 128-byte swizzle)
-//              warp 9  allocates 512 TMEM columns (four accumulators), issues tcgen05.mma (M = 128 queries,
-//                      N = 128 points, K = 8 TF32 / 16 BF16 per instruction), commits stage and
-//                      accumulator barriers
-//              warps 0-7  epilogue, two groups of four: group g drains accumulator buffer g
-//                      (every other tile) with tcgen05.ld 32 lanes x 32 columns, transposes
+//   main       352 threads per block, one block per SM:
+//              warp 8      TMA producer: query tile once, then point tiles through a ring
+//              warps 9, 10 tcgen05.mma issue in turn (tc_pipeline.cuh), M = 128 queries,
+//                          N = 256 points (two accumulators at once) or 128, K = 8 TF32 / 16 BF16
+//                          per instruction; warp 9 allocates the 512 TMEM columns
+//              warps 0-7   epilogue, two groups of four: group g drains every other 128-point
+//                      tile with tcgen05.ld 32 lanes x 32 columns, transposes
 //                      through a shared-memory staging tile so that every 128-byte row segment
 //                      is written by 8 lanes, adds the norms, streaming 128-bit stores; each group
-//                      alternates between two accumulators, so the MMAs run two tiles ahead of it
+//                      alternates between two accumulators, so the MMAs run ahead of it
 // Every mbarrier wait is bounded; on expiry the role stops, the block reaches its final barrier,
 // frees its TMEM and sets the device status word.
 #include <algorithm>
@@ -35,6 +34,7 @@
 #include "ptx.cuh"
 #include "tc.cuh"
 #include "tc_host.cuh"
+#include "tc_pipeline.cuh"
 
 namespace bitsknn
 {
@@ -42,11 +42,10 @@ namespace bitsknn
 namespace
 {
 
-constexpr int TC_THREADS = 320;     // 8 epilogue warps + TMA producer warp + MMA warp
+constexpr int TC_THREADS = 352;     // 8 epilogue warps + TMA producer warp + two MMA warps
 constexpr int PRODUCER_WARP = 8;
 constexpr int MMA_WARP = 9;
-constexpr int TMEM_COLS = 512;      // four 128-column accumulators: each epilogue group owns two
-constexpr int ACCS = 4;
+constexpr int ACCS = tcpipe::ACCS;  // four 128-column accumulators: each epilogue group owns two
 constexpr int STAGE_LD = 36;       // row stride (floats) of the epilogue staging tiles
 
 struct tc_params
@@ -58,60 +57,61 @@ struct tc_params
     int64_t n;
     int64_t q;
     int nkb;      // K blocks per tile
+    int nsteps;   // MMA K steps per row that hold data
+    int hs;       // steps of the hi part of the compact split image (0: plain image)
     int stages;   // ring stages
     int parts;    // blocks per query tile
     int64_t tiles; // point tiles
     int* status;
 };
 
-template <bool BF16>
+template <bool BF16, int NMMA>
 __global__ void __launch_bounds__(TC_THREADS, 1)
     l2_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_p, const tc_params p)
 {
+    constexpr int NT = NMMA / TILE_N;            // 128-column tiles per MMA (1 or 2)
+    constexpr int STAGE_B = NT * STAGE_BYTES;    // one K block of NMMA points
     extern __shared__ unsigned char smem_raw[];
     // 1024-byte alignment for the swizzled tiles
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    unsigned char* a_tiles = smem;                                       // nkb x 16 KiB
-    unsigned char* b_ring = a_tiles + static_cast<size_t>(p.nkb) * STAGE_BYTES; // stages x 16 KiB
-    uint64_t* bars = reinterpret_cast<uint64_t*>(b_ring + static_cast<size_t>(p.stages) * STAGE_BYTES);
-    uint64_t* a_full = bars;
-    uint64_t* full_b = bars + 1;
-    uint64_t* empty_b = full_b + 16;
-    uint64_t* acc_full = empty_b + 16;
-    uint64_t* acc_empty = acc_full + ACCS;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + ACCS);
+    __shared__ uint2 a_tab_both[2][MAX_KB * 4]; // one descriptor table per MMA-issuing thread
+    __shared__ volatile int fills_seen[2];      // ring fills each issuing thread has seen complete
+    tcpipe::state pipe;
+    pipe.a_tiles = smem;                                                            // nkb x 16 KiB
+    pipe.b_ring = pipe.a_tiles + static_cast<size_t>(p.nkb) * STAGE_BYTES;          // stages x STAGE_B
+    uint64_t* bars = reinterpret_cast<uint64_t*>(pipe.b_ring + static_cast<size_t>(p.stages) * STAGE_B);
+    pipe.a_full = bars;
+    pipe.full_b = bars + 1;
+    pipe.empty_b = pipe.full_b + 16;
+    pipe.acc_full = pipe.empty_b + 16;
+    pipe.acc_empty = pipe.acc_full + ACCS;
+    pipe.a_tab = &a_tab_both[0][0];
+    pipe.fills_seen = fills_seen;
+    uint64_t* acc_full = pipe.acc_full;
+    uint64_t* acc_empty = pipe.acc_empty;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pipe.acc_empty + ACCS);
     float* staging = reinterpret_cast<float*>(bars + 64); // 8 warps x 32 rows x STAGE_LD floats
+    const tcpipe::shape shape{p.nkb, p.nsteps, p.hs, p.stages};
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
-    constexpr int KB_ELEMS = BF16 ? 64 : 32; // elements per 128-byte K block
-    constexpr int K_STEP_BYTES = 32;         // one MMA consumes 32 bytes of K (8 TF32 / 16 BF16)
 
     const int64_t qb = blockIdx.x / p.parts;
     const int part = static_cast<int>(blockIdx.x - qb * p.parts);
-    const int64_t per = (p.tiles + p.parts - 1) / p.parts;
+    // tiles of 128 points; a part is a whole number of MMAs (a tile beyond n stores nothing)
+    const int64_t per = ((p.tiles + p.parts - 1) / p.parts + NT - 1) / NT * NT;
+    const int64_t tiles_up = (p.tiles + NT - 1) / NT * NT;
     const int64_t t_begin = part * per;
-    const int64_t t_end = t_begin + per < p.tiles ? t_begin + per : p.tiles;
+    const int64_t t_end = t_begin + per < tiles_up ? t_begin + per : tiles_up;
 
     if (tid == 0)
     {
-        ptx::mbar_init(a_full, 1);
-        for (int s = 0; s < p.stages; ++s)
-        {
-            ptx::mbar_init(&full_b[s], 1);
-            ptx::mbar_init(&empty_b[s], 1);
-        }
-        for (int a = 0; a < ACCS; ++a)
-        {
-            ptx::mbar_init(&acc_full[a], 1);
-            ptx::mbar_init(&acc_empty[a], 128);
-        }
-        ptx::mbar_init_fence();
+        tcpipe::init_barriers(pipe, p.stages);
     }
     if (warp == MMA_WARP)
     {
-        tc::tmem_alloc(tmem_slot, TMEM_COLS);
+        tc::tmem_alloc(tmem_slot, tcpipe::TMEM_COLS);
     }
     tc::fence_before_sync();
     __syncthreads();
@@ -123,81 +123,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     {
         if (lane == 0 && t_begin < t_end)
         {
-            ptx::mbar_expect_tx(a_full, static_cast<uint32_t>(p.nkb) * STAGE_BYTES);
-            for (int kb = 0; kb < p.nkb; ++kb)
-            {
-                tc::tma_load_2d(a_tiles + static_cast<size_t>(kb) * STAGE_BYTES, &map_q, kb * KB_ELEMS,
-                                static_cast<int>(qb * TILE_M), a_full);
-            }
-            int s = 0;
-            uint32_t ph = 0;
-            for (int64_t t = t_begin; t < t_end && ok; ++t)
-            {
-                for (int kb = 0; kb < p.nkb; ++kb)
-                {
-                    // a fresh barrier passes a wait on the opposite parity at once
-                    if (!ptx::mbar_wait_bounded(&empty_b[s], ph ^ 1U))
-                    {
-                        ok = false;
-                        break;
-                    }
-                    ptx::mbar_expect_tx(&full_b[s], STAGE_BYTES);
-                    tc::tma_load_2d(b_ring + static_cast<size_t>(s) * STAGE_BYTES, &map_p, kb * KB_ELEMS,
-                                    static_cast<int>(t * TILE_N), &full_b[s]);
-                    if (++s == p.stages)
-                    {
-                        s = 0;
-                        ph ^= 1U;
-                    }
-                }
-            }
+            ok = tcpipe::producer<BF16, NMMA>(pipe, shape, &map_q, &map_p, qb * TILE_M, t_begin, t_end);
         }
     }
-    else if (warp == MMA_WARP)
+    else if (warp == MMA_WARP || warp == MMA_WARP + 1)
     {
         if (lane == 0 && t_begin < t_end)
         {
-            constexpr uint32_t idesc = tc::instr_desc(BF16 ? 1U : 2U, TILE_M, TILE_N);
-            ok = ptx::mbar_wait_bounded(a_full, 0);
-            int s = 0;
-            uint32_t ph = 0;
-            int64_t lt = 0;
-            for (int64_t t = t_begin; t < t_end && ok; ++t, ++lt)
-            {
-                // tile lt goes to accumulator lt % 4 (epilogue group lt % 2), used for the (lt / 4)-th time
-                const int a = static_cast<int>(lt & (ACCS - 1));
-                const uint32_t aph = static_cast<uint32_t>((lt >> 2) & 1);
-                if (!ptx::mbar_wait_bounded(&acc_empty[a], aph ^ 1U))
-                {
-                    ok = false;
-                    break;
-                }
-                tc::fence_after_sync();
-                for (int kb = 0; kb < p.nkb && ok; ++kb)
-                {
-                    if (!ptx::mbar_wait_bounded(&full_b[s], ph))
-                    {
-                        ok = false;
-                        break;
-                    }
-                    tc::fence_after_sync();
-                    const uint64_t adesc = tc::smem_desc_sw128(a_tiles + static_cast<size_t>(kb) * STAGE_BYTES);
-                    const uint64_t bdesc = tc::smem_desc_sw128(b_ring + static_cast<size_t>(s) * STAGE_BYTES);
-#pragma unroll
-                    for (int ks = 0; ks < 128 / K_STEP_BYTES; ++ks)
-                    {
-                        tc::mma<BF16>(tmem_base + static_cast<uint32_t>(a * TILE_N), adesc + (ks * K_STEP_BYTES >> 4),
-                                      bdesc + (ks * K_STEP_BYTES >> 4), idesc, kb > 0 || ks > 0);
-                    }
-                    tc::mma_commit(&empty_b[s]); // the stage is free once these MMAs have read it
-                    if (++s == p.stages)
-                    {
-                        s = 0;
-                        ph ^= 1U;
-                    }
-                }
-                tc::mma_commit(&acc_full[a]);
-            }
+            ok = tcpipe::mma_issuer<BF16, NMMA>(pipe, shape, tmem_base, warp - MMA_WARP, t_begin, t_end);
         }
     }
     else
@@ -250,7 +183,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
             // (made warp-uniform: the lanes poll independently)
             const int a = static_cast<int>(lt & (ACCS - 1));
             const uint32_t lane_base = lane_row + static_cast<uint32_t>(a * TILE_N);
-            if (!__all_sync(FULL_MASK, ptx::mbar_wait_bounded(&acc_full[a], static_cast<uint32_t>((lt >> 2) & 1))))
+            if (!__all_sync(FULL_MASK, ptx::mbar_wait_bounded_spin(&acc_full[a], static_cast<uint32_t>((lt >> 2) & 1))))
             {
                 ok = false;
                 break;
@@ -333,34 +266,38 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     if (warp == MMA_WARP)
     {
         tc::fence_after_sync();
-        tc::tmem_dealloc(tmem_base, TMEM_COLS);
+        tc::tmem_dealloc(tmem_base, tcpipe::TMEM_COLS);
     }
 }
 
 struct tc_layout
 {
-    int dim_pad; // length of a row image along K (elements), whole 128-byte blocks
-    int split;   // 1: error-compensated 3-term image
+    tcpipe::image_shape img;
     size_t off_pn, off_qn, off_p, off_q, total;
 };
 
 tc_layout layout_of(int64_t n, int64_t q, int dim, bool bf16)
 {
     tc_layout l{};
-    // padded to whole 128-byte K blocks, so that a TMA box never exceeds the row; the
-    // compensated image is used whenever 3 * dim fits the resident query tile (MAX_KB blocks)
-    const int unit = bf16 ? 64 : 32;
-    l.split = 3 * dim <= MAX_KB * unit ? 1 : 0;
-    const int ext = (l.split != 0 ? 3 : 1) * dim;
-    l.dim_pad = ((ext + unit - 1) / unit) * unit;
+    l.img = tcpipe::image_shape_of(dim, bf16, false);
     const size_t esz = bf16 ? 2 : 4;
     l.off_pn = 0;
     l.off_qn = align256(static_cast<size_t>(n) * 4);
     l.off_p = l.off_qn + align256(static_cast<size_t>(q) * 4);
-    // rows padded to a whole tile so that a box never starts beyond the allocation
-    l.off_q = l.off_p + align256(static_cast<size_t>(n) * l.dim_pad * esz);
-    l.total = l.off_q + align256(static_cast<size_t>(q) * l.dim_pad * esz);
+    l.off_q = l.off_p + align256(static_cast<size_t>(n) * l.img.dim_pad * esz);
+    l.total = l.off_q + align256(static_cast<size_t>(q) * l.img.dim_pad * esz);
     return l;
+}
+
+template <bool BF16, int NMMA>
+int launch_tc(const CUtensorMap& map_q, const CUtensorMap& map_p, const tc_params& p, size_t smem, int64_t grid,
+              cudaStream_t stream)
+{
+    auto kernel = l2_tc_kernel<BF16, NMMA>;
+    BITSKNN_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    kernel<<<static_cast<unsigned>(grid), TC_THREADS, smem, stream>>>(map_q, map_p, p);
+    BITSKNN_CUDA_TRY(cudaGetLastError());
+    return BITSKNN_OK;
 }
 
 template <bool BF16>
@@ -373,21 +310,10 @@ int run_tc(const float* points, const float* queries, int64_t n, int64_t q, int 
     void* cp = ws + l.off_p;
     void* cq = ws + l.off_q;
     tc_prepare_kernel<BF16>
-        <<<static_cast<unsigned>((n + 7) / 8), 256, 0, stream>>>(points, n, dim, l.dim_pad, l.split, 1, 0, cp, pn);
+        <<<static_cast<unsigned>((n + 7) / 8), 256, 0, stream>>>(points, n, dim, l.img.dim_pad, l.img.split, 1, 0, cp, pn);
     tc_prepare_kernel<BF16>
-        <<<static_cast<unsigned>((q + 7) / 8), 256, 0, stream>>>(queries, q, dim, l.dim_pad, l.split, 0, 0, cq, qn);
+        <<<static_cast<unsigned>((q + 7) / 8), 256, 0, stream>>>(queries, q, dim, l.img.dim_pad, l.img.split, 0, 0, cq, qn);
     BITSKNN_CUDA_TRY(cudaGetLastError());
-
-    CUtensorMap map_q;
-    CUtensorMap map_p;
-    if (const int rc = make_map(&map_q, cq, q, l.dim_pad, BF16); rc != BITSKNN_OK)
-    {
-        return rc;
-    }
-    if (const int rc = make_map(&map_p, cp, n, l.dim_pad, BF16); rc != BITSKNN_OK)
-    {
-        return rc;
-    }
 
     tc_params p{};
     p.qn = qn;
@@ -396,25 +322,62 @@ int run_tc(const float* points, const float* queries, int64_t n, int64_t q, int 
     p.ld = ld;
     p.n = n;
     p.q = q;
-    const int kb_elems = BF16 ? 64 : 32;
-    p.nkb = (l.dim_pad + kb_elems - 1) / kb_elems;
+    p.nkb = l.img.nkb;
+    p.nsteps = l.img.nsteps;
+    p.hs = l.img.hs;
     p.tiles = (n + TILE_N - 1) / TILE_N;
     const int64_t nqb = (q + TILE_M - 1) / TILE_M;
     const int sms = device_sm_count();
-    p.parts = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(p.tiles, sms / std::max<int64_t>(nqb, 1))));
-    p.stages = std::max(2, std::min(12, 11 - p.nkb));
+    // Blocks per query tile: the smallest count that keeps the last wave of blocks (one per SM)
+    // nearly full, with ranges of at least 64 point tiles per block.
+    {
+        const int64_t max_parts = std::max<int64_t>(1, std::min<int64_t>(p.tiles / 64, 64));
+        int64_t best = 1;
+        double best_eff = 0.0;
+        for (int64_t parts = 1; parts <= max_parts; ++parts)
+        {
+            const int64_t blocks = nqb * parts;
+            const int64_t waves = (blocks + sms - 1) / sms;
+            const double eff = static_cast<double>(blocks) / static_cast<double>(waves * sms);
+            if (eff > best_eff + 0.02)
+            {
+                best_eff = eff;
+                best = parts;
+            }
+        }
+        p.parts = static_cast<int>(best);
+    }
     p.status = device_status_word();
     if (p.status == nullptr)
     {
         return fail(BITSKNN_ERR_CUDA, "CUDA error. cannot resolve the device status word");
     }
-    const size_t smem = 1024 + static_cast<size_t>(p.nkb + p.stages) * STAGE_BYTES + 64 * 8 + 8 * 32 * STAGE_LD * 4;
-    auto kernel = l2_tc_kernel<BF16>;
-    BITSKNN_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    // shared memory: query image + ring + barriers + staging tiles.  An MMA covers 256 points when
+    // at least two of its 32 KiB stages fit beside the query image, else 128 points.
+    const size_t fixed = 1024 + 64 * 8 + 8 * 32 * STAGE_LD * 4;
+    const int room128 = static_cast<int>((227 * 1024 - fixed) / STAGE_BYTES) - p.nkb;
+    if (room128 < 2)
+    {
+        return fail(BITSKNN_ERR_UNSUPPORTED_DIM, "Unsupported dimension: %d (query image does not fit shared memory)", dim);
+    }
+    const bool wide = tuning_value("fused.tc_mma_n", 0) == 128 ? false : room128 >= 4;
+    const int nt = wide ? 2 : 1;
+    p.stages = std::min(wide ? 4 : 8, room128 / nt);
+    const size_t smem = fixed + (static_cast<size_t>(p.nkb) + static_cast<size_t>(p.stages) * nt) * STAGE_BYTES;
+
+    CUtensorMap map_q;
+    CUtensorMap map_p;
+    if (const int rc = make_map(&map_q, cq, q, l.img.dim_pad, BF16); rc != BITSKNN_OK)
+    {
+        return rc;
+    }
+    if (const int rc = make_map(&map_p, cp, n, l.img.dim_pad, BF16, wide ? 256U : 128U); rc != BITSKNN_OK)
+    {
+        return rc;
+    }
     const int64_t grid = nqb * p.parts;
-    kernel<<<static_cast<unsigned>(grid), TC_THREADS, smem, stream>>>(map_q, map_p, p);
-    BITSKNN_CUDA_TRY(cudaGetLastError());
-    return BITSKNN_OK;
+    return wide ? launch_tc<BF16, 256>(map_q, map_p, p, smem, grid, stream)
+                : launch_tc<BF16, 128>(map_q, map_p, p, smem, grid, stream);
 }
 
 } // namespace
