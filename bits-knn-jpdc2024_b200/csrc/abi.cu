@@ -1,4 +1,5 @@
 // Error reporting, tuning registry and the device status word shared by every entry point.
+#include <algorithm>
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
@@ -37,6 +38,7 @@ tuning_entry g_tuning[] = {
     {"select.unroll", 0, 0, 4},
     {"fused.variant", 2, 0, 2},
     {"fused.tc_mma_n", 0, 0, 256},
+    {"fused.parts", 0, 0, 64},
 };
 
 } // namespace
@@ -81,6 +83,24 @@ int tuning_value(const char* key, int fallback)
         }
     }
     return fallback;
+}
+
+int balanced_parts(int64_t query_tiles, int slots, int64_t max_parts)
+{
+    int64_t best = 1;
+    double best_eff = 0.0;
+    for (int64_t parts = 1; parts <= std::max<int64_t>(max_parts, 1); ++parts)
+    {
+        const int64_t blocks = query_tiles * parts;
+        const int64_t waves = (blocks + slots - 1) / slots;
+        const double eff = static_cast<double>(blocks) / static_cast<double>(waves * slots);
+        if (eff > best_eff + 0.02)
+        {
+            best_eff = eff;
+            best = parts;
+        }
+    }
+    return static_cast<int>(best);
 }
 
 int device_sm_count()

@@ -365,6 +365,10 @@ ftc_layout ftc_layout_of(int64_t n, int64_t q, int dim, int k, bool bf16)
     const int sms = device_sm_count();
     const int64_t want = 4 * nqb >= 3 * sms ? 1 : (sms + nqb - 1) / nqb;
     l.parts = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(want, std::max<int64_t>(1, tiles / 64))));
+    if (const int forced = tuning_value("fused.parts", 0); forced > 0)
+    {
+        l.parts = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(forced, std::max<int64_t>(1, tiles / 64))));
+    }
     const size_t esz = bf16 ? 2 : 4;
     l.off_pn = 0;
     l.off_qn = align256(static_cast<size_t>(n) * 4);

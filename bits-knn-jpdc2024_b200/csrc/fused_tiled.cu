@@ -412,10 +412,15 @@ tiled_layout tiled_layout_of(int64_t n, int64_t q, int dim, int k)
     l.dp = (dim + 3) / 4 * 4;
     const int64_t nqb = (q + FT_BM - 1) / FT_BM;
     const int64_t tiles = (n + FT_BN - 1) / FT_BN;
-    // two blocks fit an SM; split the database only when the query tiles cannot fill them
+    // two blocks fit an SM; the database is split as far as all blocks still run at once
+    // (measured: q = 2^14 on 148 SMs takes 19.3 ms with 2 ranges, 21.8 with 3, 20.5 with 4)
     const int slots = 2 * device_sm_count();
-    const int64_t want = 4 * nqb >= 3 * slots ? 1 : (slots + nqb - 1) / nqb;
+    const int64_t want = std::max<int64_t>(1, slots / nqb);
     l.parts = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(want, std::max<int64_t>(1, tiles / 32))));
+    if (const int forced = tuning_value("fused.parts", 0); forced > 0)
+    {
+        l.parts = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(forced, std::max<int64_t>(1, tiles / 32))));
+    }
     const size_t lists = static_cast<size_t>(l.parts) * static_cast<size_t>(q) * l.kl;
     auto align256 = [](size_t v) { return (v + 255) & ~static_cast<size_t>(255); };
     l.off_pimg = 0;

@@ -328,25 +328,8 @@ int run_tc(const float* points, const float* queries, int64_t n, int64_t q, int 
     p.tiles = (n + TILE_N - 1) / TILE_N;
     const int64_t nqb = (q + TILE_M - 1) / TILE_M;
     const int sms = device_sm_count();
-    // Blocks per query tile: the smallest count that keeps the last wave of blocks (one per SM)
-    // nearly full, with ranges of at least 64 point tiles per block.
-    {
-        const int64_t max_parts = std::max<int64_t>(1, std::min<int64_t>(p.tiles / 64, 64));
-        int64_t best = 1;
-        double best_eff = 0.0;
-        for (int64_t parts = 1; parts <= max_parts; ++parts)
-        {
-            const int64_t blocks = nqb * parts;
-            const int64_t waves = (blocks + sms - 1) / sms;
-            const double eff = static_cast<double>(blocks) / static_cast<double>(waves * sms);
-            if (eff > best_eff + 0.02)
-            {
-                best_eff = eff;
-                best = parts;
-            }
-        }
-        p.parts = static_cast<int>(best);
-    }
+    // blocks per query tile: ranges of at least 64 point tiles, last wave of blocks (one per SM) nearly full
+    p.parts = balanced_parts(nqb, sms, std::min<int64_t>(p.tiles / 64, 64));
     p.status = device_status_word();
     if (p.status == nullptr)
     {

@@ -75,6 +75,8 @@ int bitsknn_selftest_bounded_wait(bitsknn_stream_t stream);
  *                         filter): the reference's un-buffered ablation `partial-bitonic-regs`
  *   "fused.variant"       FP32 fused kernel: 0 = 8 queries per block, 1 = tiled (needs the
  *                         workspace), 2 = automatic (default)
+ *   "fused.parts"         blocks per query tile of the tiled fused kernels, i.e. ranges the database
+ *                         is cut into (0 = automatic, the default)
  *   "fused.tc_mma_n"      points per tensor-core MMA of the fused TF32/BF16 kernels: 0 = 256
  *                         whenever the operand ring fits shared memory (default), 128 = always 128
  * The reference's `--block-size` / `--items-per-thread` flags tune the same things for its
