@@ -7,7 +7,9 @@ by n=2^20 columns (4 GiB) per GPU, Uniform[0,1) from a seeded device generator (
 the reference itself only ever measures generated data), k=256 by default.  One step = one
 pass of the selection over the whole matrix.  With N GPUs the matrix is database-sharded:
 every rank holds its own q x n column block of a q x (N*n) matrix (weak scaling), selects
-its local top-k, the candidates are all-gathered over NCCL and merged on every rank.
+its local top-k, the candidates are all-gathered over NCCL and merged on every rank; the K timed
+searches run as a stream (`ShardedSearch.submit_select` / `drain`): the all-gather of one search
+is in flight while the next local selection runs, and all K are complete inside the timed region.
 
 The JSON line carries: `value` (distances/s with the matrix resident in HBM), `e2e` (same
 metric through the C ABI with HOST buffers: pinned host -> device copy of the matrix, the
@@ -403,6 +405,12 @@ def main():
         # local selection with global labels, then (N > 1) ONE NCCL all-gather + merge kernel
         search.select(src, k, rank * n, offsets=offsets, out=None if world == 1 else (fin_d, fin_i))
 
+    def stream_step(events=None):
+        # the same search as one of a stream of searches: with N > 1 its all-gather stays in flight
+        # while the next local selection runs (two buffer sets), and the previous search is merged
+        search.submit_select(matrix, k, rank * n, offsets=offsets, out=None if world == 1 else (fin_d, fin_i),
+                             events=events)
+
     def barrier():
         torch.cuda.synchronize()
         if world > 1:
@@ -422,23 +430,22 @@ def main():
         sampler.start()
         sampler.wait_first_sample()
     for _ in range(args.warmup):
-        step()
+        stream_step()
+    search.drain()
     barrier()
     # keep the GPU under the same load a little longer so that the clock sampler (20 ms period)
     # sees the clocks this workload settles at; still untimed
     # (a fixed count, identical on every rank: each step holds collectives when N > 1)
     for _ in range(300):
-        step()
+        stream_step()
+    search.drain()
     barrier()
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(2 * args.steps + 2)]
     barrier()
     ev[-2].record()
     for s in range(args.steps):
-        ev[2 * s].record()
-        bk.select(matrix, k, label_offsets=offsets, out=(out_d, out_i))
-        ev[2 * s + 1].record()
-        if world > 1:
-            search._exchange_and_merge(q, k, dev, out=(fin_d, fin_i))
+        stream_step(events=(ev[2 * s], ev[2 * s + 1]))
+    search.drain()  # the K-th search is complete inside the timed region too
     ev[-1].record()
     barrier()
     clocks = sampler.stop() if rank == 0 else None

@@ -59,8 +59,20 @@ def _worker(rank, world, port, n, q, k, result_dir):
     search = sharded.ShardedSearch(OracleKernels(), rank, world)
     sd, si = search.select(torch.from_numpy(np.ascontiguousarray(matrix[:, begin:end])), k, begin)
     kd, ki = search.knn(torch.from_numpy(points[begin:end]), torch.from_numpy(queries), k, begin)
+    # a stream of three searches over shifted matrices: submit returns the previous search's result
+    stream_out = []
+    for step in range(3):
+        shifted = np.ascontiguousarray(np.roll(matrix, step, axis=0)[:, begin:end])
+        done = search.submit_select(torch.from_numpy(shifted), k, begin)
+        assert (done is None) == (step == 0)
+        if done is not None:
+            stream_out.append((done[0].numpy().copy(), done[1].numpy().copy()))
+    done = search.drain()
+    stream_out.append((done[0].numpy().copy(), done[1].numpy().copy()))
+    assert search.drain() is None
     np.savez(os.path.join(result_dir, f"rank{rank}.npz"), sd=sd.numpy(), si=si.numpy(), kd=kd.numpy(), ki=ki.numpy(),
-             matrix=matrix, points=points, queries=queries)
+             matrix=matrix, points=points, queries=queries,
+             pd=np.stack([d for d, _ in stream_out]), pi=np.stack([i for _, i in stream_out]))
     dist.destroy_process_group()
 
 
@@ -94,3 +106,6 @@ def test_sharded_search_equals_unsharded(tmp_path, oracle, world):
         assert np.array_equal(got["sd"], want_d) and np.array_equal(got["si"], want_i)
         want_d, want_i = oracle.knn(got["points"], got["queries"], k, partial=True)
         assert np.array_equal(got["kd"], want_d) and np.array_equal(got["ki"], want_i)
+        for step in range(3):
+            want_d, want_i = oracle.select(np.roll(got["matrix"], step, axis=0), k)
+            assert np.array_equal(got["pd"][step], want_d) and np.array_equal(got["pi"][step], want_i)
