@@ -46,7 +46,14 @@ constexpr int QT = 8;                  // queries per block = warps per block
 constexpr int PPT = 4;                 // points per thread
 constexpr int PT = FUSED_THREADS * PPT; // points per tile
 constexpr int DT = 4;                  // coordinates per staged tile
-constexpr int FUSED_TILED_MIN_DIM = 16; // automatic choice: tiled kernel from this dimension on (measured crossover)
+// Automatic choice between the two FP32 kernels, from a sweep at q = 2^14, n = 2^20 on B200: the
+// tiled kernel wins from dim 16 on, and below that for short lists (its folds go through L2, the
+// 8-query kernel keeps its lists in registers): dim 4: 10.1 ms against 15.4 at k = 16, 16.5 against
+// 16.5 at k = 128, 29.9 against 17.3 at k = 256.
+inline bool fused_prefers_tiled(int dim, int k)
+{
+    return dim >= 16 || k <= 64 || (k <= 128 && dim >= 8);
+}
 
 struct fused_params
 {
@@ -417,7 +424,7 @@ extern "C" int bitsknn_fused(const float* d_points, const float* d_queries, int6
     const bool have_ws = fused_tiled_supports(dim) && d_workspace != nullptr &&
                          workspace_bytes >= fused_tiled_workspace_bytes(n, q, dim, k) &&
                          (reinterpret_cast<uintptr_t>(d_workspace) & 255U) == 0;
-    if (have_ws && (variant == 1 || (variant == 2 && dim >= FUSED_TILED_MIN_DIM)))
+    if (have_ws && (variant == 1 || (variant == 2 && fused_prefers_tiled(dim, k))))
     {
         return fused_tiled_launch(d_points, d_queries, n, q, dim, k, mode, index_base, d_out_dist, d_out_idx,
                                   d_workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
