@@ -657,9 +657,9 @@ int dispatch_select(const select_params& p, int64_t vrows, cudaStream_t stream)
 {
     // smallest list that holds k: the reference's dynamic_switch_le over K
     // (src/topk/singlepass/bits_knn.cu:44), with the list never shorter than the block
-    // Long lists take 512-thread blocks (the reference's tuned shapes do the same for k = 2048,
-    // scripts/optima.csv:1282): twice the threads fold a list of the same length with half the
-    // pairs, and registers, per thread.
+    // Long lists take larger blocks (the reference's tuned shapes use 512 threads for k = 2048,
+    // scripts/optima.csv:1282): more threads fold a list of the same length with fewer pairs, and
+    // registers, per thread.
     const int wide = tuning_value("select.wide_block", 1);
     if (p.k <= 256)
     {
@@ -673,7 +673,10 @@ int dispatch_select(const select_params& p, int64_t vrows, cudaStream_t stream)
     {
         return wide != 0 ? launch_select<512, 2>(p, vrows, stream) : launch_select<256, 4>(p, vrows, stream);
     }
-    return wide != 0 ? launch_select<512, 4>(p, vrows, stream) : launch_select<256, 8>(p, vrows, stream);
+    // the longest lists: 1024 threads with two pairs each (measured against 512 x 4 at q = 1024,
+    // n = 2^20, k = 2048: 1.74 ms against 2.00 on uniform rows, 4.5 against 5.5 per 128 descending rows;
+    // at k = 1024 the 512-thread block stays ahead on uniform rows, 1.09 ms against 1.25)
+    return wide != 0 ? launch_select<1024, 2>(p, vrows, stream) : launch_select<256, 8>(p, vrows, stream);
 }
 
 template <int IPT>

@@ -70,7 +70,8 @@ int bitsknn_selftest_bounded_wait(bitsknn_stream_t stream);
  *                         0 = automatic, the default: 50 for lists of up to 256 pairs, else 75)
  *   "select.unroll"       128-bit vectors per thread examined under one warp vote (0 = automatic,
  *                         2 or 4)
- *   "select.wide_block"   1 = 512-thread blocks for k > 256 (default), 0 = 256-thread blocks
+ *   "select.wide_block"   1 = 512-thread blocks for 256 < k <= 1024 and 1024-thread blocks beyond
+ *                         (default), 0 = 256-thread blocks
  *   "select.filter"       0 = bitsknn_select buffers, sorts and merges every value (no radius
  *                         filter): the reference's un-buffered ablation `partial-bitonic-regs`
  *   "fused.variant"       FP32 fused kernel: 0 = 8 queries per block, 1 = tiled (needs the
