@@ -643,9 +643,10 @@ int launch_select(select_params p, int64_t vrows, cudaStream_t stream)
     p.stage_floats = std::max(4 * THREADS, (p.stage_floats / (4 * THREADS)) * (4 * THREADS));
     const size_t smem = select_smem_bytes(L, p.stage_floats, p.stages);
     // 128-bit vectors per thread examined under one warp vote
-    // (0 = automatic: 2 for 256-thread blocks -- no register spills at 4 blocks per SM --, 4 for 512)
+    // (0 = automatic: 2, which measured a little ahead of 4 for every block size: 0.83 ms against
+    // 0.85 at k = 512, 1.70 against 1.74 at k = 2048, no register spills at 4 blocks per SM for k <= 256)
     int unroll = tuning_value("select.unroll", 0);
-    unroll = unroll != 0 ? unroll : (THREADS == 256 ? 2 : 4);
+    unroll = unroll != 0 ? unroll : 2;
     auto kernel = unroll == 2 ? select_kernel<THREADS, IPT, 2> : select_kernel<THREADS, IPT, 4>;
     BITSKNN_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     kernel<<<static_cast<unsigned>(vrows), THREADS, smem, stream>>>(p);
