@@ -37,12 +37,15 @@ SIGNATURES = {
     "bitsknn_selftest_bounded_wait": (_int, [_ptr]),
     "bitsknn_set_tuning": (_int, [ctypes.c_char_p, _int]),
     "bitsknn_get_tuning": (_int, [ctypes.c_char_p, ctypes.POINTER(_int)]),
+    "bitsknn_tuning_key": (ctypes.c_char_p, [_int]),
     "bitsknn_select": (_int, [_ptr, _i64, _ptr, _i64, _ptr, _i64, _i64, _int, _ptr, _ptr, _ptr]),
     "bitsknn_select_auto_splits": (_int, [_i64, _i64, _int]),
     "bitsknn_select_split_workspace_bytes": (_sz, [_i64, _int, _int]),
     "bitsknn_select_split": (_int, [_ptr, _i64, _ptr, _i64, _i64, _int, _int, _ptr, _sz, _ptr, _ptr, _ptr]),
     "bitsknn_select_split_static": (_int, [_ptr, _i64, _ptr, _i64, _i64, _int, _int, _ptr, _ptr, _ptr]),
     "bitsknn_merge": (_int, [_ptr, _ptr, _i64, _i64, _i64, _int, _int, _ptr, _ptr, _ptr]),
+    "bitsknn_merge_lists": (_int, [_ptr, _ptr, _i64, _i64, _i64, _int, _int, _int, _ptr, _ptr, _ptr]),
+    "bitsknn_refine": (_int, [_ptr, _ptr, _i64, _i64, _int, _ptr, _i64, _int, ctypes.c_int32, _int, _ptr, _ptr, _ptr]),
     "bitsknn_l2_workspace_bytes": (_sz, [_i64, _i64, _int, _int]),
     "bitsknn_l2": (_int, [_ptr, _ptr, _i64, _i64, _int, _int, _ptr, _i64, _ptr, _sz, _ptr]),
     "bitsknn_fused_workspace_bytes": (_sz, [_i64, _i64, _int, _int, _int]),
@@ -103,6 +106,15 @@ def get_tuning(key):
     out = ctypes.c_int(0)
     _check(lib().bitsknn_get_tuning(key.encode(), ctypes.byref(out)))
     return out.value
+
+
+def tuning_keys():
+    keys = []
+    while True:
+        key = lib().bitsknn_tuning_key(len(keys))
+        if key is None:
+            return keys
+        keys.append(key.decode())
 
 
 def device_status():
@@ -180,7 +192,7 @@ def select_split_static(dist, k, splits, label_offsets=None, out=None):
     return out
 
 
-def merge(cand_dist, cand_idx, out=None):
+def merge(cand_dist, cand_idx, out=None, sorted_lists=False):
     """cand_* of shape (lists, q, k), contiguous -> the k smallest pairs per query."""
     import torch
     _device_check(cand_dist, torch.float32, "cand_dist")
@@ -190,12 +202,12 @@ def merge(cand_dist, cand_idx, out=None):
     if out is None:
         out = (torch.empty((q, k), dtype=torch.float32, device=cand_dist.device),
                torch.empty((q, k), dtype=torch.int32, device=cand_dist.device))
-    _check(lib().bitsknn_merge(_p(cand_dist), _p(cand_idx), q * k, k, q, lists, k, _p(out[0]), _p(out[1]),
-                               _stream()))
+    _check(lib().bitsknn_merge_lists(_p(cand_dist), _p(cand_idx), q * k, k, q, lists, k, 1 if sorted_lists else 0,
+                                     _p(out[0]), _p(out[1]), _stream()))
     return out
 
 
-def merge_strided(cand_dist, cand_idx, list_stride, query_stride, q, lists, k, out=None):
+def merge_strided(cand_dist, cand_idx, list_stride, query_stride, q, lists, k, out=None, sorted_lists=False):
     """Merge with explicit element strides: pair j of list l of query i at
     [l * list_stride + i * query_stride + j] from the first element of each tensor."""
     import torch
@@ -204,8 +216,25 @@ def merge_strided(cand_dist, cand_idx, list_stride, query_stride, q, lists, k, o
     if out is None:
         out = (torch.empty((q, k), dtype=torch.float32, device=cand_dist.device),
                torch.empty((q, k), dtype=torch.int32, device=cand_dist.device))
-    _check(lib().bitsknn_merge(_p(cand_dist), _p(cand_idx), list_stride, query_stride, q, lists, k, _p(out[0]),
-                               _p(out[1]), _stream()))
+    _check(lib().bitsknn_merge_lists(_p(cand_dist), _p(cand_idx), list_stride, query_stride, q, lists, k,
+                                     1 if sorted_lists else 0, _p(out[0]), _p(out[1]), _stream()))
+    return out
+
+
+def refine(points, queries, cand_idx, k, index_base=0, out=None):
+    """Exact FP32 re-ranking of (q, candidates) int32 candidate indices -> the k nearest by it."""
+    import torch
+    _device_check(points, torch.float32, "points")
+    _device_check(queries, torch.float32, "queries")
+    _device_check(cand_idx, torch.int32, "cand_idx")
+    assert points.is_contiguous() and queries.is_contiguous()
+    n, dim = points.shape
+    q, cands = cand_idx.shape
+    if out is None:
+        out = (torch.empty((q, k), dtype=torch.float32, device=points.device),
+               torch.empty((q, k), dtype=torch.int32, device=points.device))
+    _check(lib().bitsknn_refine(_p(points), _p(queries), n, q, dim, _p(cand_idx), cand_idx.stride(0) if q > 1 else cands,
+                                cands, index_base, k, _p(out[0]), _p(out[1]), _stream()))
     return out
 
 

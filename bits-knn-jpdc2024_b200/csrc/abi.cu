@@ -32,7 +32,6 @@ tuning_entry g_tuning[] = {
     {"select.stage_bytes", 0, 0, 65536},
     {"select.stages", 0, 0, 8},
     {"select.merge_at", 0, 0, 100},
-    {"select.auto_split", 1, 0, 1},
     {"select.wide_block", 1, 0, 1},
     {"select.filter", 1, 0, 1},
     {"select.unroll", 0, 0, 4},
@@ -199,11 +198,23 @@ extern "C" int bitsknn_set_tuning(const char* key, int value)
                 return fail(BITSKNN_ERR_INVALID_ARGUMENT, "tuning value %d for '%s' outside [%d, %d]", value, key,
                             entry.min, entry.max);
             }
+            if (std::strcmp(key, "select.unroll") == 0 && value != 0 && value != 2 && value != 4)
+            {
+                return fail(BITSKNN_ERR_INVALID_ARGUMENT, "tuning value %d for 'select.unroll': only 0, 2 and 4 exist",
+                            value);
+            }
             entry.value = value;
             return BITSKNN_OK;
         }
     }
     return fail(BITSKNN_ERR_INVALID_ARGUMENT, "unknown tuning key '%s'", key);
+}
+
+extern "C" const char* bitsknn_tuning_key(int index)
+{
+    using namespace bitsknn;
+    constexpr int count = static_cast<int>(sizeof(g_tuning) / sizeof(g_tuning[0]));
+    return index >= 0 && index < count ? g_tuning[index].key : nullptr;
 }
 
 extern "C" int bitsknn_get_tuning(const char* key, int* value)

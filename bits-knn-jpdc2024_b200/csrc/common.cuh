@@ -51,8 +51,22 @@ int device_sm_count();
 
 // Merge of `lists` candidate lists of `kin` pairs per query (pair j of list l of query i at
 // [l * list_stride + i * query_stride + j]) into the `k` smallest pairs; `bias` (nullable, one
-// value per query) is added to the reported distances.  Defined in select.cu.
+// value per query) is added to the reported distances.  `input` says whether every list arrives
+// ascending (then only the merging phases of the sorting network run).  Defined in merge.cu.
+enum class merge_input
+{
+    unsorted,
+    sorted,
+    rerank
+};
 int merge_lists(const float* cand_dist, const int32_t* cand_idx, int64_t list_stride, int64_t query_stride, int64_t q,
-                int lists, int kin, int k, const float* bias, float* out_dist, int32_t* out_idx, cudaStream_t stream);
+                int lists, int kin, int k, const float* bias, float* out_dist, int32_t* out_idx, merge_input input,
+                cudaStream_t stream);
+// The same over candidate indices alone: every candidate's distance is recomputed from the vectors
+// (FP32 chain of (y - x)^2 in coordinate order) and the k smallest pairs by that distance are
+// reported.  Candidate index = index_base + row of `points`; PAD_IDX entries are skipped.
+int rerank_lists(const int32_t* cand_idx, int64_t list_stride, int64_t query_stride, int64_t q, int lists, int kin,
+                 int k, const float* points, const float* queries, int64_t n, int dim, int32_t index_base,
+                 float* out_dist, int32_t* out_idx, cudaStream_t stream);
 
 } // namespace bitsknn

@@ -25,8 +25,10 @@
 //            e % 32).  The acceptance bound of a query is the smallest of: its group's radius,
 //            the partner group's radius, and the larger of the two lists' entries
 //            ceil(k / 2) - 1 (the lists cover different points, so k pairs lie at or below it).
-// After the scan the 2 * parts lists of every query are merged by merge_lists(), which also adds
-// the query norm so that the reported distance is |x|^2 + |y|^2 - 2 x.y.
+// After the scan the 2 * parts lists of every query hold its candidates by tensor-core distance;
+// rerank_lists() recomputes every candidate's distance as the exact FP32 chain of (y - x)^2 and
+// reports the k smallest pairs by that, so the rounding of the tensor-core inputs only decides
+// which pairs are looked at (with an allowance in the acceptance bound), not what is reported.
 // Role of the reference's fused_tc_kernel (detail/fused_tc_kernel.cuh:177-445, wmma based and
 // "suboptimal" by its authors' note in src/gen.py:45), rebuilt on tcgen05 / TMEM / TMA.
 #include <algorithm>
@@ -64,8 +66,11 @@ struct ftc_params
     int stages;
     int parts;
     int64_t tiles;
-    int k;
+    int k;            // list entry k - 1 is a list's radius (the reported k plus a margin)
     int32_t index_base;
+    const float* qnorm;    // [q] squared norms of the queries
+    const float* max_norm; // largest squared norm of a point
+    float slack;           // relative error bound of the tensor-core distance (of |x|^2 + |y|^2)
     int* status;
 };
 
@@ -172,13 +177,17 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
         float h_d = INFINITY; // distance of entry ceil(k / 2) - 1 of this (group, query)'s list
         int cnt = 0;
         bool has_list = false;
+        // What a tensor-core distance may be off by (the rounding of the split images and of the
+        // accumulation grow with the norms, not with the distance): candidates are kept up to this
+        // far beyond the k-th distance found so far, and the exact re-ranking after the scan decides.
+        const float slack_d = live ? p.slack * (p.qnorm[gq] + *p.max_norm) : 0.0F;
 
         // Upper bound of the query's true k-th distance: each group's own radius, and the larger
         // of the two groups' entries ceil(k / 2) - 1 (the two lists cover different points, so at
-        // least k pairs lie at or below it).
+        // least k pairs lie at or below it) plus the error allowance.
         auto bound = [&]() {
             const int other = (group ^ 1) * TILE_M + qrow;
-            return fminf(fminf(r_d, rad[other]), fmaxf(h_d, hlf[other]));
+            return fminf(fminf(r_d, rad[other]), fmaxf(h_d, hlf[other]) + slack_d);
         };
 
         // Folds the buffers of the queries whose lanes are set in `mask` into their lists.
@@ -344,7 +353,8 @@ struct ftc_layout
     int nkb;     // 128-byte K blocks per row
     int kl;
     int parts;
-    size_t off_pn, off_qn, off_p, off_q, off_ld, off_lx, total;
+    int k_scan;  // list position of the radius during the scan: k plus a margin, at most kl
+    size_t off_pn, off_qn, off_max, off_p, off_q, off_ld, off_lx, total;
 };
 
 ftc_layout ftc_layout_of(int64_t n, int64_t q, int dim, int k, bool bf16)
@@ -357,6 +367,10 @@ ftc_layout ftc_layout_of(int64_t n, int64_t q, int dim, int k, bool bf16)
     l.nsteps = img.nsteps;
     l.nkb = img.nkb;
     l.kl = k <= 32 ? 32 : (k <= 64 ? 64 : (k <= 128 ? 128 : 256));
+    // The lists are longer than k anyway; the scan keeps a few more pairs than asked for inside
+    // them (a quarter more, at least four) so that a neighbour whose tensor-core distance came out
+    // a little too large is still a candidate when the exact re-ranking decides.
+    l.k_scan = std::min(l.kl, k + std::max(4, k / 4));
     const int64_t nqb = (q + TILE_M - 1) / TILE_M;
     const int64_t tiles = (n + TILE_N - 1) / TILE_N;
     // every extra part is one more pair of lists per query that has to find its own radius, so
@@ -372,7 +386,8 @@ ftc_layout ftc_layout_of(int64_t n, int64_t q, int dim, int k, bool bf16)
     const size_t esz = bf16 ? 2 : 4;
     l.off_pn = 0;
     l.off_qn = align256(static_cast<size_t>(n) * 4);
-    l.off_p = l.off_qn + align256(static_cast<size_t>(q) * 4);
+    l.off_max = l.off_qn + align256(static_cast<size_t>(q) * 4);
+    l.off_p = l.off_max + 256;
     l.off_q = l.off_p + align256(static_cast<size_t>(n) * l.dim_pad * esz);
     l.off_ld = l.off_q + align256(static_cast<size_t>(q) * l.dim_pad * esz);
     const size_t lists = static_cast<size_t>(l.parts) * 2 * static_cast<size_t>(q) * l.kl;
@@ -399,10 +414,12 @@ int run_ftc(const float* points, const float* queries, int64_t n, int64_t q, int
     const ftc_layout l = ftc_layout_of(n, q, dim, k, BF16);
     float* pn = reinterpret_cast<float*>(ws + l.off_pn);
     float* qn = reinterpret_cast<float*>(ws + l.off_qn);
+    float* pmax = reinterpret_cast<float*>(ws + l.off_max);
     void* cp = ws + l.off_p;
     void* cq = ws + l.off_q;
+    BITSKNN_CUDA_TRY(cudaMemsetAsync(pmax, 0, sizeof(float), stream));
     tc_prepare_kernel<BF16>
-        <<<static_cast<unsigned>((n + 7) / 8), 256, 0, stream>>>(points, n, dim, l.dim_pad, l.split, 1, 1, cp, pn);
+        <<<static_cast<unsigned>((n + 7) / 8), 256, 0, stream>>>(points, n, dim, l.dim_pad, l.split, 1, 1, cp, pn, pmax);
     tc_prepare_kernel<BF16>
         <<<static_cast<unsigned>((q + 7) / 8), 256, 0, stream>>>(queries, q, dim, l.dim_pad, l.split, 0, 1, cq, qn);
     BITSKNN_CUDA_TRY(cudaGetLastError());
@@ -417,8 +434,14 @@ int run_ftc(const float* points, const float* queries, int64_t n, int64_t q, int
     p.hs = l.hs;
     p.parts = l.parts;
     p.tiles = (n + TILE_N - 1) / TILE_N;
-    p.k = k;
+    p.k = l.k_scan;
     p.index_base = index_base;
+    p.qnorm = qn;
+    p.max_norm = pmax;
+    // split images: the dropped lo.lo products and the accumulation stay below 2^-16 (BF16) /
+    // 2^-21 (TF32) of |x|^2 + |y|^2 in every measured case; four times that is allowed.  Plainly
+    // rounded images (long vectors) carry the rounding of both inputs.
+    p.slack = l.split != 0 ? (BF16 ? 0x1p-14F : 0x1p-19F) : (BF16 ? 0x1p-8F : 0x1p-11F);
     p.status = device_status_word();
     if (p.status == nullptr)
     {
@@ -478,10 +501,11 @@ int run_ftc(const float* points, const float* queries, int64_t n, int64_t q, int
     {
         return rc;
     }
-    // merge the 2 * parts lists of every query; the query norm turns the partial distance into
-    // the full squared distance
-    return merge_lists(p.list_d, p.list_x, static_cast<int64_t>(q) * l.kl, l.kl, q, 2 * l.parts, l.kl, k, qn, out_dist,
-                       out_idx, stream);
+    // The 2 * parts lists of every query hold its candidates ranked by tensor-core distances.  The
+    // result is decided by the exact FP32 distance of every candidate (one FMA chain of (y - x)^2
+    // per pair, as the FP32 path computes it), which is also the distance reported.
+    return rerank_lists(p.list_x, static_cast<int64_t>(q) * l.kl, l.kl, q, 2 * l.parts, l.kl, k, points, queries, n, dim,
+                        index_base, out_dist, out_idx, stream);
 }
 
 } // namespace

@@ -537,7 +537,7 @@ int fused_tiled_launch(const float* points, const float* queries, int64_t n, int
         return rc;
     }
     return merge_lists(p.list_d, p.list_x, static_cast<int64_t>(q) * l.kl, l.kl, q, l.parts, l.kl, k, nullptr, out_dist,
-                       out_idx, stream);
+                       out_idx, merge_input::sorted, stream);
 }
 
 } // namespace bitsknn

@@ -1,4 +1,5 @@
-// `bits` top-k selection over a precomputed distance matrix, and the candidate-list merge.
+// `bits` top-k selection over a precomputed distance matrix (the candidate-list merge of the
+// split-row form is in merge.cu).
 //
 // One thread block scans one row (or one slice of a row).  The row is streamed from HBM by
 // 1-D bulk asynchronous copies (TMA engine, no tensor map) into a ring of shared-memory
@@ -556,71 +557,6 @@ __global__ void __launch_bounds__(THREADS) select_kernel(const select_params p)
     }
 }
 
-// Merge of candidate lists: one block per query folds lists*k candidates, L at a time.
-template <int THREADS, int IPT>
-__global__ void __launch_bounds__(THREADS)
-    merge_kernel(const float* __restrict__ cand_dist, const int32_t* __restrict__ cand_idx, int64_t list_stride,
-                 int64_t query_stride, int lists, int kin, int k, const float* __restrict__ bias,
-                 float* __restrict__ out_dist, int32_t* __restrict__ out_idx)
-{
-    constexpr int L = THREADS * IPT;
-    __shared__ float sd[L];
-    __shared__ int sx[L];
-    const int tid = threadIdx.x;
-    const int64_t query = blockIdx.x;
-    const int total = lists * kin; // `kin` candidates per list, the `k` smallest pairs are reported
-
-    float ld[IPT];
-    int lx[IPT];
-#pragma unroll
-    for (int r = 0; r < IPT; ++r)
-    {
-        ld[r] = INFINITY;
-        lx[r] = PAD_IDX;
-    }
-    for (int round = 0; round < total; round += L)
-    {
-        float cd[IPT];
-        int cx[IPT];
-#pragma unroll
-        for (int r = 0; r < IPT; ++r)
-        {
-            const int ci = round + r * THREADS + tid;
-            cd[r] = INFINITY;
-            cx[r] = PAD_IDX;
-            if (ci < total)
-            {
-                const int l = ci / kin;
-                const int j = ci - l * kin;
-                const int64_t at = l * list_stride + query * query_stride + j;
-                cd[r] = cand_dist[at];
-                cx[r] = cand_idx[at];
-            }
-        }
-        block_fold<THREADS, IPT>(ld, lx, cd, cx, sd, sx, tid);
-    }
-#pragma unroll
-    for (int r = 0; r < IPT; ++r)
-    {
-        const int e = tid * IPT + r;
-        if (e < k)
-        {
-            // `bias` (optional, one value per query) is added to every reported distance
-            out_dist[query * k + e] = bias != nullptr ? ld[r] + bias[query] : ld[r];
-            out_idx[query * k + e] = lx[r] == PAD_IDX ? e : lx[r];
-        }
-    }
-}
-
-} // namespace
-
-// Merge `lists` lists of `kin` pairs per query into the `k` smallest (library-internal; see common.cuh).
-int merge_lists(const float* cd, const int32_t* cx, int64_t list_stride, int64_t query_stride, int64_t q, int lists,
-                int kin, int k, const float* bias, float* od, int32_t* ox, cudaStream_t stream);
-
-namespace
-{
-
 size_t select_smem_bytes(int L, int stage_floats, int stages)
 {
     return static_cast<size_t>(stages) * stage_floats * 4 + static_cast<size_t>(L) * 8 + MAX_STAGES * 8 +
@@ -648,6 +584,12 @@ int launch_select(select_params p, int64_t vrows, cudaStream_t stream)
     int unroll = tuning_value("select.unroll", 0);
     unroll = unroll != 0 ? unroll : 2;
     auto kernel = unroll == 2 ? select_kernel<THREADS, IPT, 2> : select_kernel<THREADS, IPT, 4>;
+    if (smem > 227U * 1024U)
+    {
+        return fail(BITSKNN_ERR_INVALID_ARGUMENT,
+                    "select.stage_bytes x select.stages = %d x %d needs %zu bytes of shared memory per block; "
+                    "the limit is %u", p.stage_floats * 4, p.stages, smem, 227U * 1024U);
+    }
     BITSKNN_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     kernel<<<static_cast<unsigned>(vrows), THREADS, smem, stream>>>(p);
     BITSKNN_CUDA_TRY(cudaGetLastError());
@@ -680,41 +622,14 @@ int dispatch_select(const select_params& p, int64_t vrows, cudaStream_t stream)
     return wide != 0 ? launch_select<1024, 2>(p, vrows, stream) : launch_select<256, 8>(p, vrows, stream);
 }
 
-template <int IPT>
-int launch_merge(const float* cd, const int32_t* cx, int64_t list_stride, int64_t query_stride, int64_t q, int lists,
-                 int kin, int k, const float* bias, float* od, int32_t* ox, cudaStream_t stream)
-{
-    merge_kernel<SELECT_THREADS, IPT><<<static_cast<unsigned>(q), SELECT_THREADS, 0, stream>>>(
-        cd, cx, list_stride, query_stride, lists, kin, k, bias, od, ox);
-    BITSKNN_CUDA_TRY(cudaGetLastError());
-    return BITSKNN_OK;
-}
-
 int dispatch_merge(const float* cd, const int32_t* cx, int64_t list_stride, int64_t query_stride, int64_t q, int lists,
                    int k, float* od, int32_t* ox, cudaStream_t stream)
 {
-    return merge_lists(cd, cx, list_stride, query_stride, q, lists, k, k, nullptr, od, ox, stream);
+    // the slices' lists arrive ascending
+    return merge_lists(cd, cx, list_stride, query_stride, q, lists, k, k, nullptr, od, ox, merge_input::sorted, stream);
 }
 
 } // namespace
-
-int merge_lists(const float* cd, const int32_t* cx, int64_t list_stride, int64_t query_stride, int64_t q, int lists,
-                int kin, int k, const float* bias, float* od, int32_t* ox, cudaStream_t stream)
-{
-    if (k <= 256)
-    {
-        return launch_merge<1>(cd, cx, list_stride, query_stride, q, lists, kin, k, bias, od, ox, stream);
-    }
-    if (k <= 512)
-    {
-        return launch_merge<2>(cd, cx, list_stride, query_stride, q, lists, kin, k, bias, od, ox, stream);
-    }
-    if (k <= 1024)
-    {
-        return launch_merge<4>(cd, cx, list_stride, query_stride, q, lists, kin, k, bias, od, ox, stream);
-    }
-    return launch_merge<8>(cd, cx, list_stride, query_stride, q, lists, kin, k, bias, od, ox, stream);
-}
 
 namespace
 {
@@ -878,6 +793,11 @@ extern "C" int bitsknn_select_split(const float* d_dist, int64_t ld, const int32
     {
         return fail(BITSKNN_ERR_INVALID_ARGUMENT, "slices * k = %lld exceeds 65536", static_cast<long long>(s) * k);
     }
+    if (q * s > 0x7fffffffLL)
+    {
+        return fail(BITSKNN_ERR_INVALID_ARGUMENT, "q * slices = %lld row slices exceed the grid limit of 2^31 - 1",
+                    static_cast<long long>(q) * s);
+    }
     const size_t need = static_cast<size_t>(q) * s * k * 8U;
     if (d_workspace == nullptr || workspace_bytes < need)
     {
@@ -1025,32 +945,4 @@ extern "C" int bitsknn_select_split_static(const float* d_dist, int64_t ld, cons
     }
     return dispatch_merge(cand_dist, cand_idx, k, static_cast<int64_t>(splits) * k, q, splits, k, d_out_dist,
                           d_out_idx, cs);
-}
-
-extern "C" int bitsknn_merge(const float* d_cand_dist, const int32_t* d_cand_idx, int64_t list_stride,
-                             int64_t query_stride, int64_t q, int lists, int k, float* d_out_dist,
-                             int32_t* d_out_idx, bitsknn_stream_t stream)
-{
-    if (d_cand_dist == nullptr || d_cand_idx == nullptr || d_out_dist == nullptr || d_out_idx == nullptr)
-    {
-        return fail(BITSKNN_ERR_INVALID_ARGUMENT, "null pointer argument");
-    }
-    if (q < 0 || lists < 1 || list_stride < 0 || query_stride < 0 || q > 0x7fffffffLL)
-    {
-        return fail(BITSKNN_ERR_INVALID_ARGUMENT, "invalid sizes: q=%lld lists=%d", static_cast<long long>(q), lists);
-    }
-    if (k < 1 || k > BITSKNN_MAX_K)
-    {
-        return fail(BITSKNN_ERR_UNSUPPORTED_K, "Unsupported k value: %d", k);
-    }
-    if (static_cast<int64_t>(lists) * k > 65536)
-    {
-        return fail(BITSKNN_ERR_INVALID_ARGUMENT, "lists * k = %lld exceeds 65536", static_cast<long long>(lists) * k);
-    }
-    if (q == 0)
-    {
-        return BITSKNN_OK;
-    }
-    return dispatch_merge(d_cand_dist, d_cand_idx, list_stride, query_stride, q, lists, k, d_out_dist, d_out_idx,
-                          static_cast<cudaStream_t>(stream));
 }

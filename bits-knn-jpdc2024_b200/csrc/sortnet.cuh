@@ -131,6 +131,23 @@ struct sort_phases
     }
 };
 
+// Phases 2 * KMIN, ..., K of the full sort: what is left to do when the array already consists of
+// sorted runs of KMIN elements whose directions are those the phase KMIN would have left (run j
+// ascending when j is even, descending when odd; all flipped when `desc`).
+template <int THREADS, int IPT, int K, int KMIN>
+struct sort_phases_from
+{
+    static __device__ __forceinline__ void run(float (&d)[IPT], int (&x)[IPT], bool desc, float* sd, int* sx,
+                                               int tid)
+    {
+        if constexpr (K >= 2 * KMIN)
+        {
+            sort_phases_from<THREADS, IPT, K / 2, KMIN>::run(d, x, desc, sd, sx, tid);
+            merge_steps<THREADS, IPT, K, K / 2>::run(d, x, desc, sd, sx, tid);
+        }
+    }
+};
+
 // Sorts the block-wide array (ascending, or descending when `desc`).
 template <int THREADS, int IPT>
 __device__ __forceinline__ void block_sort(float (&d)[IPT], int (&x)[IPT], bool desc, float* sd, int* sx, int tid)

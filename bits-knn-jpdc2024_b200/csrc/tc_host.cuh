@@ -41,7 +41,8 @@ constexpr int MAX_KB = 8;          // K blocks of 128 bytes in the resident quer
 // comes out of the tensor core and the consumer only has to compare.
 template <bool BF16>
 __global__ void tc_prepare_kernel(const float* __restrict__ src, int64_t rows, int dim, int ext_pad, int split,
-                                  int is_points, int norm_cols, void* __restrict__ dst, float* __restrict__ norms)
+                                  int is_points, int norm_cols, void* __restrict__ dst, float* __restrict__ norms,
+                                  float* __restrict__ max_norm = nullptr)
 {
     const int lane = threadIdx.x & 31;
     const int64_t row = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
@@ -139,6 +140,15 @@ __global__ void tc_prepare_kernel(const float* __restrict__ src, int64_t rows, i
     if (lane == 0)
     {
         norms[row] = nrm;
+        if (max_norm != nullptr)
+        {
+            // largest squared norm of all rows (non-negative floats order like their bit patterns);
+            // the plain read first keeps all but a few rows away from the atomic
+            if (nrm > *reinterpret_cast<volatile float*>(max_norm))
+            {
+                atomicMax(reinterpret_cast<int*>(max_norm), __float_as_int(nrm));
+            }
+        }
     }
 }
 

@@ -63,13 +63,14 @@ int bitsknn_selftest_bounded_wait(bitsknn_stream_t stream);
 
 /* Tuning knobs (launch shapes).  Unknown keys return BITSKNN_ERR_INVALID_ARGUMENT.
  *   "select.stage_bytes"  bytes per shared-memory stage of the row stream (multiple of 4096;
- *                         0 = automatic, the default)
+ *                         0 = automatic, the default); stages x stage_bytes beyond the 227 KiB a
+ *                         block may use makes the next selection return INVALID_ARGUMENT
  *   "select.stages"       stages in the ring (2..8; 0 = automatic, the default)
  *   "select.merge_at"     merge the candidate buffer when it holds at least this percentage
  *                         of its capacity (1..100; 100 = only when full, like the reference;
  *                         0 = automatic, the default: 50 for lists of up to 256 pairs, else 75)
  *   "select.unroll"       128-bit vectors per thread examined under one warp vote (0 = automatic,
- *                         2 or 4)
+ *                         2 or 4; other values are rejected)
  *   "select.wide_block"   1 = 512-thread blocks for 256 < k <= 1024 and 1024-thread blocks beyond
  *                         (default), 0 = 256-thread blocks
  *   "select.filter"       0 = bitsknn_select buffers, sorts and merges every value (no radius
@@ -84,6 +85,8 @@ int bitsknn_selftest_bounded_wait(bitsknn_stream_t stream);
  * kernels (src/topk/singlepass/bits_knn.cu:98-114); here they are hints. */
 int bitsknn_set_tuning(const char* key, int value);
 int bitsknn_get_tuning(const char* key, int* value);
+/* The index-th registered tuning key (0, 1, ...), NULL past the last one. */
+const char* bitsknn_tuning_key(int index);
 
 /* ---------------------------------------------------------------------------------------
  * `bits` top-k selection over a precomputed distance matrix.
@@ -139,10 +142,33 @@ int bitsknn_select_split_static(const float* d_dist, int64_t ld, const int32_t* 
 /* Merge of `lists` candidate lists per query into the k smallest pairs (candidate j of
  * list l of query i is at [l * list_stride + i * query_stride + j], strides in elements).
  * Pass 2 of the reference's split-row scheme (bits_knn.cu:170-183) and the merge step of
- * the database-sharded search (lists = number of shards). lists * k <= 65536. */
+ * the database-sharded search (lists = number of shards). lists * k <= 65536.
+ * bitsknn_merge_lists with sorted_lists != 0 promises that every list is ascending in the pair
+ * order (what the selection and fused entry points write, padding (+inf, INT32_MAX) at the end):
+ * then only the merging phases of the sorting network run.  bitsknn_merge makes no assumption. */
 int bitsknn_merge(const float* d_cand_dist, const int32_t* d_cand_idx, int64_t list_stride,
                   int64_t query_stride, int64_t q, int lists, int k, float* d_out_dist,
                   int32_t* d_out_idx, bitsknn_stream_t stream);
+int bitsknn_merge_lists(const float* d_cand_dist, const int32_t* d_cand_idx, int64_t list_stride,
+                        int64_t query_stride, int64_t q, int lists, int k, int sorted_lists,
+                        float* d_out_dist, int32_t* d_out_idx, bitsknn_stream_t stream);
+
+/* Exact re-ranking of candidates: for every query the squared distance to each of its
+ * `candidates` candidate points is recomputed in FP32 exactly as BITSKNN_L2_EXACT does (one
+ * FMA chain of (y - x)^2 over the coordinates in order, the reference's l2_ops,
+ * include/bits/distance/abstract_gemm.cuh:79-93) and the k smallest (distance, index) pairs by
+ * that distance are reported.  Meant for the candidates a reduced-precision search returns
+ * (a selection with k + margin over a TF32 / BF16 distance matrix): the result then carries the
+ * distances of the FP32 path, and a neighbour that the rounded distances ranked a few places too
+ * low is put back in its place.  The tensor-core modes of bitsknn_fused run this step themselves.
+ * The reference has no such step; its tensor-core kernels report their rounded distances
+ * (include/bits/topk/singlepass/detail/fused_tc_kernel.cuh:346,440).
+ *   d_cand_idx   int32[q][ld_cand]: candidate j of query i = index_base + row of d_points;
+ *                distinct per query; entries outside [index_base, index_base + n) are skipped
+ *   candidates   candidates per query taken from each row (1 ... 65536), k <= BITSKNN_MAX_K */
+int bitsknn_refine(const float* d_points, const float* d_queries, int64_t n, int64_t q, int dim,
+                   const int32_t* d_cand_idx, int64_t ld_cand, int candidates, int32_t index_base, int k,
+                   float* d_out_dist, int32_t* d_out_idx, bitsknn_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------
  * Squared-L2 distance matrix, GEMM form.
@@ -180,9 +206,11 @@ int bitsknn_l2(const float* d_points, const float* d_queries, int64_t n, int64_t
  *   mode        BITSKNN_L2_PARTIAL (FP32 FFMA, bit-exact with the reference's fused kernel:
  *               reported distances are |x|^2 - 2 x.y), BITSKNN_L2_EXACT (FP32, sum (x-y)^2), or
  *               BITSKNN_L2_TF32 / BITSKNN_L2_BF16: the distance tile is produced by tcgen05
- *               tensor-core MMAs in tensor memory and consumed from there (reported distances
- *               are |x|^2 + |y|^2 - 2 x.y; checked against the FP32 path by recall@k and k-th
- *               distance error, not bit-exact)
+ *               tensor-core MMAs in tensor memory and consumed from there; the pairs that survive
+ *               the scan are re-ranked by their exact FP32 distance (see bitsknn_refine), which is
+ *               what is reported: sum (x-y)^2 as in BITSKNN_L2_EXACT.  The rounded tensor-core
+ *               distances only decide which pairs are candidates, so the result is checked against
+ *               the FP32 path by recall@k and k-th distance error rather than bit for bit
  *   k           1 <= k <= BITSKNN_FUSED_MAX_K
  *   index_base  added to every reported index (shard base of a sharded database)
  *   d_workspace bitsknn_fused_workspace_bytes() bytes, 256-byte aligned.  Required by the
