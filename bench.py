@@ -1,24 +1,28 @@
-"""Benchmark of the `bits` top-k selection hot path (and its CPU baseline).
+"""Benchmark of the k-NN hot paths (and their CPU baselines).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--k 256] [--impl reference]
 
-Workload (the reference's selection sweep shape): a float32 distance matrix of q=1024 rows
-by n=2^20 columns (4 GiB) per GPU, Uniform[0,1) from a seeded device generator (synthetic:
+Headline workload (the reference's selection sweep shape): a float32 distance matrix of q=1024
+rows by n=2^20 columns (4 GiB) per GPU, Uniform[0,1) from a seeded device generator (synthetic:
 the reference itself only ever measures generated data), k=256 by default.  One step = one
-pass of the selection over the whole matrix.  With N GPUs the matrix is database-sharded:
-every rank holds its own q x n column block of a q x (N*n) matrix (weak scaling), selects
-its local top-k, the candidates are all-gathered over NCCL and merged on every rank; the K timed
-searches run as a stream (`ShardedSearch.submit_select` / `drain`): the all-gather of one search
-is in flight while the next local selection runs, and all K are complete inside the timed region.
+pass of the `bits` selection over the whole matrix.  With N GPUs the matrix is database-sharded:
+every rank holds its own q x n column block of a q x (N*n) matrix (weak scaling), selects its
+local top-k, and the library (`bitsknn_sharded_*`) all-gathers the candidates over NCCL and merges
+them on every rank; the K timed searches run in the submit form: the exchange and merge of one
+search overlap the local selection of the next, and all K are complete inside the timed region.
 
-The JSON line carries: `value` (distances/s with the matrix resident in HBM), `e2e` (same
-metric through the C ABI with HOST buffers: pinned host -> device copy of the matrix, the
-selection, and the device -> host copy of the result, all inside the timed region),
-`e2e_knn` (the reference binary's own flow: host points and queries -> device, distance matrix
-made on the device, selection, result -> host),
-`roofline` (algorithmic bytes / CUDA-event kernel time against the measured HBM peak),
-`cpu_baseline` (the CPU port of the reference's OpenMP heap selection, timed on this host)
-and `sweep` (other k and the adversarial descending-row input, kernel time only).
+The JSON line carries, besides the contract's keys:
+  roofline      select_kernel: algorithmic bytes / CUDA-event kernel time against the measured HBM peak
+  kernels       the same per kernel (select, merge, rerank, l2_fp32, l2_tc, fused_tiled, fused_tc)
+  e2e           the selection through the C ABI from a pinned HOST matrix (copies inside the timed region)
+  e2e_knn       the reference binary's own flow: host points and queries -> device, distance matrix
+                made on the device, selection, result -> host
+  cpu_baseline  the reference's CPU selection timed on this host; knn_cpu_baseline: the CPU k-NN flow
+  sweep         other k and the adversarial descending rows
+  c3 / c4       distances + selection (q=8192, k=64) and the fused small-dimension grid (q=2^16),
+                every tensor-core number with its recall@k and k-th-distance error against FP32
+  knn_sharded   database-sharded fused k-NN, weak (2^24 points per GPU) and strong (2^27 points split
+                over the GPUs), each with an on-device check against the unsharded search
 
 `--impl reference` times the reference's CPU selection alone (oracle/_ref when it was
 compiled, else the oracle port) and prints the same line shape with "impl": "reference".
@@ -41,19 +45,31 @@ Q = 1024
 N_COLS = 1 << 20
 METRIC = "bits top-k selection throughput"
 UNIT = "distances/s"
-# the reference's published H100-PCIe numbers for this shape (q=1024, n=2^20), by k:
-# plots/kselection-hopper01-108424.csv lines 13, 45, 61, 106
 # ncu: (2.4831 GB read + 5.6 MB written) / 592 rows, k = 256
 NCU_DRAM_BYTES_PER_ROW = (2.4831e9 + 5.6e6) / 592
+# the reference's published H100-PCIe numbers for this shape (q=1024, n=2^20), by k:
+# plots/kselection-hopper01-108424.csv lines 13, 45, 61, 106
 PUBLISHED_H100 = {32: 4.781e11, 128: 4.637e11, 256: 4.674e11, 2048: 3.599e11}
+E2E_KNN_DIM = 32
+FP32_LANES_PER_SM = 128
 
 
 def measured_peaks():
+    """HBM GB/s, dense bf16 TFLOP/s (burst: kernels timed alone), SM max MHz, and where they come from."""
     path = ROOT / "MEASURED_PEAKS.json"
     if path.exists():
         data = json.loads(path.read_text())
-        return float(data["hbm_gbs"]), "measured"
-    return 6650.0, "fallback"
+        return {"hbm_gbs": float(data["hbm_gbs"]), "bf16_tflops": float(data["bf16_tflops"]),
+                "sm_max_mhz": float(data.get("sm_max_mhz", 1965.0)), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "sm_max_mhz": 1965.0, "source": "fallback"}
+
+
+def host_threads():
+    """Host threads this process may use (the affinity mask, not the machine's core count)."""
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
 
 
 class ClockSampler:
@@ -117,8 +133,10 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
+# ---- CPU baselines -------------------------------------------------------------------------
+
 def cpu_selection_baseline(host_matrix, k, budget_s=20.0):
-    """Times the CPU port of the reference's OpenMP heap selection on a bounded row sample."""
+    """Times the reference's OpenMP heap selection on a bounded row sample."""
     import numpy as np
     from oracle import oracle
     oracle.build()
@@ -153,79 +171,288 @@ def cpu_selection_baseline(host_matrix, k, budget_s=20.0):
                       f"matrix, k={k}, OpenMP heap selection ({what}), median of {len(times)} runs"}
 
 
-def knn_section(bk, dev):
-    """Fused k-NN (the other hot path): n = 2^20 points, q = 2^14 queries, Uniform[0,1), kernel
-    time by CUDA events.  FP32 is the bit-exact mode; tf32 / bf16 run on tcgen05.  For the
-    largest case the unfused pipelines (distance GEMM + bits selection, in query batches) and,
-    where it was compiled, the reference's own fused-cache kernel are timed beside it."""
-    import torch
+def cpu_knn_baseline(n, dim, k, queries, seed=42, budget_s=12.0):
+    """The CPU k-NN flow (distance FMA chains + max-heap per query, OpenMP over the queries: the
+    port of the reference's `parallel` algorithm with its distance computed on the CPU) on a
+    bounded query subset against n points.  Returns queries/s and distances/s."""
+    import numpy as np
+    from oracle import oracle
+    oracle.build()
+    cores = oracle.num_threads()
+    rng = np.random.default_rng(seed)
+    points = rng.random((n, dim), dtype=np.float32)
+    qs = rng.random((queries, dim), dtype=np.float32)
+    oracle.knn_heap(points[: 1 << 14], qs[:cores], min(k, 1 << 14))  # warm the thread pool
+    times = []
+    spent = 0.0
+    while len(times) < 3 and spent < budget_s:
+        t0 = time.perf_counter()
+        oracle.knn_heap(points, qs, k)
+        times.append(time.perf_counter() - t0)
+        spent += times[-1]
+    best = statistics.median(times)
+    return {"queries_per_s": queries / best, "distances_per_s": queries * n / best, "cores": cores, "kind": "port",
+            "sample": f"{queries} queries against n={n} points of dim {dim}, k={k}, Uniform[0,1) seed {seed}: partial-L2 "
+                      f"FMA chains + per-query max-heap (port of the reference's CPU `parallel` flow), median of "
+                      f"{len(times)} runs"}
 
-    def timed(fn, reps):
+
+# ---- device helpers ---------------------------------------------------------------------------
+
+def timed_ms(fn, reps, warm=1):
+    import torch
+    for _ in range(warm):
         fn()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(reps):
-            fn()
-        e1.record()
-        torch.cuda.synchronize()
-        return e0.elapsed_time(e1) / reps
-
-    n, q = 1 << 20, 1 << 14
-    gen = torch.Generator(device=dev).manual_seed(42)
-    result = {"n": n, "q": q, "data": "Uniform[0,1) coordinates, seed 42", "cases": {}}
-    modes = (("fp32", bk.L2_PARTIAL), ("tf32", bk.L2_TF32), ("bf16", bk.L2_BF16))
-    for dim, k in ((16, 32), (64, 128)):
-        points = torch.rand((n, dim), generator=gen, device=dev)
-        queries = torch.rand((q, dim), generator=gen, device=dev)
-        out = (torch.empty((q, k), device=dev), torch.empty((q, k), dtype=torch.int32, device=dev))
-        for name, mode in modes:
-            ws = torch.empty(max(bk.fused_workspace_bytes(n, q, dim, k, mode), 256), dtype=torch.uint8, device=dev)
-            ms = timed(lambda: bk.fused(points, queries, k, mode=mode, out=out, workspace=ws), 1 if name == "fp32" else 3)
-            result["cases"][f"fused_{name}_dim{dim}_k{k}"] = {"ms": ms, "queries_per_s": q / (ms * 1e-3),
-                                                             "distances_per_s": q * n / (ms * 1e-3)}
-            del ws
-        # unfused: distance matrix for 2048 queries at a time (8 GiB), then the bits selection
-        qb = 2048
-        dist = torch.empty((qb, n), device=dev)
-        sel = (torch.empty((qb, k), device=dev), torch.empty((qb, k), dtype=torch.int32, device=dev))
-        for name, mode in (("fp32", bk.L2_PARTIAL), ("bf16", bk.L2_BF16)):
-            ws = torch.empty(max(bk.l2_workspace_bytes(n, qb, dim, mode), 256), dtype=torch.uint8, device=dev)
-
-            def unfused():
-                for b in range(0, q, qb):
-                    bk.l2(points, queries[b:b + qb], mode=mode, out=dist, workspace=ws)
-                    bk.select(dist, k, out=sel)
-
-            ms = timed(unfused, 1)
-            result["cases"][f"unfused_{name}_gemm_plus_bits_dim{dim}_k{k}"] = {"ms": ms, "queries_per_s": q / (ms * 1e-3)}
-            del ws
-        del dist
-        try:
-            from oracle import ref_select
-            if ref_select.available():
-                sub = 4096  # a quarter of the queries; the kernel is linear in q
-                _, _, sec = ref_select.fused_cache(points.cpu().numpy(), queries[:sub].cpu().numpy(), k,
-                                                   block_query_dim=1, dim_mult=1, repeats=1)
-                result["cases"][f"reference_fused_cache_dim{dim}_k{k}"] = {
-                    "ms": sec * 1e3 * (q / sub), "queries_per_s": sub / sec,
-                    "note": "the reference's fused-cache kernel (8,4,2 / block-query-dim 1 / dim-mult 1) compiled "
-                            f"from its sources, timed on {sub} queries and scaled to {q}"}
-        except Exception as err:
-            result["cases"][f"reference_fused_cache_dim{dim}_k{k}"] = {"unavailable": str(err)}
-        torch.cuda.empty_cache()
-    return result
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / reps
 
 
-def sharded_knn_section(bk, search, dev, rank, world, barrier, max_over_ranks):
-    """The sharded search of the largest configuration, one shard per GPU: every rank holds 2^24
-    points of dimension 64 (4 GiB; 8 ranks = the 2^27-point database), all 16384 queries, k = 128;
-    fused tensor-core search of the shard (bf16 split images), one all-gather of the candidates,
-    merge.  Queries per second of the whole job, device time, max over ranks."""
+def make_vectors(kind, n, q, dim, seed, dev):
+    """Uniform[0,1) coordinates, or 256 Gaussian clusters (sigma 0.05) around uniform centres."""
     import torch
-    n_shard, q, dim, k = 1 << 24, 1 << 14, 64, 128
+    gen = torch.Generator(device=dev).manual_seed(seed)
+    if kind == "uniform":
+        return (torch.rand((n, dim), generator=gen, device=dev), torch.rand((q, dim), generator=gen, device=dev))
+    centres = torch.rand((256, dim), generator=gen, device=dev)
+
+    def draw(count):
+        out = torch.empty((count, dim), device=dev)
+        step = 1 << 22
+        for b in range(0, count, step):
+            e = min(count, b + step)
+            pick = torch.randint(0, 256, (e - b,), generator=gen, device=dev)
+            out[b:e] = centres[pick] + 0.05 * torch.randn((e - b, dim), generator=gen, device=dev)
+        return out
+
+    return draw(n), draw(q)
+
+
+def quality(i_tc, d_tc, i_ex, d_ex):
+    """recall@k of the rows of i_tc against i_ex, and the largest relative error of the k-th distance."""
+    import torch
+    k = i_ex.shape[1]
+    a = torch.sort(i_tc, dim=1).values
+    b = torch.sort(i_ex, dim=1).values
+    pos = torch.searchsorted(b, a).clamp_(max=k - 1)
+    recall = (torch.gather(b, 1, pos) == a).sum().item() / a.numel()
+    rel = ((d_tc[:, -1] - d_ex[:, -1]).abs() / d_ex[:, -1].abs().clamp_min(1e-30)).max().item()
+    return {"recall": recall, "kth_rel_err": rel, "queries_compared": int(i_ex.shape[0])}
+
+
+def fp32_peak_tflops(mhz):
+    return 2.0 * FP32_LANES_PER_SM * 148 * mhz * 1e6 / 1e12
+
+
+def roofline_entry(kernel, ms, peaks, bytes_=None, flops=None, flop_peak=None, flop_peak_name=None, note=None):
+    """Roofline of one launch: the slower of bytes at the measured HBM bandwidth and FLOPs at the
+    stated peak decides the bound; frac = that ideal time / the measured kernel time."""
+    t_mem = (bytes_ / (peaks["hbm_gbs"] * 1e9)) if bytes_ else 0.0
+    t_flop = (flops / (flop_peak * 1e12)) if flops else 0.0
+    bound = "hbm" if t_mem >= t_flop else "flops"
+    out = {"kernel": kernel, "kernel_ms": ms, "bound": bound,
+           "frac": max(t_mem, t_flop) / (ms * 1e-3), "peak_source": peaks["source"]}
+    if bytes_:
+        out.update({"algorithmic_bytes": bytes_, "achieved_gbs": bytes_ / (ms * 1e-3) / 1e9, "hbm_peak_gbs": peaks["hbm_gbs"]})
+    if flops:
+        out.update({"algorithmic_flops": flops, "achieved_tflops": flops / (ms * 1e-3) / 1e12,
+                    "flop_peak_tflops": flop_peak, "flop_peak": flop_peak_name})
+    if note:
+        out["note"] = note
+    return out
+
+
+# ---- sections ------------------------------------------------------------------------------------
+
+def kernels_section(bk, dev, peaks, sm_mhz):
+    """One launch of every main kernel with the library's CUDA events around it, and its roofline."""
+    import torch
+    out = {}
+    fp32_peak = fp32_peak_tflops(peaks["sm_max_mhz"])
+    fp32_name = f"FP32 FFMA, 2 x 128 lanes x 148 SMs at the maximum SM clock {peaks['sm_max_mhz']:.0f} MHz"
+    bf16_name = "dense bf16 (cuBLAS burst figure); tf32 = half of it"
+    bk.set_tuning("profile.kernel_events", 1)
+    try:
+        n, dim, k = 1 << 20, 64, 128
+        # distance matrix kernels at q = 8192 (32 GiB matrix)
+        q = 8192
+        points, queries = make_vectors("uniform", n, q, dim, 42, dev)
+        dist = torch.empty((q, n), device=dev)
+        io_bytes = 4.0 * q * n + 4.0 * dim * (n + q)
+        for name, mode in (("l2_fp32_kernel", bk.L2_PARTIAL), ("l2_tc_kernel", bk.L2_BF16), ("l2_tc_kernel_tf32", bk.L2_TF32)):
+            ws = torch.empty(max(bk.l2_workspace_bytes(n, q, dim, mode), 256), dtype=torch.uint8, device=dev)
+            kname = name.replace("_tf32", "")
+            ms = statistics.median(_kernel_times(bk, lambda: bk.l2(points, queries, mode=mode, out=dist, workspace=ws), kname, 3))
+            flops = 2.0 * q * n * dim
+            peak = fp32_peak if mode == bk.L2_PARTIAL else (peaks["bf16_tflops"] if mode == bk.L2_BF16 else peaks["bf16_tflops"] / 2)
+            out[name] = roofline_entry(kname, ms, peaks, bytes_=io_bytes, flops=flops, flop_peak=peak,
+                                       flop_peak_name=fp32_name if mode == bk.L2_PARTIAL else bf16_name,
+                                       note=f"q={q} n=2^20 dim={dim}: matrix written once (4 q n bytes) + inputs read once")
+            del ws
+        # selection over that matrix (32 GiB: far beyond L2)
+        sel = (torch.empty((q, 64), device=dev), torch.empty((q, 64), dtype=torch.int32, device=dev))
+        ms = statistics.median(_kernel_times(bk, lambda: bk.select(dist, 64, out=sel), "select_kernel", 3))
+        out["select_kernel_q8192_k64"] = roofline_entry("select_kernel", ms, peaks, bytes_=4.0 * q * n + 8.0 * q * 64,
+                                                        note="q=8192 n=2^20 k=64 over the 32 GiB matrix above")
+        del dist, sel
+        torch.cuda.empty_cache()
+        # fused kernels at q = 2^14
+        q = 1 << 14
+        points, queries = make_vectors("uniform", n, q, dim, 43, dev)
+        res = (torch.empty((q, k), device=dev), torch.empty((q, k), dtype=torch.int32, device=dev))
+        fused_bytes = 4.0 * dim * (n + q) + 8.0 * q * k
+        flops = 2.0 * q * n * dim
+        for name, mode, kname in (("fused_tiled_kernel", bk.L2_PARTIAL, "fused_tiled_kernel"),
+                                  ("fused_tc_kernel", bk.L2_BF16, "fused_tc_kernel"),
+                                  ("fused_tc_kernel_tf32", bk.L2_TF32, "fused_tc_kernel")):
+            ws = torch.empty(max(bk.fused_workspace_bytes(n, q, dim, k, mode), 256), dtype=torch.uint8, device=dev)
+            reps = 1 if mode == bk.L2_PARTIAL else 3
+            ms = statistics.median(_kernel_times(bk, lambda: bk.fused(points, queries, k, mode=mode, out=res, workspace=ws), kname, reps))
+            peak = fp32_peak if mode == bk.L2_PARTIAL else (peaks["bf16_tflops"] if mode == bk.L2_BF16 else peaks["bf16_tflops"] / 2)
+            out[name] = roofline_entry(kname, ms, peaks, bytes_=fused_bytes, flops=flops, flop_peak=peak,
+                                       flop_peak_name=fp32_name if mode == bk.L2_PARTIAL else bf16_name,
+                                       note=f"q=2^14 n=2^20 dim={dim} k={k}: max(2 q n dim / peak, (4 dim (n+q) + 8 q k) / HBM)")
+            if mode != bk.L2_PARTIAL:
+                rr = bk.kernel_ms("rerank_kernel")
+                lists = 2
+                out["rerank_kernel" + ("" if mode == bk.L2_BF16 else "_tf32")] = roofline_entry(
+                    "rerank_kernel", rr, peaks, bytes_=q * lists * 128 * (4.0 * dim + 4.0) + 8.0 * q * k,
+                    note="exact re-ranking of 2 lists x 128 candidates per query: one point row gathered per candidate")
+            del ws
+        del points, queries, res
+        # merge of 8 sorted lists (the exchange of an 8-GPU search), k = 256, q = 1024
+        lists, mq, mk = 8, 1024, 256
+        gen = torch.Generator(device=dev).manual_seed(3)
+        cd = torch.sort(torch.rand((lists, mq, mk), generator=gen, device=dev), dim=2).values
+        ci = torch.randperm(lists * mq * mk, generator=gen, device=dev).to(torch.int32).reshape(lists, mq, mk)
+        mo = (torch.empty((mq, mk), device=dev), torch.empty((mq, mk), dtype=torch.int32, device=dev))
+        ms = statistics.median(_kernel_times(bk, lambda: bk.merge(cd, ci, out=mo, sorted_lists=True), "merge_kernel", 5))
+        out["merge_kernel"] = roofline_entry("merge_kernel", ms, peaks, bytes_=8.0 * lists * mq * mk + 8.0 * mq * mk,
+                                             note="8 sorted lists x 256 pairs x 1024 queries (16 MiB): launch- and "
+                                                  "latency-bound, reported against the byte roofline all the same")
+    finally:
+        bk.set_tuning("profile.kernel_events", 0)
+    out["clock_note"] = (f"SM clock sampled during the headline region: {sm_mhz} MHz; FLOP peaks use the maximum clock, so a "
+                         "fraction is not flattered by a lower running clock")
+    torch.cuda.empty_cache()
+    return out
+
+
+def _kernel_times(bk, fn, kernel, reps):
+    import torch
+    fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(reps):
+        fn()
+        times.append(bk.kernel_ms(kernel))
+    torch.cuda.synchronize()
+    bk.device_status()
+    return times
+
+
+def c3_section(bk, dev):
+    """Distances + selection (database n=2^20, q=8192 queries, k=64, dim 32/64/128): FP32 exact and
+    tensor-core distance matrix followed by `bits` (tensor-core modes: selection of k + 16
+    candidates, exact re-ranking), beside the fused kernels; milliseconds per search by CUDA events."""
+    import torch
+    n, q, k, sub = 1 << 20, 8192, 64, 256
+    margin = 16
+    dist = torch.empty((q, n), device=dev)
+    out = {"n": n, "q": q, "k": k, "data": "Uniform[0,1) coordinates, seed 42 + dim",
+           "what": "ms per search; unfused = distance matrix (32 GiB) + bits selection (+ exact re-ranking of k+16 "
+                   "candidates in the tensor-core modes); quality of every tensor-core result against the FP32 "
+                   f"path on the first {sub} queries", "cases": {}}
+    for dim in (32, 64, 128):
+        points, queries = make_vectors("uniform", n, q, dim, 42 + dim, dev)
+        ex = bk.fused(points, queries[:sub].contiguous(), k, mode=bk.L2_EXACT)
+        res = (torch.empty((q, k), device=dev), torch.empty((q, k), dtype=torch.int32, device=dev))
+        cand = (torch.empty((q, k + margin), device=dev), torch.empty((q, k + margin), dtype=torch.int32, device=dev))
+        for name, mode in (("fp32", bk.L2_EXACT), ("tf32", bk.L2_TF32), ("bf16", bk.L2_BF16)):
+            ws = torch.empty(max(bk.l2_workspace_bytes(n, q, dim, mode), 256), dtype=torch.uint8, device=dev)
+            ms_l2 = timed_ms(lambda: bk.l2(points, queries, mode=mode, out=dist, workspace=ws), 2)
+            if mode == bk.L2_EXACT:
+                ms_sel = timed_ms(lambda: bk.select(dist, k, out=res), 2)
+                entry = {"ms_distances": ms_l2, "ms_selection": ms_sel, "ms": ms_l2 + ms_sel}
+            else:
+                def pick():
+                    bk.select(dist, k + margin, out=cand)
+                    bk.refine(points, queries, cand[1], k, out=res)
+                ms_sel = timed_ms(pick, 2)
+                entry = {"ms_distances": ms_l2, "ms_selection_and_rerank": ms_sel, "ms": ms_l2 + ms_sel}
+                entry.update(quality(res[1][:sub], res[0][:sub], ex[1], ex[0]))
+            entry["queries_per_s"] = q / (entry["ms"] * 1e-3)
+            out["cases"][f"unfused_{name}_dim{dim}"] = entry
+            del ws
+        for name, mode in (("fp32", bk.L2_EXACT), ("tf32", bk.L2_TF32), ("bf16", bk.L2_BF16)):
+            ws = torch.empty(max(bk.fused_workspace_bytes(n, q, dim, k, mode), 256), dtype=torch.uint8, device=dev)
+            ms = timed_ms(lambda: bk.fused(points, queries, k, mode=mode, out=res, workspace=ws), 1 if name == "fp32" else 3)
+            entry = {"ms": ms, "queries_per_s": q / (ms * 1e-3)}
+            if mode != bk.L2_EXACT:
+                entry.update(quality(res[1][:sub], res[0][:sub], ex[1], ex[0]))
+            out["cases"][f"fused_{name}_dim{dim}"] = entry
+            del ws
+        del points, queries
+    bk.device_status()
+    del dist
+    torch.cuda.empty_cache()
+    return out
+
+
+def c4_section(bk, dev):
+    """The fused small-dimension grid: n=2^20 points, q=2^16 queries, dim in {4,8,16,32,64},
+    k in {4,16,32,128}; uniform and clustered coordinates; ms per search by CUDA events."""
+    import torch
+    n, q, sub = 1 << 20, 1 << 16, 256
+    out = {"n": n, "q": q, "what": "ms per search (fused, the matrix is never written); tensor-core numbers carry "
+                                   f"recall@k and k-th-distance error against the FP32 path on the first {sub} queries",
+           "uniform": {}, "clustered": {}}
+    for kind in ("uniform", "clustered"):
+        for dim in (4, 8, 16, 32, 64):
+            points, queries = make_vectors(kind, n, q, dim, 100 + dim, dev)
+            for k in (4, 16, 32, 128):
+                res = (torch.empty((q, k), device=dev), torch.empty((q, k), dtype=torch.int32, device=dev))
+                ex = bk.fused(points, queries[:sub].contiguous(), k, mode=bk.L2_EXACT)
+                row = {}
+                modes = [("bf16", bk.L2_BF16), ("tf32", bk.L2_TF32)]
+                # the FP32 grid once (clustered coordinates take the same time): every dim for uniform,
+                # dim 16 for clustered
+                if kind == "uniform" or dim == 16:
+                    modes.append(("fp32", bk.L2_PARTIAL))
+                for name, mode in modes:
+                    ws = torch.empty(max(bk.fused_workspace_bytes(n, q, dim, k, mode), 256), dtype=torch.uint8, device=dev)
+                    ms = timed_ms(lambda: bk.fused(points, queries, k, mode=mode, out=res, workspace=ws),
+                                  1 if name == "fp32" else 2)
+                    row[name] = {"ms": ms, "distances_per_s": q * n / (ms * 1e-3)}
+                    if name != "fp32":
+                        row[name].update(quality(res[1][:sub], res[0][:sub], ex[1], ex[0]))
+                    del ws
+                out[kind][f"dim{dim}_k{k}"] = row
+            del points, queries
+    bk.device_status()
+    torch.cuda.empty_cache()
+    return out
+
+
+def sharded_knn_section(bk, search, dev, rank, world, barrier, max_over_ranks, dist_pg, n_total, label, with_fp32):
+    """Database-sharded fused k-NN: `n_total` points of dimension 64 split into equal contiguous
+    shards, all 16384 queries on every GPU, k = 128; fused tensor-core search of the shard (bf16
+    split images + exact re-ranking), one all-gather of the candidates, merge.  Queries per second
+    of the whole job, device time, max over ranks.  Untimed checks afterwards: (a) an FP32 sharded
+    search of 64 queries must equal, bit for bit, the unsharded FP32 search over the gathered
+    database; (b) recall of the timed tensor-core result against it."""
+    import torch
+    n_shard, q, dim, k = n_total // world, 1 << 14, 64, 128
     gen = torch.Generator(device=dev).manual_seed(1000 + rank)
-    points = torch.rand((n_shard, dim), generator=gen, device=dev)
+    points = torch.empty((n_shard, dim), device=dev)
+    step_rows = 1 << 24
+    for b in range(0, n_shard, step_rows):
+        points[b:b + step_rows] = torch.rand((min(step_rows, n_shard - b), dim), generator=gen, device=dev)
     gen_q = torch.Generator(device=dev).manual_seed(7)          # the same queries on every rank
     queries = torch.rand((q, dim), generator=gen_q, device=dev)
     mode = bk.L2_BF16
@@ -233,11 +460,11 @@ def sharded_knn_section(bk, search, dev, rank, world, barrier, max_over_ranks):
     fin = (torch.empty((q, k), device=dev), torch.empty((q, k), dtype=torch.int32, device=dev))
 
     def step():
-        search.knn(points, queries, k, rank * n_shard, out=None if world == 1 else fin, mode=mode, workspace=ws)
+        search.knn(points, queries, k, rank * n_shard, out=fin, mode=mode, workspace=ws)
 
     step()
     barrier()
-    steps = 3
+    steps = 3 if n_shard <= (1 << 25) else 2
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(steps):
@@ -246,15 +473,54 @@ def sharded_knn_section(bk, search, dev, rank, world, barrier, max_over_ranks):
     barrier()
     ms = max_over_ranks(e0.elapsed_time(e1)) / steps
     bk.device_status()
-    del points, ws
+    peak_bytes = points.numel() * 4 + ws.numel() + queries.numel() * 4 + 2 * fin[0].numel() * 4
+    del ws
+
+    # ---- checks (untimed) ----
+    sub = 64
+    qsub = queries[:sub].contiguous()
+    fp_d, fp_i = search.knn(points, qsub, k, rank * n_shard, mode=bk.L2_EXACT)
+    check = {"queries": sub}
+    if world > 1:
+        everything = torch.empty((world * n_shard, dim), device=dev)
+        dist_pg.all_gather_into_tensor(everything, points)
+        one_d, one_i = bk.fused(everything, qsub, k, mode=bk.L2_EXACT)
+        torch.cuda.synchronize()
+        same = bool(torch.equal(one_d, fp_d) and torch.equal(one_i, fp_i))
+        del everything
+        flag = torch.tensor([1 if same else 0], device=dev)
+        dist_pg.all_reduce(flag, op=dist_pg.ReduceOp.MIN)
+        check["fp32_sharded_equals_unsharded"] = "pass" if int(flag.item()) == 1 else "FAIL"
+    else:
+        one_d, one_i = fp_d, fp_i
+        check["fp32_sharded_equals_unsharded"] = "single shard"
+    check.update({"tensor_core_" + key: val for key, val in quality(fin[1][:sub], fin[0][:sub], one_i, one_d).items()})
+    ms_fp32 = None
+    if with_fp32:
+        # one FP32-exact sharded point: all queries, bit-exact mode, one search (seconds long)
+        ws32 = torch.empty(max(bk.fused_workspace_bytes(n_shard, q, dim, k, bk.L2_PARTIAL), 256), dtype=torch.uint8, device=dev)
+        barrier()
+        e0.record()
+        search.knn(points, queries, k, rank * n_shard, out=fin, mode=bk.L2_PARTIAL, workspace=ws32)
+        e1.record()
+        barrier()
+        ms_fp32 = max_over_ranks(e0.elapsed_time(e1))
+        del ws32
+    bk.device_status()
+    del points
     torch.cuda.empty_cache()
-    return {"n_total": n_shard * world, "n_per_gpu": n_shard, "q": q, "dim": dim, "k": k, "mode": "bf16 (tcgen05)",
-            "ms_per_step": ms, "queries_per_s": q / (ms * 1e-3), "distances_per_s": q * n_shard * world / (ms * 1e-3),
-            "steps": steps}
+    out = {"scaling": label, "n_total": n_shard * world, "n_per_gpu": n_shard, "q": q, "dim": dim, "k": k,
+           "mode": "bf16 (tcgen05) + exact re-ranking", "ms_per_step": ms, "queries_per_s": q / (ms * 1e-3),
+           "distances_per_s": q * n_shard * world / (ms * 1e-3), "steps": steps, "check": check,
+           "peak_device_bytes_per_gpu": peak_bytes}
+    if ms_fp32 is not None:
+        out["fp32_exact"] = {"ms_per_step": ms_fp32, "queries_per_s": q / (ms_fp32 * 1e-3), "steps": 1,
+                             "mode": "FP32 FFMA (bit-exact with the reference's fused kernel)"}
+    return out
 
 
 def run_profile_case(name):
-    """Small cases of the k-NN kernels for profiler captures: a few hundred MB on the device,
+    """Small cases of the kernels for profiler captures: a few hundred MB on the device,
     three launches each (inputs larger than L2 where the kernel streams them)."""
     import torch
     import __graft_entry__ as entry
@@ -276,6 +542,18 @@ def run_profile_case(name):
         out = (torch.empty((q, k), device=dev), torch.empty((q, k), dtype=torch.int32, device=dev))
         for _ in range(3):
             bk.fused(points, queries, k, mode=mode, out=out, workspace=ws)
+    elif name in ("select_k1024", "select_k2048", "select_desc_k256"):
+        # one full wave of rows: 2 GiB of matrix
+        n = 1 << 20
+        k = {"select_k1024": 1024, "select_k2048": 2048, "select_desc_k256": 256}[name]
+        q = 512
+        dist = torch.rand((q, n), generator=gen, device=dev)
+        if name == "select_desc_k256":
+            q = 148
+            dist = torch.sort(dist[:q], dim=1, descending=True).values.contiguous()
+        out = (torch.empty((q, k), device=dev), torch.empty((q, k), dtype=torch.int32, device=dev))
+        for _ in range(3):
+            bk.select(dist, k, out=out)
     else:
         n, q = 1 << 18, 2048                            # 2 GiB distance matrix
         mode = bk.L2_BF16 if name == "l2_tc" else bk.L2_PARTIAL
@@ -291,12 +569,16 @@ def run_profile_case(name):
 
 
 def run_reference_arm(args):
-    """The reference's own CPU implementation of the path, timed on the host cores."""
-    import numpy as np
-    from oracle import oracle
+    """The reference's own CPU implementation of the path, timed on the host cores (rank 0 only)."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    # a launcher may pin OpenMP to one thread per rank; this arm is the only worker of its run and
+    # takes every core the process may use (set before the OpenMP runtime is loaded)
+    os.environ["OMP_NUM_THREADS"] = str(host_threads())
+    os.environ.pop("OMP_THREAD_LIMIT", None)
+    import numpy as np
+    from oracle import oracle
     oracle.build()
     cores = oracle.num_threads()
     rows = max(cores, 64)
@@ -329,6 +611,11 @@ def run_reference_arm(args):
         select()
     dt = sum(times) / len(times)
     value = rows * N_COLS / dt
+    del sample
+    # the reference binary's whole flow on the CPU (vectors -> distances -> selection), same shape
+    # as the GPU arm's `e2e_knn`: q rows of the q x n problem with dim 32 vectors
+    knn_rows = max(cores, 32)
+    knn = cpu_knn_baseline(N_COLS, E2E_KNN_DIM, args.k, knn_rows, seed=42, budget_s=15.0)
     sample_text = (f"each step = {rows} of {Q} rows x {N_COLS} columns, Uniform[0,1) seed 42, k={args.k}, "
                    f"OpenMP heap selection on {cores} threads "
                    f"({'the reference parallel_knn::selection compiled from its sources' if kind == 'reference' else 'CPU port of parallel_knn::selection'})")
@@ -339,6 +626,9 @@ def run_reference_arm(args):
                        "q": Q, "n": N_COLS, "k": args.k},
             "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample_text},
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "e2e_knn": {"value": knn["distances_per_s"], "unit": UNIT, "dim": E2E_KNN_DIM, "cores": knn["cores"],
+                        "kind": knn["kind"], "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+                        "what": "the reference binary's flow on the CPU: " + knn["sample"]},
             "gpu_launches": 0}
     print(json.dumps(line), flush=True)
 
@@ -350,11 +640,14 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--k", type=int, default=256)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
-    ap.add_argument("--no-sweep", action="store_true", help="skip the k / input-order sweep")
+    ap.add_argument("--no-sweep", action="store_true", help="skip everything but the headline selection")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-grid", action="store_true", help="skip the distances+selection and fused grids")
     ap.add_argument("--rows", type=int, default=Q, help="rows of the matrix (smaller = profiling case)")
-    ap.add_argument("--profile-case", default=None, choices=["fused_tc", "fused_tc_small", "l2_tc", "fused_fp32", "l2_fp32"],
+    ap.add_argument("--profile-case", default=None,
+                    choices=["fused_tc", "fused_tc_small", "l2_tc", "fused_fp32", "l2_fp32", "select_k1024", "select_k2048",
+                             "select_desc_k256"],
                     help="run a few launches of one small case of that kernel and exit (for ncu captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "native" else args.warmup
@@ -386,30 +679,26 @@ def main():
         import torch.distributed as dist_pg_mod
         dist_pg_mod.init_process_group("nccl", device_id=dev)
         dist_pg = dist_pg_mod
+    peaks = measured_peaks()
 
     q, n, k = args.rows, N_COLS, args.k
     gen = torch.Generator(device=dev).manual_seed(42 + rank)
     matrix = torch.rand((q, n), generator=gen, device=dev, dtype=torch.float32)
-    offsets = torch.full((q,), rank * n, dtype=torch.int32, device=dev)  # global column index of the shard
-    if world > 1:
-        fin_d = torch.empty((q, k), dtype=torch.float32, device=dev)
-        fin_i = torch.empty((q, k), dtype=torch.int32, device=dev)
+    fin_d = torch.empty((q, k), dtype=torch.float32, device=dev)
+    fin_i = torch.empty((q, k), dtype=torch.int32, device=dev)
 
-    launches_per_step = 1 if world == 1 else 2
+    launches_per_step = 1 if world == 1 else 2   # select_kernel (+ merge_kernel; the all-gather is NCCL's)
     from importlib import import_module
     search = import_module(entry.PKG_NAME + ".sharded").ShardedSearch(bk, rank, world)
 
-    out_d, out_i = search.local_views(q, k, dev)  # the local candidates live in the exchange buffer
-
     def step(src=matrix):
         # local selection with global labels, then (N > 1) ONE NCCL all-gather + merge kernel
-        search.select(src, k, rank * n, offsets=offsets, out=None if world == 1 else (fin_d, fin_i))
+        search.select(src, k, rank * n, out=(fin_d, fin_i))
 
     def stream_step(events=None):
-        # the same search as one of a stream of searches: with N > 1 its all-gather stays in flight
-        # while the next local selection runs (two buffer sets), and the previous search is merged
-        search.submit_select(matrix, k, rank * n, offsets=offsets, out=None if world == 1 else (fin_d, fin_i),
-                             events=events)
+        # the same search in the submit form: with N > 1 its exchange and merge stay in flight on the
+        # library's stream while the next local selection runs
+        search.submit_select(matrix, k, rank * n, out=(fin_d, fin_i), events=events)
 
     def barrier():
         torch.cuda.synchronize()
@@ -455,18 +744,48 @@ def main():
     ms_per_step = total_ms / args.steps
     value = q * n * world / (ms_per_step * 1e-3)
 
-    peak_gbs, peak_kind = measured_peaks()
     algo_bytes = 4.0 * q * n + 8.0 * q * k
     achieved = algo_bytes / (kernel_ms * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "kernel": "select_kernel", "achieved": achieved, "peak": peak_gbs, "unit": "GB/s",
-                "frac": achieved / peak_gbs, "peak_source": f"{peak_kind} (copy bandwidth, burst)",
+    roofline = {"bound": "hbm", "kernel": "select_kernel", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                "frac": achieved / peaks["hbm_gbs"], "peak_source": f"{peaks['source']} (copy bandwidth, burst)",
                 "algorithmic_bytes_per_launch": algo_bytes, "kernel_ms": kernel_ms,
-                "traffic": None}
-    # DRAM traffic of the same kernel from one ncu capture of a 592-row case (one full wave), per
-    # row; traffic is proportional to the rows, so a full launch is rows x that.
-    roofline["traffic"] = NCU_DRAM_BYTES_PER_ROW * q
-    roofline["traffic_source"] = ("ncu dram__bytes_read.sum + dram__bytes_write.sum of select_kernel<256,1>, "
-                                  "592 x 2^20 capture, scaled by rows")
+                # DRAM traffic of the same kernel from one ncu capture of a 592-row case (one full
+                # wave), per row; traffic is proportional to the rows
+                "traffic": NCU_DRAM_BYTES_PER_ROW * q,
+                "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of select_kernel<256,1>, "
+                                  "592 x 2^20 capture, scaled by rows"}
+
+    # ---- N > 1: the merged result against the unsharded selection, on the benchmark's own data ----
+    sharded_check = None
+    if world > 1:
+        rows = 8
+        step()
+        search.drain()
+        torch.cuda.synchronize()
+        mine = matrix[:rows].contiguous()
+        blocks = torch.empty((world, rows, n), device=dev)
+        dist_pg.all_gather_into_tensor(blocks, mine)
+        whole = blocks.permute(1, 0, 2).reshape(rows, world * n).contiguous()
+        one_d, one_i = bk.select(whole, k)
+        ok = bool(torch.equal(one_d, fin_d[:rows]) and torch.equal(one_i, fin_i[:rows]))
+        # and the submit form, on a smaller seeded problem every rank can build in full
+        gen_c = torch.Generator(device=dev).manual_seed(5)
+        small = torch.randint(0, 1000, (64, world * (1 << 16)), generator=gen_c, device=dev).to(torch.float32)
+        want = bk.select(small, 100)
+        outs = []
+        for shift in range(3):
+            outs.append((torch.empty((64, 100), device=dev), torch.empty((64, 100), dtype=torch.int32, device=dev)))
+            shard = torch.roll(small, shift, dims=0)[:, rank << 16:(rank + 1) << 16].contiguous()
+            search.submit_select(shard, 100, rank << 16, out=outs[-1])
+        search.drain()
+        torch.cuda.synchronize()
+        for shift in range(3):
+            wd, wi = torch.roll(want[0], shift, dims=0), torch.roll(want[1], shift, dims=0)
+            ok = ok and bool(torch.equal(outs[shift][0], wd) and torch.equal(outs[shift][1], wi))
+        flag = torch.tensor([1 if ok else 0], device=dev)
+        dist_pg.all_reduce(flag, op=dist_pg.ReduceOp.MIN)
+        sharded_check = "pass" if int(flag.item()) == 1 else "FAIL"
+        del blocks, whole, small
 
     # ---- sweep: other k, and the adversarial descending rows (kernel time only) -------------
     sweep = None
@@ -483,18 +802,9 @@ def main():
                 od = torch.empty((q, kk), dtype=torch.float32, device=dev)
                 oi = torch.empty((q, kk), dtype=torch.int32, device=dev)
                 reps = 5 if order == "uniform" else 2
-                for _ in range(2 if order == "uniform" else 1):
-                    bk.select(src, kk, out=(od, oi))
-                torch.cuda.synchronize()
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                e0.record()
-                for _ in range(reps):
-                    bk.select(src, kk, out=(od, oi))
-                e1.record()
-                torch.cuda.synchronize()
-                ms = e0.elapsed_time(e1) / reps
+                ms = timed_ms(lambda: bk.select(src, kk, out=(od, oi)), reps, warm=2 if order == "uniform" else 1)
                 sweep[f"{order}_k{kk}"] = {"ms": ms, "distances_per_s": q * n / (ms * 1e-3),
-                                           "frac_of_hbm_peak": (4.0 * q * n + 8.0 * q * kk) / (ms * 1e-3) / 1e9 / peak_gbs}
+                                           "frac_of_hbm_peak": (4.0 * q * n + 8.0 * q * kk) / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}
             del src
         # kept on the host for the same-box run of the reference's kernel on the adversarial rows
         desc_host = desc.cpu().numpy() if (desc is not None and not args.no_cpu and not args.no_e2e) else None
@@ -506,16 +816,9 @@ def main():
         try:
             od = torch.empty((q, 32), dtype=torch.float32, device=dev)
             oi = torch.empty((q, 32), dtype=torch.int32, device=dev)
-            bk.select(matrix, 32, out=(od, oi))
-            torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            bk.select(matrix, 32, out=(od, oi))
-            e1.record()
-            torch.cuda.synchronize()
-            ms = e0.elapsed_time(e1)
+            ms = timed_ms(lambda: bk.select(matrix, 32, out=(od, oi)), 1)
             sweep["uniform_k32_without_filter"] = {"ms": ms, "distances_per_s": q * n / (ms * 1e-3),
-                                                   "frac_of_hbm_peak": (4.0 * q * n + 8.0 * q * 32) / (ms * 1e-3) / 1e9 / peak_gbs}
+                                                   "frac_of_hbm_peak": (4.0 * q * n + 8.0 * q * 32) / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}
         finally:
             bk.set_tuning("select.filter", 1)
 
@@ -529,13 +832,12 @@ def main():
         host_d = torch.empty((q, k), dtype=torch.float32).pin_memory()
         host_i = torch.empty((q, k), dtype=torch.int32).pin_memory()
         staging = torch.empty_like(matrix)
-        res_d, res_i = (out_d, out_i) if world == 1 else (fin_d, fin_i)
 
         def e2e_step():
             staging.copy_(host, non_blocking=True)
             step(staging)
-            host_d.copy_(res_d, non_blocking=True)
-            host_i.copy_(res_i, non_blocking=True)
+            host_d.copy_(fin_d, non_blocking=True)
+            host_i.copy_(fin_i, non_blocking=True)
 
         e2e_steps = max(3, min(args.steps, 10))
         for _ in range(2):
@@ -556,7 +858,7 @@ def main():
         # The flow of the reference's `knn` binary (prepare / distances / selection / finish,
         # src/main.cpp): the VECTORS come from the host every step, the distance matrix is made on
         # the device (exact FP32 kernel) and never crosses PCIe.
-        e2e_dim = 32
+        e2e_dim = E2E_KNN_DIM
         hp = torch.rand((n, e2e_dim), dtype=torch.float32).pin_memory()
         hq = torch.rand((q, e2e_dim), dtype=torch.float32).pin_memory()
         dp = torch.empty((n, e2e_dim), dtype=torch.float32, device=dev)
@@ -571,7 +873,7 @@ def main():
         consumed = torch.cuda.Event()
 
         def knn_step():
-            main = torch.cuda.current_stream()
+            main_stream = torch.cuda.current_stream()
             copy_stream.wait_event(consumed)       # the previous step no longer reads dp / dq
             with torch.cuda.stream(copy_stream):
                 dq.copy_(hq, non_blocking=True)
@@ -579,12 +881,12 @@ def main():
                     dp[b:e].copy_(hp[b:e], non_blocking=True)
                     arrived[i].record(copy_stream)
             for i, (b, e) in enumerate(bounds):
-                main.wait_event(arrived[i])
+                main_stream.wait_event(arrived[i])
                 bk.l2(dp[b:e], dq, mode=bk.L2_EXACT, out=staging[:, b:e])
-            consumed.record(main)
+            consumed.record(main_stream)
             step(staging)
-            host_d.copy_(res_d, non_blocking=True)
-            host_i.copy_(res_i, non_blocking=True)
+            host_d.copy_(fin_d, non_blocking=True)
+            host_i.copy_(fin_i, non_blocking=True)
 
         consumed.record(torch.cuda.current_stream())
 
@@ -602,12 +904,13 @@ def main():
                    "h2d_bytes_per_step": 4 * e2e_dim * (n + q), "d2h_bytes_per_step": 8 * q * k, "dim": e2e_dim,
                    "what": "pinned host points and queries -> device (four pieces on a copy stream, the distance "
                            "kernel of a piece starts when it has arrived), exact FP32 distance matrix on the device, "
-                           "selection, result -> host: the reference's own end-to-end flow"}
+                           "selection, result -> host: the reference's own end-to-end flow; the reference arm's "
+                           "e2e_knn is the same flow on the CPU"}
         del staging, dp, dq, hp, hq
 
     # ---- same-box comparator: the reference's own `bits-prefetch` kernel, recompiled ---------
     reference_gpu = None
-    if rank == 0 and world == 1 and not args.no_cpu and host is not None:
+    if rank == 0 and world == 1 and not args.no_cpu and host is not None and not args.no_sweep:
         try:
             from oracle import ref_select
             if ref_select.available():
@@ -627,27 +930,38 @@ def main():
         except Exception as err:  # the comparator is optional
             reference_gpu = {"unavailable": str(err)}
 
-    knn = None
-    if rank == 0 and world == 1 and not args.no_sweep:
-        del matrix
-        torch.cuda.empty_cache()
-        knn = knn_section(bk, dev)
-
-    # ---- database-sharded fused k-NN: 2^24 points of dim 64 per GPU, 16384 queries, k = 128 ----
-    knn_sharded = None
-    if not args.no_sweep:
-        if "matrix" in dir():
-            del matrix
-        torch.cuda.empty_cache()
-        knn_sharded = sharded_knn_section(bk, search, dev, rank, world, barrier, max_over_ranks)
-
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
         if host is None:
             gen2 = torch.Generator(device=dev).manual_seed(42)
             host = torch.rand((64, n), generator=gen2, device=dev, dtype=torch.float32).cpu()
         cpu = cpu_selection_baseline(host.numpy(), k)
+    del host
+    del matrix
+    torch.cuda.empty_cache()
 
+    # ---- per-kernel rooflines, distances + selection, the fused grid (1 GPU) -----------------
+    kernels = c3 = c4 = None
+    if rank == 0 and world == 1 and not args.no_sweep:
+        kernels = kernels_section(bk, dev, peaks, None if clocks is None else clocks.get("sm_mhz"))
+        if not args.no_grid:
+            c3 = c3_section(bk, dev)
+            c4 = c4_section(bk, dev)
+
+    # ---- database-sharded fused k-NN: weak (2^24 points per GPU) and strong (2^27 points) --------
+    knn_sharded = knn_sharded_strong = None
+    if not args.no_sweep:
+        knn_sharded = sharded_knn_section(bk, search, dev, rank, world, barrier, max_over_ranks, dist_pg,
+                                          (1 << 24) * world, "weak", with_fp32=world == 8)
+        if world < 8:   # at 8 GPUs the weak configuration IS the 2^27-point one
+            knn_sharded_strong = sharded_knn_section(bk, search, dev, rank, world, barrier, max_over_ranks, dist_pg,
+                                                     1 << 27, "strong", with_fp32=True)
+
+    knn_cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu and not args.no_sweep:
+        knn_cpu = cpu_knn_baseline(1 << 20, 64, 128, max(host_threads(), 32), seed=43)
+
+    search.close()
     if rank == 0:
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
@@ -658,17 +972,18 @@ def main():
                            "l2_policy": "input (4 GiB per GPU) is larger than L2; no flush needed"},
                 "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "e2e_knn": e2e_knn,
                 "gpu_launches": launches_per_step * args.steps, "clocks": clocks}
-        if sweep is not None:
-            line["sweep"] = sweep
-        if reference_gpu is not None:
-            line["reference_gpu"] = reference_gpu
-        if knn is not None:
-            line["knn"] = knn
-        if knn_sharded is not None:
-            line["knn_sharded"] = knn_sharded
+        for key, val in (("sharded_check", sharded_check), ("sweep", sweep), ("reference_gpu", reference_gpu),
+                         ("kernels", kernels), ("c3", c3), ("c4", c4), ("knn_cpu_baseline", knn_cpu),
+                         ("knn_sharded", knn_sharded), ("knn_sharded_strong", knn_sharded_strong)):
+            if val is not None:
+                line[key] = val
         print(json.dumps(line), flush=True)
+    failed = sharded_check == "FAIL" or any(
+        s is not None and s["check"].get("fp32_sharded_equals_unsharded") == "FAIL" for s in (knn_sharded, knn_sharded_strong))
     if world > 1:
         dist_pg.destroy_process_group()
+    if failed:
+        raise SystemExit("sharded result differs from the unsharded one")
 
 
 if __name__ == "__main__":

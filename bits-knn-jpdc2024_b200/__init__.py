@@ -21,6 +21,8 @@ ERR_WORKSPACE = 4
 ERR_CUDA = 5
 ERR_DEVICE_TIMEOUT = 6
 ERR_UNSUPPORTED_MODE = 7
+ERR_COMM = 8
+SHARDED_ID_BYTES = 128
 
 L2_EXACT, L2_PARTIAL, L2_TF32, L2_BF16 = 0, 1, 2, 3
 STATIC_SCRATCH_BYTES = 8 << 20  # BITSKNN_STATIC_SCRATCH_BYTES
@@ -38,6 +40,7 @@ SIGNATURES = {
     "bitsknn_set_tuning": (_int, [ctypes.c_char_p, _int]),
     "bitsknn_get_tuning": (_int, [ctypes.c_char_p, ctypes.POINTER(_int)]),
     "bitsknn_tuning_key": (ctypes.c_char_p, [_int]),
+    "bitsknn_kernel_ms": (_int, [ctypes.c_char_p, ctypes.POINTER(ctypes.c_float)]),
     "bitsknn_select": (_int, [_ptr, _i64, _ptr, _i64, _ptr, _i64, _i64, _int, _ptr, _ptr, _ptr]),
     "bitsknn_select_auto_splits": (_int, [_i64, _i64, _int]),
     "bitsknn_select_split_workspace_bytes": (_sz, [_i64, _int, _int]),
@@ -46,6 +49,18 @@ SIGNATURES = {
     "bitsknn_merge": (_int, [_ptr, _ptr, _i64, _i64, _i64, _int, _int, _ptr, _ptr, _ptr]),
     "bitsknn_merge_lists": (_int, [_ptr, _ptr, _i64, _i64, _i64, _int, _int, _int, _ptr, _ptr, _ptr]),
     "bitsknn_refine": (_int, [_ptr, _ptr, _i64, _i64, _int, _ptr, _i64, _int, ctypes.c_int32, _int, _ptr, _ptr, _ptr]),
+    "bitsknn_sharded_unique_id": (_int, [_ptr]),
+    "bitsknn_sharded_create": (_int, [ctypes.POINTER(_ptr), _ptr, _int, _int]),
+    "bitsknn_sharded_init": (_int, [ctypes.POINTER(_ptr), _ptr, _int, _int]),
+    "bitsknn_sharded_destroy": (_int, [_ptr]),
+    "bitsknn_sharded_workspace_bytes": (_sz, [_ptr, _i64, _int]),
+    "bitsknn_sharded_search_select": (_int, [_ptr, _ptr, _i64, _i64, _i64, _int, ctypes.c_int32, _ptr, _ptr, _ptr, _sz,
+                                             _ptr]),
+    "bitsknn_sharded_submit_select": (_int, [_ptr, _ptr, _i64, _i64, _i64, _int, ctypes.c_int32, _ptr, _ptr, _ptr, _sz,
+                                             _ptr]),
+    "bitsknn_sharded_search_fused": (_int, [_ptr, _ptr, _ptr, _i64, _i64, _int, _int, _int, ctypes.c_int32, _ptr, _ptr,
+                                            _ptr, _sz, _ptr, _sz, _ptr]),
+    "bitsknn_sharded_drain": (_int, [_ptr, _ptr]),
     "bitsknn_l2_workspace_bytes": (_sz, [_i64, _i64, _int, _int]),
     "bitsknn_l2": (_int, [_ptr, _ptr, _i64, _i64, _int, _int, _ptr, _i64, _ptr, _sz, _ptr]),
     "bitsknn_fused_workspace_bytes": (_sz, [_i64, _i64, _int, _int, _int]),
@@ -115,6 +130,13 @@ def tuning_keys():
         if key is None:
             return keys
         keys.append(key.decode())
+
+
+def kernel_ms(name):
+    """Device time of the last timed launch of that kernel (knob "profile.kernel_events" = 1)."""
+    out = ctypes.c_float(0)
+    _check(lib().bitsknn_kernel_ms(name.encode(), ctypes.byref(out)))
+    return out.value
 
 
 def device_status():
@@ -281,3 +303,70 @@ def fused(points, queries, k, mode=L2_PARTIAL, index_base=0, out=None, workspace
     _check(lib().bitsknn_fused(_p(points), _p(queries), n, q, dim, k, mode, index_base, _p(out[0]), _p(out[1]),
                                _p(workspace), 0 if workspace is None else workspace.numel(), _stream()))
     return out
+
+
+# ---- database-sharded search (one handle per GPU; NCCL inside the library) --------------------
+def sharded_unique_id():
+    """An NCCL unique id (bytes) made on the calling rank; distribute it to the other ranks."""
+    buf = ctypes.create_string_buffer(SHARDED_ID_BYTES)
+    _check(lib().bitsknn_sharded_unique_id(buf))
+    return buf.raw
+
+
+def sharded_create(unique_id, rank, world):
+    """Handle with its own communicator (collective over the ranks; the rank's device is current)."""
+    handle = ctypes.c_void_p()
+    buf = None if unique_id is None else ctypes.create_string_buffer(bytes(unique_id), SHARDED_ID_BYTES)
+    _check(lib().bitsknn_sharded_create(ctypes.byref(handle), buf, rank, world))
+    return handle
+
+
+def sharded_destroy(handle):
+    _check(lib().bitsknn_sharded_destroy(handle))
+
+
+def sharded_workspace_bytes(handle, q, k):
+    return int(lib().bitsknn_sharded_workspace_bytes(handle, q, k))
+
+
+def _sharded_out(q, k, device, out):
+    import torch
+    if out is None:
+        out = (torch.empty((q, k), dtype=torch.float32, device=device),
+               torch.empty((q, k), dtype=torch.int32, device=device))
+    return out
+
+
+def sharded_select(handle, dist, k, shard_begin, workspace, out=None, wait=True):
+    """One sharded selection; `wait=False` is the submit form (finish with `sharded_drain`)."""
+    import torch
+    _device_check(dist, torch.float32, "dist")
+    q, n = dist.shape
+    ld = dist.stride(0) if q > 1 else n
+    out = _sharded_out(q, k, dist.device, out)
+    fn = lib().bitsknn_sharded_search_select if wait else lib().bitsknn_sharded_submit_select
+    _check(fn(handle, _p(dist), ld, q, n, k, shard_begin, _p(out[0]), _p(out[1]), _p(workspace),
+              0 if workspace is None else workspace.numel(), _stream()))
+    return out
+
+
+def sharded_fused(handle, points, queries, k, shard_begin, workspace, mode=L2_PARTIAL, fused_workspace=None, out=None):
+    import torch
+    _device_check(points, torch.float32, "points")
+    _device_check(queries, torch.float32, "queries")
+    assert points.is_contiguous() and queries.is_contiguous()
+    n, dim = points.shape
+    q = queries.shape[0]
+    out = _sharded_out(q, k, points.device, out)
+    need = fused_workspace_bytes(n, q, dim, k, mode)
+    if fused_workspace is None and need > 0:
+        fused_workspace = torch.empty(need, dtype=torch.uint8, device=points.device)
+    _check(lib().bitsknn_sharded_search_fused(handle, _p(points), _p(queries), n, q, dim, k, mode, shard_begin,
+                                              _p(out[0]), _p(out[1]), _p(fused_workspace),
+                                              0 if fused_workspace is None else fused_workspace.numel(), _p(workspace),
+                                              0 if workspace is None else workspace.numel(), _stream()))
+    return out
+
+
+def sharded_drain(handle):
+    _check(lib().bitsknn_sharded_drain(handle, _stream()))

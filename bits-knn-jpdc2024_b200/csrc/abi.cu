@@ -38,7 +38,46 @@ tuning_entry g_tuning[] = {
     {"fused.variant", 2, 0, 2},
     {"fused.tc_mma_n", 0, 0, 256},
     {"fused.parts", 0, 0, 64},
+    {"profile.kernel_events", 0, 0, 1},
 };
+
+// kernel timing slots: one pair of events per kernel name (names are string literals)
+struct timing_slot
+{
+    const char* name;
+    cudaEvent_t begin;
+    cudaEvent_t end;
+    bool recorded;
+};
+constexpr int MAX_TIMING_SLOTS = 16;
+std::mutex g_timing_mutex;
+timing_slot g_timing[MAX_TIMING_SLOTS] = {};
+int g_timing_count = 0;
+
+timing_slot* timing_slot_of(const char* name, bool create)
+{
+    std::lock_guard<std::mutex> lock{g_timing_mutex};
+    for (int i = 0; i < g_timing_count; ++i)
+    {
+        if (std::strcmp(g_timing[i].name, name) == 0)
+        {
+            return &g_timing[i];
+        }
+    }
+    if (!create || g_timing_count == MAX_TIMING_SLOTS)
+    {
+        return nullptr;
+    }
+    timing_slot& slot = g_timing[g_timing_count];
+    if (cudaEventCreate(&slot.begin) != cudaSuccess || cudaEventCreate(&slot.end) != cudaSuccess)
+    {
+        return nullptr;
+    }
+    slot.name = name;
+    slot.recorded = false;
+    ++g_timing_count;
+    return &slot;
+}
 
 } // namespace
 
@@ -69,6 +108,27 @@ int* device_status_word()
         return nullptr;
     }
     return ptr;
+}
+
+kernel_scope::kernel_scope(const char* name, cudaStream_t stream) : slot_(nullptr), stream_(stream)
+{
+    if (tuning_value("profile.kernel_events", 0) != 0)
+    {
+        timing_slot* slot = timing_slot_of(name, true);
+        if (slot != nullptr && cudaEventRecord(slot->begin, stream) == cudaSuccess)
+        {
+            slot_ = slot;
+        }
+    }
+}
+
+kernel_scope::~kernel_scope()
+{
+    if (slot_ != nullptr)
+    {
+        auto* slot = static_cast<timing_slot*>(slot_);
+        slot->recorded = cudaEventRecord(slot->end, stream_) == cudaSuccess;
+    }
 }
 
 int tuning_value(const char* key, int fallback)
@@ -208,6 +268,24 @@ extern "C" int bitsknn_set_tuning(const char* key, int value)
         }
     }
     return fail(BITSKNN_ERR_INVALID_ARGUMENT, "unknown tuning key '%s'", key);
+}
+
+extern "C" int bitsknn_kernel_ms(const char* kernel, float* ms)
+{
+    using namespace bitsknn;
+    if (kernel == nullptr || ms == nullptr)
+    {
+        return fail(BITSKNN_ERR_INVALID_ARGUMENT, "null pointer argument");
+    }
+    timing_slot* slot = timing_slot_of(kernel, false);
+    if (slot == nullptr || !slot->recorded)
+    {
+        return fail(BITSKNN_ERR_INVALID_ARGUMENT, "no timed launch of '%s' (set \"profile.kernel_events\" to 1 first)",
+                    kernel);
+    }
+    BITSKNN_CUDA_TRY(cudaEventSynchronize(slot->end));
+    BITSKNN_CUDA_TRY(cudaEventElapsedTime(ms, slot->begin, slot->end));
+    return BITSKNN_OK;
 }
 
 extern "C" const char* bitsknn_tuning_key(int index)

@@ -42,12 +42,34 @@ int* device_status_word();
 constexpr int DEVICE_STATUS_TIMEOUT = 1;
 
 int tuning_value(const char* key, int fallback);
+
+// Optional device timing of the dominant kernels ("profile.kernel_events" = 1): the launch sites
+// wrap their kernel in a kernel_scope, which records a CUDA event on the stream before and after
+// it; bitsknn_kernel_ms() returns the elapsed time of the last launch recorded under a name.
+// Off (the default) a scope does nothing.
+struct kernel_scope
+{
+    kernel_scope(const char* name, cudaStream_t stream);
+    ~kernel_scope();
+    kernel_scope(const kernel_scope&) = delete;
+    kernel_scope& operator=(const kernel_scope&) = delete;
+
+private:
+    void* slot_;
+    cudaStream_t stream_;
+};
 // Blocks per query tile for kernels that may cut the database into ranges: the smallest count up
 // to `max_parts` after which no larger one fills the last wave of `slots` concurrent blocks
 // noticeably (2 %) better.
 int balanced_parts(int64_t query_tiles, int slots, int64_t max_parts);
 
 int device_sm_count();
+
+// bitsknn_select with `label_base` added to every implicit label (the global index of the first
+// column when the matrix is one shard of a wider one).  Defined in select.cu.
+int select_rows(const float* d_dist, int64_t ld, const int32_t* d_labels, int64_t ld_labels,
+                const int32_t* d_label_offsets, int32_t label_base, int64_t q, int64_t n, int k, float* d_out_dist,
+                int32_t* d_out_idx, cudaStream_t stream);
 
 // Merge of `lists` candidate lists of `kin` pairs per query (pair j of list l of query i at
 // [l * list_stride + i * query_stride + j]) into the `k` smallest pairs; `bias` (nullable, one

@@ -343,6 +343,7 @@ int launch_fused(const fused_params& p, int mode, cudaStream_t stream)
                     p.dim);
     }
     const int64_t grid = (p.q + QT - 1) / QT;
+    kernel_scope timed{"fused_kernel", stream};
     if (mode == BITSKNN_L2_PARTIAL)
     {
         auto kernel = fused_kernel<IPT, true>;

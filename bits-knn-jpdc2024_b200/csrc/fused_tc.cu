@@ -402,7 +402,10 @@ int launch_ftc(const CUtensorMap& map_q, const CUtensorMap& map_p, const ftc_par
 {
     auto kernel = fused_tc_kernel<BF16, IPT, NMMA>;
     BITSKNN_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-    kernel<<<static_cast<unsigned>(grid), FT_THREADS, smem, stream>>>(map_q, map_p, p);
+    {
+        kernel_scope timed{"fused_tc_kernel", stream};
+        kernel<<<static_cast<unsigned>(grid), FT_THREADS, smem, stream>>>(map_q, map_p, p);
+    }
     BITSKNN_CUDA_TRY(cudaGetLastError());
     return BITSKNN_OK;
 }

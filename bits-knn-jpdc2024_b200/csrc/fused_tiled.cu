@@ -441,6 +441,7 @@ template <int IPT>
 int launch_tiled(const tiled_params& p, int mode, int64_t grid, cudaStream_t stream)
 {
     const size_t smem = tiled_smem_bytes(p.dp);
+    kernel_scope timed{"fused_tiled_kernel", stream};
     if (mode == BITSKNN_L2_PARTIAL)
     {
         auto kernel = fused_tiled_kernel<IPT, true>;

@@ -254,6 +254,7 @@ extern "C" int bitsknn_l2(const float* d_points, const float* d_queries, int64_t
                        ((reinterpret_cast<uintptr_t>(d_queries) & 15U) == 0);
     const int vec_out = (ld % 4 == 0) && ((reinterpret_cast<uintptr_t>(d_dist) & 15U) == 0);
     const dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(gy));
+    kernel_scope timed{"l2_fp32_kernel", cs};
     if (mode == BITSKNN_L2_PARTIAL)
     {
         l2_fp32_kernel<true><<<grid, L2_THREADS, 0, cs>>>(d_points, d_queries, n, q, dim, d_dist, ld, vec_in, vec_out);

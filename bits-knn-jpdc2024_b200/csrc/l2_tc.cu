@@ -295,7 +295,10 @@ int launch_tc(const CUtensorMap& map_q, const CUtensorMap& map_p, const tc_param
 {
     auto kernel = l2_tc_kernel<BF16, NMMA>;
     BITSKNN_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-    kernel<<<static_cast<unsigned>(grid), TC_THREADS, smem, stream>>>(map_q, map_p, p);
+    {
+        kernel_scope timed{"l2_tc_kernel", stream};
+        kernel<<<static_cast<unsigned>(grid), TC_THREADS, smem, stream>>>(map_q, map_p, p);
+    }
     BITSKNN_CUDA_TRY(cudaGetLastError());
     return BITSKNN_OK;
 }

@@ -210,7 +210,10 @@ template <int IPT, int RUN, bool RERANK>
 int launch_merge(const merge_params& p, int64_t q, cudaStream_t stream)
 {
     const size_t dyn = RERANK ? static_cast<size_t>(p.dim) * sizeof(float) : 0;
-    merge_kernel<IPT, RUN, RERANK><<<static_cast<unsigned>(q), MERGE_THREADS, dyn, stream>>>(p);
+    {
+        kernel_scope timed{RERANK ? "rerank_kernel" : "merge_kernel", stream};
+        merge_kernel<IPT, RUN, RERANK><<<static_cast<unsigned>(q), MERGE_THREADS, dyn, stream>>>(p);
+    }
     BITSKNN_CUDA_TRY(cudaGetLastError());
     return BITSKNN_OK;
 }

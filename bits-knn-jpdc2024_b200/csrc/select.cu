@@ -46,6 +46,7 @@ struct select_params
     const int32_t* labels;
     int64_t ld_labels;
     const int32_t* label_offsets;
+    int32_t label_base; // added to every implicit label (the first column's global index)
     int64_t n;
     int k;
     int splits;       // slices per row (1 = whole rows)
@@ -320,7 +321,7 @@ __global__ void __launch_bounds__(THREADS) select_kernel(const select_params p)
     const int m = m64 > 0 ? static_cast<int>(m64) : 0;
     const float* rowp = p.dist + row * p.ld + begin;
     blk.labp = p.labels != nullptr ? p.labels + row * p.ld_labels + begin : nullptr;
-    blk.lab0 = static_cast<int>(begin) + (p.label_offsets != nullptr ? p.label_offsets[row] : 0);
+    blk.lab0 = static_cast<int>(begin) + p.label_base + (p.label_offsets != nullptr ? p.label_offsets[row] : 0);
 
     // [0,h): scalar head up to the first 16-byte boundary, [h,h+mid): streamed, then a tail < 4
     int h = static_cast<int>(((16U - (reinterpret_cast<uintptr_t>(rowp) & 15U)) & 15U) >> 2);
@@ -591,7 +592,10 @@ int launch_select(select_params p, int64_t vrows, cudaStream_t stream)
                     "the limit is %u", p.stage_floats * 4, p.stages, smem, 227U * 1024U);
     }
     BITSKNN_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-    kernel<<<static_cast<unsigned>(vrows), THREADS, smem, stream>>>(p);
+    {
+        kernel_scope timed{"select_kernel", stream};
+        kernel<<<static_cast<unsigned>(vrows), THREADS, smem, stream>>>(p);
+    }
     BITSKNN_CUDA_TRY(cudaGetLastError());
     return BITSKNN_OK;
 }
@@ -687,9 +691,12 @@ void fill_stream_config(select_params& p)
 
 using namespace bitsknn;
 
-extern "C" int bitsknn_select(const float* d_dist, int64_t ld, const int32_t* d_labels, int64_t ld_labels,
-                              const int32_t* d_label_offsets, int64_t q, int64_t n, int k, float* d_out_dist,
-                              int32_t* d_out_idx, bitsknn_stream_t stream)
+namespace bitsknn
+{
+
+int select_rows(const float* d_dist, int64_t ld, const int32_t* d_labels, int64_t ld_labels,
+                const int32_t* d_label_offsets, int32_t label_base, int64_t q, int64_t n, int k, float* d_out_dist,
+                int32_t* d_out_idx, cudaStream_t stream)
 {
     if (const int rc = check_select_args(d_dist, ld, q, n, k, d_out_dist, d_out_idx); rc != BITSKNN_OK)
     {
@@ -709,6 +716,7 @@ extern "C" int bitsknn_select(const float* d_dist, int64_t ld, const int32_t* d_
     p.labels = d_labels;
     p.ld_labels = ld_labels;
     p.label_offsets = d_label_offsets;
+    p.label_base = label_base;
     p.n = n;
     p.k = k;
     p.splits = 1;
@@ -725,7 +733,17 @@ extern "C" int bitsknn_select(const float* d_dist, int64_t ld, const int32_t* d_
     // reference keeps as an ablation (partial-bitonic-regs, src/topk/singlepass/partial_bitonic.cu:217-294)
     p.no_filter = tuning_value("select.filter", 1) == 0 ? 1 : 0;
     fill_stream_config(p);
-    return dispatch_select(p, q, static_cast<cudaStream_t>(stream));
+    return dispatch_select(p, q, stream);
+}
+
+} // namespace bitsknn
+
+extern "C" int bitsknn_select(const float* d_dist, int64_t ld, const int32_t* d_labels, int64_t ld_labels,
+                              const int32_t* d_label_offsets, int64_t q, int64_t n, int k, float* d_out_dist,
+                              int32_t* d_out_idx, bitsknn_stream_t stream)
+{
+    return select_rows(d_dist, ld, d_labels, ld_labels, d_label_offsets, 0, q, n, k, d_out_dist, d_out_idx,
+                       static_cast<cudaStream_t>(stream));
 }
 
 namespace

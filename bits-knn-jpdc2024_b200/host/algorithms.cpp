@@ -5,7 +5,9 @@
 #include <algorithm>
 #include <cmath>
 #include <cstdio>
+#include <exception>
 #include <iostream>
+#include <thread>
 
 #include "bitsknn/knn.hpp"
 
@@ -28,6 +30,16 @@ void abi_check(int status)
     {
         throw std::runtime_error{bitsknn_last_error_string()};
     }
+}
+
+// End of a device phase: the stream is idle (host timers around the phase measure the kernels,
+// as the reference's do: src/topk/singlepass/bits_knn.cu:95,113) and no kernel of the phase gave
+// up a bounded wait -- an expired wait leaves the outputs incomplete, so it is an error like any
+// other ("a kernel gave up a bounded wait"), not a result.
+void end_phase()
+{
+    BITS_CUCH(cudaStreamSynchronize(nullptr));
+    abi_check(bitsknn_device_status(nullptr));
 }
 
 // events are created on first use, so that building the registry needs no device
@@ -180,7 +192,7 @@ void knn::initialize(const knn_args& args)
 void knn::distances()
 {
     dist_impl_->compute();
-    BITS_CUCH(cudaStreamSynchronize(nullptr));
+    end_phase();
 }
 
 void cuda_knn::initialize(const knn_args& args)
@@ -243,7 +255,7 @@ void bits_knn::selection()
         abi_check(bitsknn_select(in_dist_gpu(), n, nullptr, 0, nullptr, static_cast<std::int64_t>(query_count()), n,
                                  static_cast<int>(k()), out_dist_gpu(), out_label_gpu(), nullptr));
     }
-    BITS_CUCH(cudaStreamSynchronize(nullptr));
+    end_phase();
 }
 
 void partial_bitonic_regs_knn::selection()
@@ -254,7 +266,7 @@ void partial_bitonic_regs_knn::selection()
                                       static_cast<int>(k()), out_dist_gpu(), out_label_gpu(), nullptr);
     bitsknn_set_tuning("select.filter", 1);
     abi_check(status);
-    BITS_CUCH(cudaStreamSynchronize(nullptr));
+    end_phase();
 }
 
 void bits_sq_knn::initialize(const knn_args& args)
@@ -272,7 +284,7 @@ void bits_sq_knn::selection()
     abi_check(bitsknn_select_split(in_dist_gpu(), n, nullptr, static_cast<std::int64_t>(query_count()), n,
                                    static_cast<int>(k()), deg, workspace_.data(), workspace_.size(), out_dist_gpu(),
                                    out_label_gpu(), nullptr));
-    BITS_CUCH(cudaStreamSynchronize(nullptr));
+    end_phase();
 }
 
 void fused_knn::initialize(const knn_args& args)
@@ -288,7 +300,185 @@ void fused_knn::selection()
     abi_check(bitsknn_fused(dist_impl_->points_gpu(), dist_impl_->queries_gpu(), static_cast<std::int64_t>(point_count()),
                             static_cast<std::int64_t>(query_count()), static_cast<int>(dim()), static_cast<int>(k()),
                             mode_, 0, out_dist_gpu(), out_label_gpu(), workspace_.data(), workspace_.size(), nullptr));
-    BITS_CUCH(cudaStreamSynchronize(nullptr));
+    end_phase();
+}
+
+// ---- bits-sharded: the database split over the visible GPUs, one host thread per GPU ------------
+
+namespace
+{
+
+// Runs fn(g) on one host thread per shard and rethrows the first failure.
+template <class Fn>
+void for_each_shard(std::size_t shards, Fn fn)
+{
+    std::vector<std::thread> threads;
+    std::vector<std::exception_ptr> errors(shards);
+    for (std::size_t g = 0; g < shards; ++g)
+    {
+        threads.emplace_back([&, g] {
+            try
+            {
+                fn(g);
+            }
+            catch (...)
+            {
+                errors[g] = std::current_exception();
+            }
+        });
+    }
+    for (auto& t : threads)
+    {
+        t.join();
+    }
+    for (auto& e : errors)
+    {
+        if (e)
+        {
+            std::rethrow_exception(e);
+        }
+    }
+}
+
+} // namespace
+
+sharded_knn::~sharded_knn()
+{
+    for (std::size_t g = 0; g < shards_.size(); ++g)
+    {
+        cudaSetDevice(shards_[g].device);
+        bitsknn_sharded_destroy(shards_[g].handle);
+        shards_[g] = shard{};
+    }
+    cudaSetDevice(0);
+}
+
+void sharded_knn::initialize(const knn_args& args)
+{
+    args_ = args;
+    int visible = 0;
+    BITS_CUCH(cudaGetDeviceCount(&visible));
+    // `--deg G` limits the search to G GPUs (the reference's `--deg` cuts a row into G slices for
+    // `bits-sq`, src/topk/singlepass/bits_knn.cu:132-186; here it cuts the database into G shards);
+    // the default of 1 means "all visible GPUs"
+    std::size_t world = static_cast<std::size_t>(std::max(visible, 1));
+    if (args_.deg > 1)
+    {
+        world = std::min<std::size_t>(world, args_.deg);
+    }
+    world = std::min<std::size_t>(world, std::max<std::size_t>(point_count(), 1));
+    for (auto& old : shards_)
+    {
+        cudaSetDevice(old.device);
+        bitsknn_sharded_destroy(old.handle);
+    }
+    shards_.clear();
+    shards_.resize(world);
+
+    // row-major host inputs (a column-major host matrix is transposed once, here)
+    std::vector<float> tmp_points;
+    std::vector<float> tmp_queries;
+    const float* points = args_.points;
+    const float* queries = args_.queries;
+    if (args_.points_layout == matrix_layout::column_major)
+    {
+        tmp_points = to_row_major(points, point_count(), dim());
+        points = tmp_points.data();
+    }
+    if (args_.queries_layout == matrix_layout::column_major)
+    {
+        tmp_queries = to_row_major(queries, query_count(), dim());
+        queries = tmp_queries.data();
+    }
+    unsigned char id[BITSKNN_SHARDED_ID_BYTES] = {};
+    if (world > 1)
+    {
+        abi_check(bitsknn_sharded_unique_id(id));
+    }
+    const auto n = point_count();
+    const auto q = static_cast<std::int64_t>(query_count());
+    const int kk = static_cast<int>(k());
+    const int d = static_cast<int>(dim());
+    for_each_shard(world, [&](std::size_t g) {
+        shard& s = shards_[g];
+        s.device = static_cast<int>(g);
+        BITS_CUCH(cudaSetDevice(s.device));
+        // contiguous, nearly equal shards: the first n % world shards hold one point more
+        const std::size_t base = n / world;
+        const std::size_t extra = n % world;
+        s.begin = g * base + std::min(g, extra);
+        s.count = base + (g < extra ? 1 : 0);
+        s.points = device_buffer<float>{s.count * dim()};
+        s.queries = device_buffer<float>{query_count() * dim()};
+        s.out_dist = device_buffer<float>{query_count() * k()};
+        s.out_label = device_buffer<std::int32_t>{query_count() * k()};
+        transfer_timer timer;
+        timer.begin();
+        BITS_CUCH(cudaMemcpyAsync(s.points.data(), points + s.begin * dim(), s.count * dim() * sizeof(float),
+                                  cudaMemcpyHostToDevice, nullptr));
+        BITS_CUCH(cudaMemcpyAsync(s.queries.data(), queries, query_count() * dim() * sizeof(float), cudaMemcpyHostToDevice,
+                                  nullptr));
+        timer.end();
+        s.transfer_seconds = timer.seconds();
+        abi_check(bitsknn_sharded_create(&s.handle, id, static_cast<int>(g), static_cast<int>(world)));
+        s.fused_ws = device_buffer<unsigned char>{
+            bitsknn_fused_workspace_bytes(static_cast<std::int64_t>(s.count), q, d, kk, mode_)};
+        s.exchange_ws = device_buffer<unsigned char>{bitsknn_sharded_workspace_bytes(s.handle, q, kk)};
+    });
+    BITS_CUCH(cudaSetDevice(0));
+}
+
+void sharded_knn::selection()
+{
+    for_each_shard(shards_.size(), [&](std::size_t g) {
+        shard& s = shards_[g];
+        BITS_CUCH(cudaSetDevice(s.device));
+        abi_check(bitsknn_sharded_search_fused(s.handle, s.points.data(), s.queries.data(),
+                                               static_cast<std::int64_t>(s.count),
+                                               static_cast<std::int64_t>(query_count()), static_cast<int>(dim()),
+                                               static_cast<int>(k()), mode_, static_cast<std::int32_t>(s.begin),
+                                               s.out_dist.data(), s.out_label.data(), s.fused_ws.data(),
+                                               s.fused_ws.size(), s.exchange_ws.data(), s.exchange_ws.size(), nullptr));
+        end_phase();
+    });
+    BITS_CUCH(cudaSetDevice(0));
+}
+
+std::vector<distance_pair> sharded_knn::finish()
+{
+    // every shard ends with the full result; shard 0's copy is the one downloaded
+    const shard& s = shards_.front();
+    BITS_CUCH(cudaSetDevice(s.device));
+    if (no_output_)
+    {
+        out_timer_.begin();
+        out_timer_.end();
+        return {};
+    }
+    const std::size_t count = query_count() * k();
+    std::vector<float> dist(count);
+    std::vector<std::int32_t> label(count);
+    out_timer_.begin();
+    BITS_CUCH(cudaMemcpyAsync(dist.data(), s.out_dist.data(), count * sizeof(float), cudaMemcpyDeviceToHost, nullptr));
+    BITS_CUCH(cudaMemcpyAsync(label.data(), s.out_label.data(), count * sizeof(std::int32_t), cudaMemcpyDeviceToHost,
+                              nullptr));
+    out_timer_.end();
+    std::vector<distance_pair> result(count);
+    for (std::size_t i = 0; i < count; ++i)
+    {
+        result[i] = distance_pair{dist[i], label[i]};
+    }
+    return result;
+}
+
+float sharded_knn::transfer_in_seconds() const
+{
+    float longest = 0;
+    for (const auto& s : shards_)
+    {
+        longest = std::max(longest, s.transfer_seconds);
+    }
+    return longest;
 }
 
 void serial_knn::distances()
@@ -381,6 +571,8 @@ std::vector<std::unique_ptr<knn>> make_registry()
     algorithms.push_back(std::make_unique<fused_knn>("bits-fused"));
     algorithms.push_back(std::make_unique<fused_knn>("bits-fused-tf32", BITSKNN_L2_TF32));
     algorithms.push_back(std::make_unique<fused_knn>("bits-fused-bf16", BITSKNN_L2_BF16));
+    algorithms.push_back(std::make_unique<sharded_knn>("bits-sharded", BITSKNN_L2_EXACT));
+    algorithms.push_back(std::make_unique<sharded_knn>("bits-sharded-bf16", BITSKNN_L2_BF16));
     algorithms.push_back(std::make_unique<dist_runner>(BITSKNN_L2_EXACT, "magma-dist"));
     algorithms.push_back(std::make_unique<dist_runner>(BITSKNN_L2_PARTIAL, "magma-part-dist"));
     algorithms.push_back(std::make_unique<dist_runner>(BITSKNN_L2_TF32, "tc-dist-tf32"));

@@ -295,6 +295,46 @@ private:
     device_buffer<unsigned char> workspace_; // tensor-core modes only
 };
 
+// `bits-sharded`: the database cut into contiguous shards over the visible GPUs (`--deg G` limits
+// their number), one host thread and one stream per GPU; every shard runs the fused search of its
+// points with global indices, the library all-gathers the candidates (NCCL) and merges them.  The
+// reference is single-GPU; the closest thing it has is `bits-sq`, which cuts rows into slices
+// and merges their candidates (src/topk/singlepass/bits_knn.cu:116-186).
+class sharded_knn : public knn
+{
+public:
+    explicit sharded_knn(std::string id = "bits-sharded", int mode = BITSKNN_L2_EXACT) : id_(std::move(id)), mode_(mode) {}
+    ~sharded_knn() override;
+    std::string id() const override { return id_; }
+    void initialize(const knn_args& args) override;
+    void distances() override {}
+    void selection() override;
+    std::vector<distance_pair> finish() override;
+    float transfer_in_seconds() const override;
+    float transfer_out_seconds() const override { return out_timer_.seconds(); }
+    std::size_t shard_count() const { return shards_.size(); }
+
+private:
+    struct shard
+    {
+        int device = 0;
+        std::size_t begin = 0; // first point of the shard
+        std::size_t count = 0;
+        bitsknn_sharded_t* handle = nullptr;
+        device_buffer<float> points;
+        device_buffer<float> queries;
+        device_buffer<float> out_dist;
+        device_buffer<std::int32_t> out_label;
+        device_buffer<unsigned char> fused_ws;
+        device_buffer<unsigned char> exchange_ws;
+        float transfer_seconds = 0;
+    };
+    std::string id_;
+    int mode_;
+    std::vector<shard> shards_;
+    transfer_timer out_timer_;
+};
+
 // Distance-only registry entries (reference: dist_runner<D>, include/bits/distance/dist_runner.hpp:8-15).
 class dist_runner : public knn
 {

@@ -35,7 +35,8 @@ enum bitsknn_status
     BITSKNN_ERR_WORKSPACE = 4,        /* caller-provided workspace too small */
     BITSKNN_ERR_CUDA = 5,             /* a CUDA runtime call failed (the reference's "CUDA error.") */
     BITSKNN_ERR_DEVICE_TIMEOUT = 6,   /* a bounded device-side wait expired */
-    BITSKNN_ERR_UNSUPPORTED_MODE = 7
+    BITSKNN_ERR_UNSUPPORTED_MODE = 7,
+    BITSKNN_ERR_COMM = 8              /* NCCL is missing or one of its calls failed */
 };
 
 /* Largest k of the selection / merge kernels (the reference's limit,
@@ -79,6 +80,7 @@ int bitsknn_selftest_bounded_wait(bitsknn_stream_t stream);
  *                         workspace), 2 = automatic (default)
  *   "fused.parts"         blocks per query tile of the tiled fused kernels, i.e. ranges the database
  *                         is cut into (0 = automatic, the default)
+ *   "profile.kernel_events"  1 = record CUDA events around the main kernels (bitsknn_kernel_ms)
  *   "fused.tc_mma_n"      points per tensor-core MMA of the fused TF32/BF16 kernels: 0 = 256
  *                         whenever the operand ring fits shared memory (default), 128 = always 128
  * The reference's `--block-size` / `--items-per-thread` flags tune the same things for its
@@ -87,6 +89,14 @@ int bitsknn_set_tuning(const char* key, int value);
 int bitsknn_get_tuning(const char* key, int* value);
 /* The index-th registered tuning key (0, 1, ...), NULL past the last one. */
 const char* bitsknn_tuning_key(int index);
+
+/* Device time of the last launch of one of the library's main kernels, in milliseconds, taken
+ * with CUDA events on the launching stream while the knob "profile.kernel_events" is 1 (the
+ * role of the reference's cuda_event pairs, include/bits/cuda_event.hpp:63-68, moved from the
+ * transfers to the kernels).  Names: "select_kernel", "merge_kernel", "rerank_kernel",
+ * "l2_fp32_kernel", "l2_tc_kernel", "fused_kernel", "fused_tiled_kernel", "fused_tc_kernel".
+ * Synchronises on that launch's end.  INVALID_ARGUMENT if no timed launch of that name exists. */
+int bitsknn_kernel_ms(const char* kernel, float* ms);
 
 /* ---------------------------------------------------------------------------------------
  * `bits` top-k selection over a precomputed distance matrix.
@@ -129,8 +139,11 @@ int bitsknn_select_split(const float* d_dist, int64_t ld, const int32_t* d_label
  * is part of the library's device image: BITSKNN_STATIC_SCRATCH_BYTES on every GPU that
  * loads the library, for the life of the process.  Limits and rules:
  *   - q * splits * k * 8 bytes must fit (BITSKNN_ERR_WORKSPACE otherwise); splits >= 1;
- *   - the first call on each device looks up the array's device address; make that call
- *     before starting any stream capture on that device;
+ *   - the first call on each device looks up the array's device address and, with the CUDA
+ *     runtime's lazy loading, is also when the driver places the kernels and the array on that
+ *     device: make it at start-up, while memory is still to be had, and before starting any
+ *     stream capture on that device.  The address is remembered per device; after a
+ *     cudaDeviceReset() it is stale and the process must not use this entry point again;
  *   - every call on a device uses the same array: calls that can overlap on the GPU (different
  *     streams, different host threads) race and must be serialised by the caller;
  *   - neither this function nor anything it calls allocates or frees memory. */
@@ -222,6 +235,59 @@ size_t bitsknn_fused_workspace_bytes(int64_t n, int64_t q, int dim, int k, int m
 int bitsknn_fused(const float* d_points, const float* d_queries, int64_t n, int64_t q, int dim, int k,
                   int mode, int32_t index_base, float* d_out_dist, int32_t* d_out_idx, void* d_workspace,
                   size_t workspace_bytes, bitsknn_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Database-sharded search over several GPUs (one handle per GPU; one process or host thread
+ * per GPU).  The reference is single-GPU; this generalises its split-row two-pass scheme
+ * (single_query_bits, src/topk/singlepass/bits_knn.cu:116-186: per-slice top-k with
+ * label_offsets, then a pass over the slices' candidates) from slices of a row to shards of the
+ * database, and plugs into the same registry (src/main.cpp:109-155) as the id `bits-sharded`.
+ *
+ * Rank r of `world` holds points / matrix columns [shard_begin, shard_begin + n_local) and ALL
+ * queries.  A search = local top-k with global labels on the caller's stream, ONE NCCL all-gather
+ * of every rank's q x k pairs and the merge kernel, both on a stream the handle owns; every rank
+ * ends with the full result in its d_out arrays.  All ranks must issue the same sequence of
+ * searches with the same q and k.
+ *
+ *   bitsknn_sharded_unique_id  fills BITSKNN_SHARDED_ID_BYTES bytes (an ncclUniqueId) on one
+ *                              rank; the caller distributes them to the others
+ *   bitsknn_sharded_create     makes the handle and its own NCCL communicator from that id
+ *                              (collective: every rank calls it, with its device current)
+ *   bitsknn_sharded_init       the same over a communicator the caller owns (an ncclComm_t);
+ *                              world == 1 needs neither NCCL nor a communicator (NULL)
+ *   bitsknn_sharded_workspace_bytes  exchange buffers the caller provides (0 for one shard)
+ *   ..._search_select / ..._search_fused  one search; stream-ordered: the result is complete
+ *                              for work queued on `stream` after the call
+ *   ..._submit_select          the same search, but `stream` does not wait for the exchange and
+ *                              the merge, so they overlap the next search's local kernel (two
+ *                              buffer slots); bitsknn_sharded_drain makes `stream` wait for
+ *                              everything submitted
+ *   bitsknn_sharded_destroy    synchronises the handle's stream, frees its events, stream and
+ *                              (if it made it) the communicator
+ * NCCL is looked up at run time (libnccl.so.2); without it these calls return BITSKNN_ERR_COMM
+ * for world > 1 and the rest of the library is unaffected.
+ * --------------------------------------------------------------------------------------- */
+#define BITSKNN_SHARDED_ID_BYTES 128
+typedef struct bitsknn_sharded bitsknn_sharded_t;
+int bitsknn_sharded_unique_id(void* id);
+int bitsknn_sharded_create(bitsknn_sharded_t** handle, const void* id, int rank, int world);
+int bitsknn_sharded_init(bitsknn_sharded_t** handle, void* nccl_comm, int rank, int world);
+int bitsknn_sharded_destroy(bitsknn_sharded_t* handle);
+size_t bitsknn_sharded_workspace_bytes(const bitsknn_sharded_t* handle, int64_t q, int k);
+int bitsknn_sharded_search_select(bitsknn_sharded_t* handle, const float* d_dist, int64_t ld, int64_t q,
+                                  int64_t n_local, int k, int32_t shard_begin, float* d_out_dist,
+                                  int32_t* d_out_idx, void* d_workspace, size_t workspace_bytes,
+                                  bitsknn_stream_t stream);
+int bitsknn_sharded_submit_select(bitsknn_sharded_t* handle, const float* d_dist, int64_t ld, int64_t q,
+                                  int64_t n_local, int k, int32_t shard_begin, float* d_out_dist,
+                                  int32_t* d_out_idx, void* d_workspace, size_t workspace_bytes,
+                                  bitsknn_stream_t stream);
+int bitsknn_sharded_search_fused(bitsknn_sharded_t* handle, const float* d_points, const float* d_queries,
+                                 int64_t n_local, int64_t q, int dim, int k, int mode, int32_t shard_begin,
+                                 float* d_out_dist, int32_t* d_out_idx, void* d_fused_workspace,
+                                 size_t fused_workspace_bytes, void* d_workspace, size_t workspace_bytes,
+                                 bitsknn_stream_t stream);
+int bitsknn_sharded_drain(bitsknn_sharded_t* handle, bitsknn_stream_t stream);
 
 #ifdef __cplusplus
 }

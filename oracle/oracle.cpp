@@ -342,6 +342,68 @@ void oracle_knn(const float* points, const float* queries, std::size_t n, std::s
     }
 }
 
+// The CPU k-NN flow as the reference's `parallel` algorithm runs it, without the matrix in between:
+// per query (OpenMP) the distance to every point -- the FMA chains of partial_l2_ops
+// (include/bits/distance/abstract_gemm.cuh:139-169; its CPU distance, src/distance/eigen_distance.cpp:39-43,
+// computes the same partial form) or of l2_ops (:79-93) -- fed into the max-heap of
+// src/topk/parallel_knn.cpp:30-65 (`top > d` replaces the top), final sort of the k survivors.
+// This is the routine the benchmark times as the CPU baseline of the k-NN paths.  Requires k <= n.
+void oracle_knn_heap(const float* points, const float* queries, std::size_t n, std::size_t q,
+                     std::size_t dim, std::size_t k, int partial, float* out_dist, std::int32_t* out_idx)
+{
+#pragma omp parallel
+    {
+        std::vector<pair_t> heap(k);
+#pragma omp for schedule(dynamic, 1)
+        for (std::size_t i = 0; i < q; ++i)
+        {
+            const float* qv = queries + i * dim;
+            auto distance = [&](std::size_t j) {
+                const float* pv = points + j * dim;
+                if (partial != 0)
+                {
+                    float dot = 0.0F;
+                    float nrm = 0.0F;
+                    for (std::size_t c = 0; c < dim; ++c)
+                    {
+                        dot = std::fmaf(qv[c], pv[c], dot);
+                        nrm = std::fmaf(pv[c], pv[c], nrm);
+                    }
+                    return nrm - 2.0F * dot;
+                }
+                float acc = 0.0F;
+                for (std::size_t c = 0; c < dim; ++c)
+                {
+                    const float diff = qv[c] - pv[c];
+                    acc = std::fmaf(diff, diff, acc);
+                }
+                return acc;
+            };
+            for (std::size_t j = 0; j < k; ++j)
+            {
+                heap[j] = pair_t{distance(j), static_cast<std::int32_t>(j)};
+            }
+            std::make_heap(heap.begin(), heap.end(), pair_less);
+            for (std::size_t j = k; j < n; ++j)
+            {
+                const float d = distance(j);
+                if (heap.front().distance > d)
+                {
+                    std::pop_heap(heap.begin(), heap.end(), pair_less);
+                    heap.back() = pair_t{d, static_cast<std::int32_t>(j)};
+                    std::push_heap(heap.begin(), heap.end(), pair_less);
+                }
+            }
+            std::sort(heap.begin(), heap.end(), pair_less);
+            for (std::size_t j = 0; j < k; ++j)
+            {
+                out_dist[i * k + j] = heap[j].distance;
+                out_idx[i * k + j] = heap[j].index;
+            }
+        }
+    }
+}
+
 // Merge `lists` candidate lists of k pairs per query into the k smallest pairs.
 // Candidates are addressed as cand[list * list_stride + query * query_stride + j]; this
 // is pass 2 of the reference's split-row scheme (src/topk/singlepass/bits_knn.cu:170-183:

@@ -54,6 +54,8 @@ def lib():
         L.oracle_knn.restype = None
         L.oracle_knn.argtypes = [_f32p, _f32p, _sz, _sz, _sz, _sz, ctypes.c_int, ctypes.c_int32,
                                  _f32p, _i32p]
+        L.oracle_knn_heap.restype = None
+        L.oracle_knn_heap.argtypes = [_f32p, _f32p, _sz, _sz, _sz, _sz, ctypes.c_int, _f32p, _i32p]
         L.oracle_merge.restype = None
         L.oracle_merge.argtypes = [_f32p, _i32p, _sz, _sz, _sz, _sz, _sz, _f32p, _i32p]
         L.oracle_checksum.restype = ctypes.c_uint32
@@ -140,6 +142,16 @@ def knn(points, queries, k, partial=True, index_base=0):
     out_i = np.empty((q, k), dtype=np.int32)
     lib().oracle_knn(_f(points), _f(queries), n, q, dim, k, 1 if partial else 0, index_base,
                      _f(out_d), _i(out_i))
+    return out_d, out_i
+
+
+def knn_heap(points, queries, k, partial=True):
+    """The CPU k-NN flow (distance chains + max-heap per query, OpenMP over the queries)."""
+    n, dim = points.shape
+    q = queries.shape[0]
+    out_d = np.empty((q, k), dtype=np.float32)
+    out_i = np.empty((q, k), dtype=np.int32)
+    lib().oracle_knn_heap(_f(points), _f(queries), n, q, dim, k, 1 if partial else 0, _f(out_d), _i(out_i))
     return out_d, out_i
 
 

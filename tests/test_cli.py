@@ -27,7 +27,7 @@ def test_header_and_help(knn):
     r = run(knn, "--help")
     assert r.returncode == 0
     for name in ("serial", "parallel", "partial-bitonic-regs", "bits", "bits-prefetch", "bits-sq", "fused-cache", "magma-dist",
-                 "magma-part-dist"):
+                 "magma-part-dist", "bits-sharded"):
         assert f"- {name}\n" in r.stderr
     for flag in ("--algorithm", "--repeat", "--knn", "--number", "--query", "--dimension", "--generator",
                  "--preprocessor", "--seed", "--block-size", "--items-per-thread", "--verify", "--point-layout",
@@ -101,6 +101,25 @@ def test_fused_labels_equal_serial_labels(knn, cuda, args):
         assert r.returncode == 0, r.stderr
         sums.append(r.stderr.strip())
     assert sums[0] == sums[1] == sums[2] and sums[0].startswith("Checksum: ")
+
+
+@pytest.mark.gpu
+def test_expired_device_wait_makes_the_next_phase_throw(knn, cuda):
+    # host/selftest.cpp: for several registry entries, selection() after the library's diagnostic
+    # kernel gave up its bounded wait must throw, and the next selection() gives the old result
+    exe = KNN.parent / "host_selftest"
+    r = subprocess.run([str(exe)], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and r.stdout.strip() == "ok", r.stdout + r.stderr
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("alg", ["bits-sharded", "bits-sharded-bf16"])
+def test_sharded_id_verifies_against_serial(knn, cuda, alg):
+    # uses every visible GPU (one on a single-GPU box: the same code path without the exchange)
+    r = run(knn, "-a", alg, "-n", "100000", "-q", "64", "-k", "32", "-d", "8", "--seed", "11", "--verify", "serial")
+    assert r.returncode == 0, r.stderr
+    assert "Difference" not in r.stderr
+    assert r.stderr.count("Checksum:") == 1
 
 
 @pytest.mark.gpu

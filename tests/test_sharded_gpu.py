@@ -1,6 +1,7 @@
-"""The sharded-search host layer on one GPU (world size 1): `select`, `knn` and the stream form
-`submit_select` / `drain` go through the CUDA kernels and must agree with the plain calls.  The
-multi-rank exchange itself is covered by the gloo test on CPU and by `bench.py --gpus N`."""
+"""The sharded search on one GPU (world size 1) through `bitsknn_sharded_*`: `select`, `knn` and the
+submit form `submit_select` / `drain` must agree with the plain calls.  The multi-rank exchange is
+covered by test_sharded_multi_gpu.py (two or more GPUs), the gloo test of the host logic on CPU and
+the checks inside `bench.py --gpus N`."""
 import pytest
 import torch
 
@@ -18,12 +19,15 @@ def test_single_rank_search_equals_plain_calls(bk, cuda):
     search = sharded.ShardedSearch(bk, 0, 1)
     got_d, got_i = search.select(matrix, k, 0)
     assert torch.equal(got_d, want_d) and torch.equal(got_i, want_i)
-    # stream form: three searches, results identical to the plain call
+    # submit form: three searches; a submit hands back the previous search's output, drain the last
+    done = []
     for step in range(3):
-        done = search.submit_select(torch.roll(matrix, step, dims=0).contiguous(), k, 0)
+        done.append(search.submit_select(torch.roll(matrix, step, dims=0).contiguous(), k, 0))
+    done.append(search.drain())
+    assert done[0] is None and search.drain() is None
+    for step in range(3):
         exp_d, exp_i = bk.select(torch.roll(matrix, step, dims=0).contiguous(), k)
-        assert torch.equal(done[0], exp_d) and torch.equal(done[1], exp_i)
-    assert search.drain() is None
+        assert torch.equal(done[step + 1][0], exp_d) and torch.equal(done[step + 1][1], exp_i)
     # shard offset = global labels
     off_d, off_i = search.select(matrix, k, 1000)
     assert torch.equal(off_d, want_d) and torch.equal(off_i, want_i + 1000)
@@ -34,3 +38,16 @@ def test_single_rank_search_equals_plain_calls(bk, cuda):
     torch.cuda.synchronize()
     bk.device_status()
     assert torch.equal(kd, fd) and torch.equal(ki, fi)
+    search.close()
+
+
+def test_argument_checks_of_the_sharded_entry_points(bk, cuda):
+    import ctypes
+    lib = bk.lib()
+    handle = ctypes.c_void_p()
+    assert lib.bitsknn_sharded_create(ctypes.byref(handle), None, 2, 2) == bk.ERR_INVALID_ARGUMENT   # rank >= world
+    assert lib.bitsknn_sharded_create(ctypes.byref(handle), None, 0, 2) == bk.ERR_INVALID_ARGUMENT   # no id
+    assert lib.bitsknn_sharded_init(ctypes.byref(handle), None, 0, 2) == bk.ERR_INVALID_ARGUMENT     # no communicator
+    h = bk.sharded_create(None, 0, 1)
+    assert bk.sharded_workspace_bytes(h, 100, 10) == 0
+    bk.sharded_destroy(h)

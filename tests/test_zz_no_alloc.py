@@ -24,6 +24,12 @@ def test_static_scratch_selection_matches_workspace_selection(bk, cuda):
         torch.cuda.synchronize()
         assert torch.cuda.memory_allocated() == before        # nothing came from torch's allocator
         bk.device_status()
+        # ... nor from the driver: after that warm call (the first call on a device loads the kernels
+        # and looks up the array), a second call leaves the device's free memory where it was
+        free_before = torch.cuda.mem_get_info()[0]
+        bk.select_split_static(dist, k, splits, out=out)
+        torch.cuda.synchronize()
+        assert torch.cuda.mem_get_info()[0] == free_before
         assert np.array_equal(out[0].cpu().numpy().view(np.uint32), want_d.cpu().numpy().view(np.uint32))
         assert np.array_equal(out[1].cpu().numpy(), want_i.cpu().numpy())
 
