@@ -810,17 +810,14 @@ def main():
         desc_host = desc.cpu().numpy() if (desc is not None and not args.no_cpu and not args.no_e2e) else None
         del desc
         torch.cuda.empty_cache()
-        # ablation: the same kernel without its radius filter (the reference's partial-bitonic-regs):
-        # what the buffer + filter buy on uniform rows
-        bk.set_tuning("select.filter", 0)
-        try:
+        # ablations (the reference's partial-bitonic-regs / partial-bitonic-buffered-static): what the
+        # filtered buffer and the register-resident list buy on uniform rows
+        for name, variant in (("without_buffer", bk.ABLATION_NO_BUFFER), ("list_in_shared_memory", bk.ABLATION_SHARED_LIST)):
             od = torch.empty((q, 32), dtype=torch.float32, device=dev)
             oi = torch.empty((q, 32), dtype=torch.int32, device=dev)
-            ms = timed_ms(lambda: bk.select(matrix, 32, out=(od, oi)), 1)
-            sweep["uniform_k32_without_filter"] = {"ms": ms, "distances_per_s": q * n / (ms * 1e-3),
-                                                   "frac_of_hbm_peak": (4.0 * q * n + 8.0 * q * 32) / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}
-        finally:
-            bk.set_tuning("select.filter", 1)
+            ms = timed_ms(lambda: bk.select_ablation(matrix, 32, variant, out=(od, oi)), 1)
+            sweep[f"uniform_k32_{name}"] = {"ms": ms, "distances_per_s": q * n / (ms * 1e-3),
+                                           "frac_of_hbm_peak": (4.0 * q * n + 8.0 * q * 32) / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}
 
     # ---- end to end through the C ABI from host buffers (`e2e`) ----------------------------
     e2e = None

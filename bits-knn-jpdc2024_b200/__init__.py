@@ -42,6 +42,7 @@ SIGNATURES = {
     "bitsknn_tuning_key": (ctypes.c_char_p, [_int]),
     "bitsknn_kernel_ms": (_int, [ctypes.c_char_p, ctypes.POINTER(ctypes.c_float)]),
     "bitsknn_select": (_int, [_ptr, _i64, _ptr, _i64, _ptr, _i64, _i64, _int, _ptr, _ptr, _ptr]),
+    "bitsknn_select_ablation": (_int, [_ptr, _i64, _i64, _i64, _int, _int, _ptr, _ptr, _ptr]),
     "bitsknn_select_auto_splits": (_int, [_i64, _i64, _int]),
     "bitsknn_select_split_workspace_bytes": (_sz, [_i64, _int, _int]),
     "bitsknn_select_split": (_int, [_ptr, _i64, _ptr, _i64, _i64, _int, _int, _ptr, _sz, _ptr, _ptr, _ptr]),
@@ -62,6 +63,7 @@ SIGNATURES = {
                                             _ptr, _sz, _ptr, _sz, _ptr]),
     "bitsknn_sharded_drain": (_int, [_ptr, _ptr]),
     "bitsknn_l2_workspace_bytes": (_sz, [_i64, _i64, _int, _int]),
+    "bitsknn_transpose": (_int, [_ptr, _i64, _i64, _ptr, _ptr]),
     "bitsknn_l2": (_int, [_ptr, _ptr, _i64, _i64, _int, _int, _ptr, _i64, _ptr, _sz, _ptr]),
     "bitsknn_fused_workspace_bytes": (_sz, [_i64, _i64, _int, _int, _int]),
     "bitsknn_fused": (_int, [_ptr, _ptr, _i64, _i64, _int, _int, _int, ctypes.c_int32, _ptr, _ptr, _ptr, _sz, _ptr]),
@@ -177,6 +179,22 @@ def select(dist, k, labels=None, label_offsets=None, n=None, out=None):
     return out
 
 
+ABLATION_NO_BUFFER, ABLATION_SHARED_LIST = 0, 1
+
+
+def select_ablation(dist, k, variant, out=None):
+    """The selection without its radius filter / with its list in shared memory (ablations)."""
+    import torch
+    _device_check(dist, torch.float32, "dist")
+    q, n = dist.shape
+    ld = dist.stride(0) if q > 1 else n
+    if out is None:
+        out = (torch.empty((q, k), dtype=torch.float32, device=dist.device),
+               torch.empty((q, k), dtype=torch.int32, device=dist.device))
+    _check(lib().bitsknn_select_ablation(_p(dist), ld, q, n, k, variant, _p(out[0]), _p(out[1]), _stream()))
+    return out
+
+
 def select_auto_splits(q, n, k):
     return int(lib().bitsknn_select_auto_splits(q, n, k))
 
@@ -279,6 +297,18 @@ def l2(points, queries, mode=L2_EXACT, out=None, workspace=None):
         workspace = torch.empty(need, dtype=torch.uint8, device=points.device)
     _check(lib().bitsknn_l2(_p(points), _p(queries), n, q, dim, mode, _p(out), out.stride(0) if q > 1 else n,
                             _p(workspace), 0 if workspace is None else workspace.numel(), _stream()))
+    return out
+
+
+def transpose(src, out=None):
+    """(rows, cols) float32 CUDA matrix -> its (cols, rows) transpose, on the device."""
+    import torch
+    _device_check(src, torch.float32, "src")
+    assert src.is_contiguous()
+    rows, cols = src.shape
+    if out is None:
+        out = torch.empty((cols, rows), dtype=torch.float32, device=src.device)
+    _check(lib().bitsknn_transpose(_p(src), rows, cols, _p(out), _stream()))
     return out
 
 

@@ -20,7 +20,7 @@ LIB_DIR = PKG / "lib"
 OBJ_DIR = LIB_DIR / "obj"
 LIB = LIB_DIR / "libbitsknn.so"
 
-SOURCES = ["abi.cu", "select.cu", "merge.cu", "sharded.cu", "l2.cu", "l2_tc.cu", "fused.cu", "fused_tiled.cu", "fused_tc.cu"]
+SOURCES = ["abi.cu", "select.cu", "ablation.cu", "merge.cu", "sharded.cu", "l2.cu", "l2_tc.cu", "fused.cu", "fused_tiled.cu", "fused_tc.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

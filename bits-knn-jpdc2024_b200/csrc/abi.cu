@@ -32,8 +32,6 @@ tuning_entry g_tuning[] = {
     {"select.stage_bytes", 0, 0, 65536},
     {"select.stages", 0, 0, 8},
     {"select.merge_at", 0, 0, 100},
-    {"select.wide_block", 1, 0, 1},
-    {"select.filter", 1, 0, 1},
     {"select.unroll", 0, 0, 4},
     {"fused.variant", 2, 0, 2},
     {"fused.tc_mma_n", 0, 0, 256},

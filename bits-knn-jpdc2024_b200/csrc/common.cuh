@@ -66,10 +66,11 @@ int balanced_parts(int64_t query_tiles, int slots, int64_t max_parts);
 int device_sm_count();
 
 // bitsknn_select with `label_base` added to every implicit label (the global index of the first
-// column when the matrix is one shard of a wider one).  Defined in select.cu.
+// column when the matrix is one shard of a wider one); `no_filter` switches the radius filter off
+// (ablation).  Defined in select.cu.
 int select_rows(const float* d_dist, int64_t ld, const int32_t* d_labels, int64_t ld_labels,
                 const int32_t* d_label_offsets, int32_t label_base, int64_t q, int64_t n, int k, float* d_out_dist,
-                int32_t* d_out_idx, cudaStream_t stream);
+                int32_t* d_out_idx, cudaStream_t stream, bool no_filter = false);
 
 // Merge of `lists` candidate lists of `kin` pairs per query (pair j of list l of query i at
 // [l * list_stride + i * query_stride + j]) into the `k` smallest pairs; `bias` (nullable, one

@@ -205,6 +205,68 @@ __global__ void __launch_bounds__(L2_THREADS, 2)
 
 using namespace bitsknn;
 
+namespace bitsknn
+{
+
+namespace
+{
+
+// dst[c][r] = src[r][c] for a rows x cols matrix: 32 x 32 tiles through a padded shared-memory
+// tile so that both the loads and the stores are coalesced.
+__global__ void __launch_bounds__(256) transpose_kernel(const float* __restrict__ src, int64_t rows, int64_t cols,
+                                                        float* __restrict__ dst)
+{
+    __shared__ float tile[32][33];
+    const int tx = threadIdx.x & 31;
+    const int ty = threadIdx.x >> 5; // 0..7
+    const int64_t c0 = static_cast<int64_t>(blockIdx.x) * 32;
+    const int64_t r0 = static_cast<int64_t>(blockIdx.y) * 32;
+#pragma unroll
+    for (int i = 0; i < 32; i += 8)
+    {
+        const int64_t r = r0 + ty + i;
+        const int64_t c = c0 + tx;
+        tile[ty + i][tx] = (r < rows && c < cols) ? src[r * cols + c] : 0.0F;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 32; i += 8)
+    {
+        const int64_t c = c0 + ty + i;
+        const int64_t r = r0 + tx;
+        if (c < cols && r < rows)
+        {
+            dst[c * rows + r] = tile[tx][ty + i];
+        }
+    }
+}
+
+} // namespace
+
+} // namespace bitsknn
+
+extern "C" int bitsknn_transpose(const float* d_src, int64_t rows, int64_t cols, float* d_dst, bitsknn_stream_t stream)
+{
+    using namespace bitsknn;
+    if (d_src == nullptr || d_dst == nullptr)
+    {
+        return fail(BITSKNN_ERR_INVALID_ARGUMENT, "null pointer argument");
+    }
+    if (rows < 0 || cols < 0 || (rows + 31) / 32 > 65535 || (cols + 31) / 32 > 0x7fffffffLL)
+    {
+        return fail(BITSKNN_ERR_INVALID_ARGUMENT, "invalid sizes: rows=%lld cols=%lld (at most 2097120 rows)",
+                    static_cast<long long>(rows), static_cast<long long>(cols));
+    }
+    if (rows == 0 || cols == 0)
+    {
+        return BITSKNN_OK;
+    }
+    const dim3 grid(static_cast<unsigned>((cols + 31) / 32), static_cast<unsigned>((rows + 31) / 32));
+    transpose_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(d_src, rows, cols, d_dst);
+    BITSKNN_CUDA_TRY(cudaGetLastError());
+    return BITSKNN_OK;
+}
+
 extern "C" size_t bitsknn_l2_workspace_bytes(int64_t n, int64_t q, int dim, int mode)
 {
     if (mode == BITSKNN_L2_TF32 || mode == BITSKNN_L2_BF16)

@@ -6,7 +6,7 @@
 // stages guarded by mbarriers; the threads read the stages with 128-bit loads, keep only the
 // values below the running k-th pair ("radius"), append the survivors to a shared-memory
 // candidate buffer by warp-aggregated slot allocation, and fold the buffer into a sorted,
-// register-resident list of L = 256 * IPT pairs with bitonic networks when it fills up.
+// register-resident list of L = THREADS * IPT pairs with bitonic networks when it fills up.
 //
 // The algorithm is the reference's buffered partial bitonic sort
 // (include/bits/topk/singlepass/detail/bits_kernel.cuh:317-408: filter by radius :117-126,
@@ -14,10 +14,16 @@
 // wants it to:
 //   * bulk-copy ring instead of per-thread 4-byte loads + prefetch.global.L2 (:221-259);
 //   * an optimistic pass per stage with ONE barrier (survivors are rare once the radius has
-//     settled) that falls back to the reference's barrier-per-batch loop only when the
-//     buffer would overflow;
-//   * one ballot-free warp scan + one shared atomic per warp instead of one atomic per
-//     survivor;
+//     settled), redone only when the buffer (2 L slots) would overflow;
+//   * a DENSE stage -- more survivors than the buffer has room for: the first stage of a row, or
+//     rows that arrive in descending order, where every value passes the filter -- is not pushed
+//     through the buffer batch by batch (the reference sorts and merges every buffered value,
+//     :145-199, 383-391, which makes its adversarial case seven times slower than its random
+//     case).  The stage already sits in shared memory, so it is cut down first: a sorted sample
+//     of L of its values proposes a pivot with at least L and at most `room` survivors at or
+//     below it; only those enter the buffer and are sorted and merged -- everything above the
+//     pivot cannot be among the L smallest.  The reference's batch loop stays as the last resort;
+//   * warp ballots + one shared atomic per warp instead of one atomic per survivor;
 //   * every comparison is on the (distance, index) pair, so the output is the unique
 //     lowest-index answer whatever the arrival order of candidates.
 #include <algorithm>
@@ -36,7 +42,6 @@ namespace bitsknn
 namespace
 {
 
-constexpr int SELECT_THREADS = 256;
 constexpr int MAX_STAGES = 8;
 
 struct select_params
@@ -55,7 +60,7 @@ struct select_params
     int32_t* out_idx; // [rows * splits][k]
     int raw_pad;      // 1: leave padding as (+inf, PAD_IDX) (candidate lists for a later merge)
     int no_filter;    // 1: never tighten the radius: every value is buffered, sorted and merged (ablation)
-    int stage_floats; // floats per stage, a multiple of 4 * SELECT_THREADS
+    int stage_floats; // floats per stage, a multiple of 4 * THREADS
     int stages;
     int merge_at;     // fold the buffer as soon as it holds this many candidates (<= L)
     int* status;
@@ -63,255 +68,719 @@ struct select_params
 
 struct select_ctrl
 {
-    int count;  // slow path: allocated slots (may exceed L)
-    int inc[3]; // fast path: slots allocated during stage c, in inc[c % 3]
-    float r_d;  // radius pair, written by the owner of list element k-1
+    int count;         // guaranteed path / head and tail / after a fold: entries in the buffer
+    int inc[3];        // optimistic path: slots allocated during stage c, in inc[c % 3]
+    int warp_sums[32]; // block-wide counts
+    float r_d;         // radius pair, written by the owner of list element k-1 (fold) or the pivot (plan)
     int r_x;
+    int dense;         // plan: the stage was dense
 };
 
-template <int THREADS, int IPT>
-struct select_block
+// What a block knows about its row besides the list: passed by value to the out-of-line parts.
+struct row_ctx
 {
-    static constexpr int L = THREADS * IPT;
-
-    float ld[IPT]; // the sorted list (ascending), blocked arrangement
-    int lx[IPT];
-    float r_d; // radius = k-th smallest pair seen so far
-    int r_x;
-    float* buf_d;
+    float* buf_d; // candidate buffer, 2 L slots
     int* buf_x;
     select_ctrl* ctrl;
     const int32_t* labp; // explicit labels of this slice or nullptr
     int lab0;            // implicit label of slice element 0
     int k;
-    bool keep_radius;    // the un-buffered ablation: the filter radius stays at +inf
+    float r_d; // radius = k-th smallest pair seen so far
+    int r_x;
+    bool keep_radius; // the un-buffered ablation: the filter radius stays at +inf
+};
 
-    __device__ __forceinline__ int label_of(int e) const { return labp != nullptr ? labp[e] : lab0 + e; }
+__device__ __forceinline__ int label_of(const row_ctx& s, int e) { return s.labp != nullptr ? s.labp[e] : s.lab0 + e; }
 
-    // Folds the first `valid` buffer entries into the list and refreshes the radius.
-    // Entered and left with all threads; leaves the buffer empty (ctrl->count = 0).
-    __device__ __forceinline__ void fold(int valid)
+// Evaluates the filter on one 4-vector; returns the number of survivors of this lane.
+__device__ __forceinline__ int filter4(const row_ctx& s, const float4& val, bool live, int e0, float (&dv)[4],
+                                       int (&lab)[4], bool (&pr)[4])
+{
+    dv[0] = val.x;
+    dv[1] = val.y;
+    dv[2] = val.z;
+    dv[3] = val.w;
+    int cnt = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
     {
-        const int tid = threadIdx.x;
+        pr[j] = false;
+        lab[j] = 0;
+        if (live && dv[j] <= s.r_d)
+        {
+            lab[j] = label_of(s, e0 + j);
+            pr[j] = pair_lt(dv[j], lab[j], s.r_d, s.r_x);
+        }
+        cnt += pr[j] ? 1 : 0;
+    }
+    return cnt;
+}
+
+// Slot offsets of this lane's survivors inside the warp's allocation: one ballot per vector
+// component, no dependent shuffle chain.  Returns the warp's total.
+__device__ __forceinline__ int warp_slots(const bool (&pr)[4], int (&off)[4])
+{
+    const unsigned below = (1U << (threadIdx.x & 31)) - 1U;
+    int total = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+    {
+        const unsigned b = __ballot_sync(FULL_MASK, pr[j]);
+        off[j] = total + __popc(b & below);
+        total += __popc(b);
+    }
+    return total;
+}
+
+// Optimistic insertion of one 4-vector (whole warp): survivors beyond the capacity `cap` are
+// dropped; the caller detects that from the stage's slot count and redoes the stage.
+__device__ __forceinline__ void insert_fast(const row_ctx& s, int cap, const float4& val, bool live, int e0, int count0,
+                                            int* inc)
+{
+    float dv[4];
+    int lab[4];
+    bool pr[4];
+    int off[4];
+    filter4(s, val, live, e0, dv, lab, pr);
+    const int total = warp_slots(pr, off);
+    if (total == 0)
+    {
+        return;
+    }
+    int base = 0;
+    if ((threadIdx.x & 31) == 0)
+    {
+        base = atomicAdd(inc, total);
+    }
+    base = count0 + __shfl_sync(FULL_MASK, base, 0);
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+    {
+        const int pos = base + off[j];
+        if (pr[j] && pos < cap)
+        {
+            s.buf_d[pos] = dv[j];
+            s.buf_x[pos] = lab[j];
+        }
+    }
+}
+
+// Optimistic insertion by a single lane (no warp cooperation): used when hits are sparse.
+__device__ __forceinline__ void insert_lane(const row_ctx& s, int cap, const float4& val, int e0, int count0, int* inc)
+{
+    const float dv[4] = {val.x, val.y, val.z, val.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+    {
+        if (dv[j] <= s.r_d)
+        {
+            const int lab = label_of(s, e0 + j);
+            if (pair_lt(dv[j], lab, s.r_d, s.r_x))
+            {
+                const int pos = count0 + atomicAdd(inc, 1);
+                if (pos < cap)
+                {
+                    s.buf_d[pos] = dv[j];
+                    s.buf_x[pos] = lab;
+                }
+            }
+        }
+    }
+}
+
+// One pass over a stage with the current radius: every survivor takes a slot of `inc`
+// (optimistic: slots beyond the capacity are dropped).  UNROLL vectors per thread are examined
+// under one warp vote.
+template <int THREADS, int UNROLL>
+__device__ __forceinline__ void scan_stage(const row_ctx& s, int cap, const float4* sv, int nv, int e_base, int count0,
+                                           int* inc)
+{
+    constexpr int SPARSE_LANES = 6; // up to this many lanes with a candidate: per-lane insertion
+    const int tid = threadIdx.x;
+    int vb = 0;
+    // groups of UNROLL vectors per thread, no bounds checks; one vote per group
+    for (; vb + THREADS * UNROLL <= nv; vb += THREADS * UNROLL)
+    {
+        float4 val[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u)
+        {
+            val[u] = sv[vb + u * THREADS + tid];
+        }
+        float mn[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u)
+        {
+            mn[u] = fminf(fminf(val[u].x, val[u].y), fminf(val[u].z, val[u].w));
+        }
+        float mall = mn[0];
+#pragma unroll
+        for (int u = 1; u < UNROLL; ++u)
+        {
+            mall = fminf(mall, mn[u]);
+        }
+        const unsigned hitters = __ballot_sync(FULL_MASK, mall <= s.r_d);
+        if (hitters == 0)
+        {
+            continue;
+        }
+        if (__popc(hitters) <= SPARSE_LANES)
+        {
+            // few lanes saw a candidate: they take slots one by one, the others idle
+            if (mall <= s.r_d)
+            {
+#pragma unroll
+                for (int u = 0; u < UNROLL; ++u)
+                {
+                    if (mn[u] <= s.r_d)
+                    {
+                        insert_lane(s, cap, val[u], e_base + 4 * (vb + u * THREADS + tid), count0, inc);
+                    }
+                }
+            }
+        }
+        else
+        {
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u)
+            {
+                const bool hit = mn[u] <= s.r_d;
+                if (__any_sync(FULL_MASK, hit))
+                {
+                    insert_fast(s, cap, val[u], hit, e_base + 4 * (vb + u * THREADS + tid), count0, inc);
+                }
+            }
+        }
+    }
+    // ragged end of the last stage
+    for (; vb < nv; vb += THREADS)
+    {
+        const int v = vb + tid;
+        const bool live = v < nv;
+        const float4 val = live ? sv[v] : make_float4(INFINITY, INFINITY, INFINITY, INFINITY);
+        const bool hit = live && fminf(fminf(val.x, val.y), fminf(val.z, val.w)) <= s.r_d;
+        if (__any_sync(FULL_MASK, hit))
+        {
+            insert_fast(s, cap, val, hit, e_base + 4 * v, count0, inc);
+        }
+    }
+}
+
+// ---- the parts that run a few times per row ---------------------------------------------------
+
+// Folds buffer entries into the list, L at a time, and publishes the new radius in ctrl->r_d/r_x.
+// Whole chunks of L are always folded; a remainder is folded too (padded) when it holds at least
+// `keep_below` entries, else it is moved to the front of the buffer and stays a candidate.
+// Returns the number of entries left in the buffer.  Entered and left with all threads.
+template <int THREADS, int IPT>
+__device__ __forceinline__ int fold_buffer(float (&ld)[IPT], int (&lx)[IPT], row_ctx s, int valid, int keep_below)
+{
+    constexpr int L = THREADS * IPT;
+    const int tid = threadIdx.x;
+    int base = 0;
+    for (; base < valid; base += L)
+    {
+        const int here = valid - base < L ? valid - base : L;
+        if (here < L && here < keep_below)
+        {
+            break;
+        }
         float cd[IPT];
         int cx[IPT];
 #pragma unroll
         for (int r = 0; r < IPT; ++r)
         {
-            const int s = r * THREADS + tid;
-            const bool in = s < valid;
-            cd[r] = in ? buf_d[s] : INFINITY;
-            cx[r] = in ? buf_x[s] : PAD_IDX;
+            const int e = r * THREADS + tid;
+            const bool in = e < here;
+            cd[r] = in ? s.buf_d[base + e] : INFINITY;
+            cx[r] = in ? s.buf_x[base + e] : PAD_IDX;
         }
-        __syncthreads(); // the buffer now doubles as exchange scratch of the networks
-        block_fold<THREADS, IPT>(ld, lx, cd, cx, buf_d, buf_x, tid);
+        __syncthreads(); // these L slots now double as exchange scratch of the networks
+        block_fold<THREADS, IPT>(ld, lx, cd, cx, s.buf_d + base, s.buf_x + base, tid);
+    }
+    const int left = base < valid ? valid - base : 0;
+    float md[IPT];
+    int mx[IPT];
+    if (left > 0 && base > 0)
+    {
+        // the remainder moves to the front (it is shorter than a chunk: one read, barrier, write)
 #pragma unroll
         for (int r = 0; r < IPT; ++r)
         {
-            if (tid * IPT + r == k - 1)
+            const int e = r * THREADS + tid;
+            md[r] = e < left ? s.buf_d[base + e] : 0.0F;
+            mx[r] = e < left ? s.buf_x[base + e] : 0;
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < IPT; ++r)
+    {
+        if (tid * IPT + r == s.k - 1)
+        {
+            s.ctrl->r_d = ld[r];
+            s.ctrl->r_x = lx[r];
+        }
+    }
+    if (tid == 0)
+    {
+        s.ctrl->count = left;
+    }
+    __syncthreads();
+    if (left > 0 && base > 0)
+    {
+#pragma unroll
+        for (int r = 0; r < IPT; ++r)
+        {
+            const int e = r * THREADS + tid;
+            if (e < left)
             {
-                ctrl->r_d = ld[r];
-                ctrl->r_x = lx[r];
+                s.buf_d[e] = md[r];
+                s.buf_x[e] = mx[r];
             }
         }
-        if (tid == 0)
-        {
-            ctrl->count = 0;
-        }
-        __syncthreads();
-        if (!keep_radius)
-        {
-            r_d = ctrl->r_d;
-            r_x = ctrl->r_x;
-        }
     }
+    return left;
+}
 
-    // Evaluates the filter on one 4-vector; returns the number of survivors of this lane.
-    __device__ __forceinline__ int filter4(const float4& val, bool live, int e0, float (&dv)[4], int (&lab)[4],
-                                           bool (&pr)[4]) const
+// Guaranteed insertion of one stage: the reference's scheme (bits_kernel.cuh:277-302,
+// 383-391) -- allocate slots for a batch of THREADS*4 values, write those that fit, fold
+// the full buffer and retry the rest.  Leaves the number of buffered entries in ctrl->count and
+// the radius in ctrl->r_d/r_x.
+template <int THREADS, int IPT>
+__device__ __forceinline__ void stage_slow(float (&ld)[IPT], int (&lx)[IPT], row_ctx s, const float4* sv, int nv, int e_base,
+                                        int count0)
+{
+    constexpr int B = 2 * THREADS * IPT;
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    if (tid == 0)
     {
-        dv[0] = val.x;
-        dv[1] = val.y;
-        dv[2] = val.z;
-        dv[3] = val.w;
-        int cnt = 0;
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-        {
-            pr[j] = false;
-            lab[j] = 0;
-            if (live && dv[j] <= r_d)
-            {
-                lab[j] = label_of(e0 + j);
-                pr[j] = pair_lt(dv[j], lab[j], r_d, r_x);
-            }
-            cnt += pr[j] ? 1 : 0;
-        }
-        return cnt;
+        s.ctrl->count = count0;
+        s.ctrl->r_d = s.r_d;
+        s.ctrl->r_x = s.r_x;
     }
-
-    // Slot offsets of this lane's survivors inside the warp's allocation: one ballot per vector
-    // component, no dependent shuffle chain.  Returns the warp's total.
-    static __device__ __forceinline__ int warp_slots(const bool (&pr)[4], int (&off)[4])
+    __syncthreads();
+    for (int vb = 0; vb < nv; vb += THREADS)
     {
-        const unsigned below = (1U << (threadIdx.x & 31)) - 1U;
-        int total = 0;
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-        {
-            const unsigned b = __ballot_sync(FULL_MASK, pr[j]);
-            off[j] = total + __popc(b & below);
-            total += __popc(b);
-        }
-        return total;
-    }
-
-    // Optimistic insertion of one 4-vector (whole warp): survivors beyond the capacity are
-    // dropped; the caller detects that from the stage's slot count and redoes the stage.
-    __device__ __forceinline__ void insert_fast(const float4& val, bool live, int e0, int count0, int* inc)
-    {
+        const int v = vb + tid;
+        const bool live = v < nv;
+        const float4 val = live ? sv[v] : make_float4(INFINITY, INFINITY, INFINITY, INFINITY);
         float dv[4];
         int lab[4];
         bool pr[4];
-        int off[4];
-        filter4(val, live, e0, dv, lab, pr);
-        const int total = warp_slots(pr, off);
-        if (total == 0)
+        filter4(s, val, live, e_base + 4 * v, dv, lab, pr);
+        while (true)
         {
-            return;
-        }
-        int base = 0;
-        if ((threadIdx.x & 31) == 0)
-        {
-            base = atomicAdd(inc, total);
-        }
-        base = count0 + __shfl_sync(FULL_MASK, base, 0);
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-        {
-            const int pos = base + off[j];
-            if (pr[j] && pos < L)
+            // allocate slots for what is still pending, write what fits
+            int off[4];
+            const int total = warp_slots(pr, off);
+            int base = 0;
+            if (lane == 0 && total > 0)
             {
-                buf_d[pos] = dv[j];
-                buf_x[pos] = lab[j];
+                base = atomicAdd(&s.ctrl->count, total);
+            }
+            base = __shfl_sync(FULL_MASK, base, 0);
+            bool overflow = false;
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+            {
+                if (pr[j])
+                {
+                    const int pos = base + off[j];
+                    if (pos < B)
+                    {
+                        s.buf_d[pos] = dv[j];
+                        s.buf_x[pos] = lab[j];
+                        pr[j] = false;
+                    }
+                    else
+                    {
+                        overflow = true;
+                    }
+                }
+            }
+            if (__syncthreads_or(overflow ? 1 : 0) == 0)
+            {
+                break;
+            }
+            // the buffer is full: fold it, then offer the rest again under the tighter radius
+            // (unlike the reference, which carries every allocated slot over)
+            fold_buffer<THREADS, IPT>(ld, lx, s, B, 0);
+            if (!s.keep_radius)
+            {
+                s.r_d = s.ctrl->r_d;
+                s.r_x = s.ctrl->r_x;
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+            {
+                pr[j] = pr[j] && pair_lt(dv[j], lab[j], s.r_d, s.r_x);
             }
         }
     }
+}
 
-    // Optimistic insertion by a single lane (no warp cooperation): used when hits are sparse.
-    __device__ __forceinline__ void insert_lane(const float4& val, int e0, int count0, int* inc)
+// Number of values of the stage that pass the radius filter and are not above the pivot pair
+// (block-wide; two barriers).  A pivot that is itself a survivor is below the radius, so
+// everything at or below it passes the filter too and only the pivot is compared (BELOW_RADIUS).
+template <int THREADS, bool BELOW_RADIUS>
+__device__ __forceinline__ int count_stage(const row_ctx& s, const float4* sv, int nv, int e_base, float pd, int px)
+{
+    const int tid = threadIdx.x;
+    int c = 0;
+    for (int v = tid; v < nv; v += THREADS)
     {
+        const float4 val = sv[v];
         const float dv[4] = {val.x, val.y, val.z, val.w};
 #pragma unroll
         for (int j = 0; j < 4; ++j)
         {
-            if (dv[j] <= r_d)
+            if constexpr (BELOW_RADIUS)
             {
-                const int lab = label_of(e0 + j);
-                if (pair_lt(dv[j], lab, r_d, r_x))
+                c += dv[j] < pd ? 1 : 0;
+                if (dv[j] == pd)
                 {
-                    const int pos = count0 + atomicAdd(inc, 1);
-                    if (pos < L)
-                    {
-                        buf_d[pos] = dv[j];
-                        buf_x[pos] = lab;
-                    }
+                    c += label_of(s, e_base + 4 * v + j) <= px ? 1 : 0;
+                }
+            }
+            else
+            {
+                if (dv[j] <= s.r_d)
+                {
+                    c += pair_lt(dv[j], label_of(s, e_base + 4 * v + j), s.r_d, s.r_x) ? 1 : 0;
                 }
             }
         }
     }
-
-    // Guaranteed insertion of one stage: the reference's scheme (bits_kernel.cuh:277-302,
-    // 383-391) -- allocate slots for a batch of THREADS*4 values, write those that fit, fold
-    // the full buffer and retry the rest.  Returns the number of folds it needed.
-    __device__ __forceinline__ int stage_slow(const float4* sv, int nv, int e_base, int count0)
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
     {
-        const int tid = threadIdx.x;
-        const int lane = tid & 31;
-        int folds = 0;
-        if (tid == 0)
+        c += __shfl_xor_sync(FULL_MASK, c, o);
+    }
+    if ((tid & 31) == 0)
+    {
+        s.ctrl->warp_sums[tid >> 5] = c;
+    }
+    __syncthreads();
+    int total = 0;
+#pragma unroll
+    for (int w = 0; w < THREADS / 32; ++w)
+    {
+        total += s.ctrl->warp_sums[w];
+    }
+    __syncthreads();
+    return total;
+}
+
+// Decides how the survivors of a stage that the optimistic pass could not place (or that is
+// expected to be dense) reach the buffer.  Returns the number of values the next pass over the
+// stage will insert, or -1 when no pivot was found (the caller falls back to stage_slow).
+//   * no more survivors than the buffer has room for: the radius stays, all of them go in
+//     (ctrl->dense = 0);
+//   * a dense stage (ctrl->dense = 1): a sorted sample of L of its values proposes pivots until
+//     one has at least k and at most `room` survivors at or below it (preferably no more than fit
+//     one chunk of L, or little more than k when k is close to L).  That pivot, published in
+//     ctrl->r_d/r_x as an inclusive bound, becomes the radius of the pass (the fold that follows
+//     replaces it by the list's own radius, which is not above it); everything above the pivot
+//     cannot be among the k smallest pairs.
+// `expect_dense` skips the count of all survivors.  The buffer holds count0 < L candidates in
+// its first half; the second half is scratch here (sample sort, sorted samples).
+template <int THREADS, int IPT>
+__device__ __forceinline__ int plan_stage(row_ctx s, const float4* sv, int nv, int e_base, int count0, bool expect_dense)
+{
+    constexpr int L = THREADS * IPT;
+    constexpr int B = 2 * L;
+    const int tid = threadIdx.x;
+    const int total = 4 * nv;
+    const int room = B - count0;
+    if (!expect_dense)
+    {
+        const int survivors = count_stage<THREADS, false>(s, sv, nv, e_base, 0.0F, 0);
+        if (survivors <= room)
         {
-            ctrl->count = count0;
+            if (tid == 0)
+            {
+                s.ctrl->dense = 0;
+            }
+            __syncthreads();
+            return survivors;
+        }
+    }
+    float* scr_d = s.buf_d + L;
+    int* scr_x = s.buf_x + L;
+    // sorted sample of L values of the stage (values that fail the filter count as padding)
+    {
+        float sd[IPT];
+        int sx[IPT];
+#pragma unroll
+        for (int r = 0; r < IPT; ++r)
+        {
+            const int e = tid * IPT + r;
+            sd[r] = INFINITY;
+            sx[r] = PAD_IDX;
+            if (total >= L || e < total)
+            {
+                const int at = total >= L ? static_cast<int>((static_cast<int64_t>(e) * total) / L) : e;
+                const float v = reinterpret_cast<const float*>(sv)[at];
+                const int lab = label_of(s, e_base + at);
+                if (pair_lt(v, lab, s.r_d, s.r_x))
+                {
+                    sd[r] = v;
+                    sx[r] = lab;
+                }
+            }
+        }
+        block_sort<THREADS, IPT>(sd, sx, false, scr_d, scr_x, tid);
+#pragma unroll
+        for (int r = 0; r < IPT; ++r)
+        {
+            scr_d[tid * IPT + r] = sd[r];
+            scr_x[tid * IPT + r] = sx[r];
         }
         __syncthreads();
-        for (int vb = 0; vb < nv; vb += THREADS)
+    }
+    // Acceptable: k <= c <= room.  Preferred: one chunk (c <= L) when k leaves space for that,
+    // else at most a quarter chunk beyond k (what is beyond a chunk stays in the buffer).
+    const int k = s.k;
+    const bool one_chunk = 4 * k <= 3 * L;
+    const int want_hi = one_chunk ? L : (k + L / 4 < room ? k + L / 4 : room);
+    const int target = (k + want_hi) / 2;
+    int lo = -1; // largest sample rank known to have fewer than k survivors at or below it
+    int hi = L;  // smallest sample rank known to have more than want_hi
+    int best_j = -1; // a sample inside [k, room] but above want_hi, in case nothing better turns up
+    int best_c = 0;
+    // the j-th smallest sample has about (j + 1) * total / L survivors at or below it
+    int j = static_cast<int>((static_cast<int64_t>(target) * L) / (total > 0 ? total : 1)) - 1;
+    j = j < 0 ? 0 : (j > L - 1 ? L - 1 : j);
+    int chosen = -1;
+    int chosen_c = 0;
+    for (int it = 0; it < 8; ++it)
+    {
+        const float pd = scr_d[j];
+        const int px = scr_x[j];
+        int c = room + 1; // a padding sample is at or above every survivor
+        if (px != PAD_IDX)
         {
-            const int v = vb + tid;
-            const bool live = v < nv;
-            const float4 val = live ? sv[v] : make_float4(INFINITY, INFINITY, INFINITY, INFINITY);
-            float dv[4];
-            int lab[4];
-            bool pr[4];
-            filter4(val, live, e_base + 4 * v, dv, lab, pr);
-            while (true)
+            c = count_stage<THREADS, true>(s, sv, nv, e_base, pd, px);
+        }
+        if (c >= k && c <= want_hi)
+        {
+            chosen = j;
+            chosen_c = c;
+            break;
+        }
+        if (c < k)
+        {
+            lo = j;
+        }
+        else
+        {
+            hi = j;
+            if (c <= room && (best_j < 0 || c < best_c))
             {
-                // allocate slots for what is still pending, write what fits
-                int off[4];
-                const int total = warp_slots(pr, off);
-                int base = 0;
-                if (lane == 0 && total > 0)
-                {
-                    base = atomicAdd(&ctrl->count, total);
-                }
-                base = __shfl_sync(FULL_MASK, base, 0);
-                bool overflow = false;
-#pragma unroll
-                for (int j = 0; j < 4; ++j)
-                {
-                    if (pr[j])
-                    {
-                        const int pos = base + off[j];
-                        if (pos < L)
-                        {
-                            buf_d[pos] = dv[j];
-                            buf_x[pos] = lab[j];
-                            pr[j] = false;
-                        }
-                        else
-                        {
-                            overflow = true;
-                        }
-                    }
-                }
-                if (__syncthreads_or(overflow ? 1 : 0) == 0)
-                {
-                    break;
-                }
-                // the buffer is full: fold it, then offer the rest again under the tighter radius
-                // (unlike the reference, which carries every allocated slot over)
-                fold(L);
-                ++folds;
-#pragma unroll
-                for (int j = 0; j < 4; ++j)
-                {
-                    pr[j] = pr[j] && pair_lt(dv[j], lab[j], r_d, r_x);
-                }
+                best_j = j;
+                best_c = c;
             }
         }
-        return folds;
+        if (hi - lo <= 1)
+        {
+            break;
+        }
+        int64_t next = (c > 0 && c <= room) ? (static_cast<int64_t>(j + 1) * target) / c - 1 : (lo + hi) / 2;
+        if (next <= lo || next >= hi)
+        {
+            next = (lo + hi) / 2;
+        }
+        j = static_cast<int>(next);
     }
+    if (chosen < 0)
+    {
+        chosen = best_j;
+        chosen_c = best_c;
+    }
+    if (chosen < 0)
+    {
+        if (expect_dense)
+        {
+            // the stage was not dense after all: if all its survivors fit, they simply go in
+            const int survivors = count_stage<THREADS, false>(s, sv, nv, e_base, 0.0F, 0);
+            if (survivors <= room)
+            {
+                if (tid == 0)
+                {
+                    s.ctrl->dense = 0;
+                }
+                __syncthreads();
+                return survivors;
+            }
+        }
+        return -1;
+    }
+    if (tid == 0)
+    {
+        // inclusive bound for the strict filter: labels are integers
+        s.ctrl->r_d = scr_d[chosen];
+        s.ctrl->r_x = scr_x[chosen] + 1;
+        s.ctrl->dense = 1;
+    }
+    __syncthreads(); // the bound is published; every thread is done with the scratch half
+    return chosen_c;
+}
+
+// Position of a block in its row: which chunk comes next, where the ring and the rotating
+// counters stand, how many candidates wait in the buffer, the radius.  Lives in local memory and
+// is only read and written when stream_row() is entered and left.
+struct stream_state
+{
+    int c;          // next chunk
+    int st;         // its stage                      (c % stages)
+    uint32_t phase; // parity of that stage's use     ((c / stages) & 1)
+    int i3;         // c % 3
+    int count0;     // candidates in the buffer; identical in every thread
+    int dense_run;  // dense stages in a row
+    float r_d;      // radius = k-th smallest pair seen so far
+    int r_x;
 };
 
-template <int THREADS, int IPT, int UNROLL>
-__global__ void __launch_bounds__(THREADS) select_kernel(const select_params p)
+// What does not change while a row is scanned.
+struct row_layout
 {
-    using block_t = select_block<THREADS, IPT>;
-    constexpr int L = block_t::L;
-    constexpr int SPARSE_LANES = 6; // up to this many lanes with a candidate: per-lane insertion
+    float* stage_base;
+    uint64_t* bars;
+    const float* stream; // first streamed element of the row (16-byte aligned)
+    int h;               // elements before it (labels of the stream start at h)
+    int mid;             // streamed elements
+    int nchunks;
+    int CH;
+    int NST;
+    int merge_at;
+};
+
+enum stream_event
+{
+    EV_DONE = 0,     // the row is finished
+    EV_PLAN = 1,     // chunk c has arrived and is expected to be dense: nothing was done with it
+    EV_OVERFLOW = 2, // the optimistic pass over chunk c did not fit: it is to be forgotten
+    EV_FOLD = 3,     // the pass over chunk c went in and the buffer wants folding
+    EV_TIMEOUT = 4
+};
+
+__device__ __forceinline__ void issue_chunk(const row_layout& g, int c, int st)
+{
+    const int floats = (g.mid - c * g.CH) < g.CH ? (g.mid - c * g.CH) : g.CH;
+    ptx::mbar_expect_tx(&g.bars[st], static_cast<uint32_t>(floats) * 4U);
+    ptx::bulk_g2s(g.stage_base + static_cast<size_t>(st) * g.CH, g.stream + static_cast<int64_t>(c) * g.CH,
+                  static_cast<uint32_t>(floats) * 4U, &g.bars[st]);
+}
+
+// The streaming loop: stage after stage, one optimistic pass and one barrier each, for as long as
+// the survivors fit and the buffer does not want folding.  Everything else is reported to the
+// caller as an event, with the chunk in question still in its stage.  The caller runs it as the
+// inner loop of its event loop, so the compiler treats this loop, and not the sorting networks
+// of the event handlers, as the place where registers matter (64 per thread at four blocks per SM).
+template <int THREADS, int IPT, int UNROLL>
+__device__ __forceinline__ int stream_row(stream_state* state, row_ctx s, const row_layout& g)
+{
+    constexpr int B = 2 * THREADS * IPT;
+    const int tid = threadIdx.x;
+    int c = state->c;
+    int st = state->st;
+    uint32_t phase = state->phase;
+    int i3 = state->i3;
+    int count0 = state->count0;
+    const int dense_run = state->dense_run;
+    s.r_d = state->r_d;
+    s.r_x = state->r_x;
+    int event = EV_DONE;
+    for (; c < g.nchunks; ++c)
+    {
+        const float4* sv = reinterpret_cast<const float4*>(g.stage_base + static_cast<size_t>(st) * g.CH);
+        const int floats = (g.mid - c * g.CH) < g.CH ? (g.mid - c * g.CH) : g.CH;
+        const int nv = floats >> 2;
+        const int e_base = g.h + c * g.CH;
+        int* inc = &s.ctrl->inc[i3];
+
+        const bool arrived = ptx::mbar_wait_bounded(&g.bars[st], phase);
+        // no optimistic pass where it is bound to fail: the first stage (radius +inf), or after
+        // two dense stages in a row (the same decision in every thread)
+        const bool plan = (c == 0 || dense_run >= 2) && 4 * nv > B - count0 && !s.keep_radius;
+        if (arrived && !plan)
+        {
+            scan_stage<THREADS, UNROLL>(s, B, sv, nv, e_base, count0, inc);
+        }
+        // one barrier per stage: every thread is done reading the stage and adding to `inc`; a
+        // thread whose wait expired takes the whole block out with it
+        if (__syncthreads_or(arrived ? 0 : 1) != 0)
+        {
+            event = EV_TIMEOUT;
+            break;
+        }
+        if (plan)
+        {
+            event = EV_PLAN;
+            break;
+        }
+        const int added = *inc;
+        if (count0 + added > B)
+        {
+            event = EV_OVERFLOW; // some survivors were dropped
+            break;
+        }
+        count0 += added;
+        if (count0 >= g.merge_at)
+        {
+            event = EV_FOLD;
+            break;
+        }
+        if (tid == 0)
+        {
+            s.ctrl->inc[i3 == 0 ? 2 : i3 - 1] = 0; // slot of stage c+2: last read before this barrier
+            // every thread has passed a barrier after its last read of this stage
+            if (c + g.NST < g.nchunks)
+            {
+                issue_chunk(g, c + g.NST, st);
+            }
+        }
+        i3 = i3 == 2 ? 0 : i3 + 1;
+        if (++st == g.NST)
+        {
+            st = 0;
+            phase ^= 1U;
+        }
+    }
+    state->c = c;
+    state->st = st;
+    state->phase = phase;
+    state->i3 = i3;
+    state->count0 = count0;
+    return event;
+}
+
+// 64 registers per thread at most: four blocks of 256 threads (two of 512, one of 1024) per SM
+#ifndef BITSKNN_SELECT_MINBLOCKS
+#define BITSKNN_SELECT_MINBLOCKS (1024 / THREADS)
+#endif
+template <int THREADS, int IPT, int UNROLL>
+__global__ void __launch_bounds__(THREADS, BITSKNN_SELECT_MINBLOCKS) select_kernel(const select_params p)
+{
+    constexpr int L = THREADS * IPT;
+    constexpr int B = 2 * L;
 
     extern __shared__ __align__(128) unsigned char smem[];
     const int tid = threadIdx.x;
-    const int CH = p.stage_floats;
-    const int NST = p.stages;
 
-    float* stage_base = reinterpret_cast<float*>(smem);
-    block_t blk;
-    blk.buf_d = stage_base + static_cast<size_t>(NST) * CH;
-    blk.buf_x = reinterpret_cast<int*>(blk.buf_d + L);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(blk.buf_x + L);
-    blk.ctrl = reinterpret_cast<select_ctrl*>(bars + MAX_STAGES);
-    blk.k = p.k;
-    blk.keep_radius = p.no_filter != 0;
+    row_layout g;
+    g.CH = p.stage_floats;
+    g.NST = p.stages;
+    g.merge_at = p.merge_at;
+    g.stage_base = reinterpret_cast<float*>(smem);
+    row_ctx s;
+    s.buf_d = g.stage_base + static_cast<size_t>(g.NST) * g.CH;
+    s.buf_x = reinterpret_cast<int*>(s.buf_d + B);
+    g.bars = reinterpret_cast<uint64_t*>(s.buf_x + B);
+    s.ctrl = reinterpret_cast<select_ctrl*>(g.bars + MAX_STAGES);
+    s.k = p.k;
+    s.keep_radius = p.no_filter != 0;
 
     // which slice of which row
     const int64_t vrow = blockIdx.x;
@@ -320,223 +789,184 @@ __global__ void __launch_bounds__(THREADS) select_kernel(const select_params p)
     int64_t m64 = (p.n < begin + p.slice ? p.n : begin + p.slice) - begin;
     const int m = m64 > 0 ? static_cast<int>(m64) : 0;
     const float* rowp = p.dist + row * p.ld + begin;
-    blk.labp = p.labels != nullptr ? p.labels + row * p.ld_labels + begin : nullptr;
-    blk.lab0 = static_cast<int>(begin) + p.label_base + (p.label_offsets != nullptr ? p.label_offsets[row] : 0);
+    s.labp = p.labels != nullptr ? p.labels + row * p.ld_labels + begin : nullptr;
+    s.lab0 = static_cast<int>(begin) + p.label_base + (p.label_offsets != nullptr ? p.label_offsets[row] : 0);
 
     // [0,h): scalar head up to the first 16-byte boundary, [h,h+mid): streamed, then a tail < 4
     int h = static_cast<int>(((16U - (reinterpret_cast<uintptr_t>(rowp) & 15U)) & 15U) >> 2);
     h = h < m ? h : m;
-    const int mid = ((m - h) >> 2) << 2;
-    const int tail = m - h - mid;
-    const int nchunks = (mid + CH - 1) / CH;
+    g.h = h;
+    g.mid = ((m - h) >> 2) << 2;
+    const int tail = m - h - g.mid;
+    g.nchunks = (g.mid + g.CH - 1) / g.CH;
+    g.stream = rowp + h;
 
+    // the sorted list (ascending), blocked arrangement
+    float ld[IPT];
+    int lx[IPT];
 #pragma unroll
     for (int r = 0; r < IPT; ++r)
     {
-        blk.ld[r] = INFINITY;
-        blk.lx[r] = PAD_IDX;
+        ld[r] = INFINITY;
+        lx[r] = PAD_IDX;
     }
-    blk.r_d = INFINITY;
-    blk.r_x = PAD_IDX;
-
-    auto issue = [&](int c, int st) {
-        const int floats = (mid - c * CH) < CH ? (mid - c * CH) : CH;
-        ptx::mbar_expect_tx(&bars[st], static_cast<uint32_t>(floats) * 4U);
-        ptx::bulk_g2s(stage_base + static_cast<size_t>(st) * CH, rowp + h + static_cast<int64_t>(c) * CH,
-                      static_cast<uint32_t>(floats) * 4U, &bars[st]);
-    };
+    s.r_d = INFINITY;
+    s.r_x = PAD_IDX;
 
     if (tid == 0)
     {
-        for (int s = 0; s < NST; ++s)
+        for (int i = 0; i < g.NST; ++i)
         {
-            ptx::mbar_init(&bars[s], 1);
+            ptx::mbar_init(&g.bars[i], 1);
         }
-        blk.ctrl->count = 0;
-        blk.ctrl->inc[0] = 0;
-        blk.ctrl->inc[1] = 0;
-        blk.ctrl->inc[2] = 0;
+        s.ctrl->count = 0;
+        s.ctrl->inc[0] = 0;
+        s.ctrl->inc[1] = 0;
+        s.ctrl->inc[2] = 0;
         ptx::mbar_init_fence();
     }
     __syncthreads();
     if (tid == 0)
     {
-        for (int c = 0; c < NST && c < nchunks; ++c)
+        for (int c = 0; c < g.NST && c < g.nchunks; ++c)
         {
-            issue(c, c);
+            issue_chunk(g, c, c);
         }
     }
 
     // head and tail elements go straight into the buffer (at most 6 of them)
     if (tid < h + tail)
     {
-        const int e = tid < h ? tid : mid + tid;
+        const int e = tid < h ? tid : g.mid + tid;
         const float d = rowp[e];
-        const int lab = blk.label_of(e);
-        if (pair_lt(d, lab, blk.r_d, blk.r_x))
+        const int lab = label_of(s, e);
+        if (pair_lt(d, lab, s.r_d, s.r_x))
         {
-            const int pos = atomicAdd(&blk.ctrl->count, 1);
-            blk.buf_d[pos] = d;
-            blk.buf_x[pos] = lab;
+            const int pos = atomicAdd(&s.ctrl->count, 1);
+            s.buf_d[pos] = d;
+            s.buf_x[pos] = lab;
         }
     }
     __syncthreads();
-    int count0 = blk.ctrl->count; // candidates in the buffer; identical in every thread
-    bool go_slow = true;          // the first stage always overflows (radius = +inf)
-    bool timed_out = false;
-    int c = 0;
 
-    int st = 0;          // stage of chunk c            (c % NST without a division)
-    uint32_t phase = 0;  // parity of that stage's use  ((c / NST) & 1)
-    int i3 = 0;          // c % 3
+    stream_state state;
+    state.c = 0;
+    state.st = 0;
+    state.phase = 0;
+    state.i3 = 0;
+    state.count0 = s.ctrl->count;
+    state.dense_run = 0;
+    state.r_d = s.r_d;
+    state.r_x = s.r_x;
 
-    for (; c < nchunks; ++c)
+    while (true)
     {
-        const float4* sv = reinterpret_cast<const float4*>(stage_base + static_cast<size_t>(st) * CH);
-        const int floats = (mid - c * CH) < CH ? (mid - c * CH) : CH;
-        const int nv = floats >> 2;
-        const int e_base = h + c * CH;
-        int* inc = &blk.ctrl->inc[i3];
-
-        if (!ptx::mbar_wait_bounded(&bars[st], phase))
+        const int event = stream_row<THREADS, IPT, UNROLL>(&state, s, g);
+        if (event == EV_DONE)
         {
-            timed_out = true;
+            break;
         }
-
-        bool redo = go_slow;
-        if (!go_slow)
+        if (event == EV_TIMEOUT)
         {
-            int vb = 0;
-            // groups of UNROLL vectors per thread, no bounds checks; one vote per group
-            for (; vb + THREADS * UNROLL <= nv; vb += THREADS * UNROLL)
+            // report, let the copies still in flight land (bounded), and leave
+            for (int cc = state.c + 1; cc < g.nchunks && cc < state.c + g.NST; ++cc)
             {
-                float4 val[UNROLL];
-#pragma unroll
-                for (int u = 0; u < UNROLL; ++u)
+                ptx::mbar_wait_bounded(&g.bars[cc % g.NST], static_cast<uint32_t>((cc / g.NST) & 1), 1U << 16);
+            }
+            if (tid == 0)
+            {
+                atomicOr(p.status, DEVICE_STATUS_TIMEOUT);
+            }
+            return;
+        }
+        // chunk state.c sits in its stage and wants more than an optimistic pass
+        const int c = state.c;
+        const float4* sv = reinterpret_cast<const float4*>(g.stage_base + static_cast<size_t>(state.st) * g.CH);
+        const int floats = (g.mid - c * g.CH) < g.CH ? (g.mid - c * g.CH) : g.CH;
+        const int nv = floats >> 2;
+        const int e_base = g.h + c * g.CH;
+        int* inc = &s.ctrl->inc[state.i3];
+        int count0 = state.count0;
+        bool dense = false;
+        if (event == EV_PLAN || event == EV_OVERFLOW)
+        {
+            bool slow = s.keep_radius; // the un-buffered ablation sorts and merges every value
+            if (!slow)
+            {
+                if (event == EV_OVERFLOW)
                 {
-                    val[u] = sv[vb + u * THREADS + tid];
-                }
-                float mn[UNROLL];
-#pragma unroll
-                for (int u = 0; u < UNROLL; ++u)
-                {
-                    mn[u] = fminf(fminf(val[u].x, val[u].y), fminf(val[u].z, val[u].w));
-                }
-                float mall = mn[0];
-#pragma unroll
-                for (int u = 1; u < UNROLL; ++u)
-                {
-                    mall = fminf(mall, mn[u]);
-                }
-                const unsigned hitters = __ballot_sync(FULL_MASK, mall <= blk.r_d);
-                if (hitters == 0)
-                {
-                    continue;
-                }
-                if (__popc(hitters) <= SPARSE_LANES)
-                {
-                    // few lanes saw a candidate: they take slots one by one, the others idle
-                    if (mall <= blk.r_d)
+                    // the pass is forgotten; the barrier keeps the reset behind every thread's read of
+                    // the pass's count (a thread that read 0 instead would carry on alone)
+                    __syncthreads();
+                    if (tid == 0)
                     {
-#pragma unroll
-                        for (int u = 0; u < UNROLL; ++u)
-                        {
-                            if (mn[u] <= blk.r_d)
-                            {
-                                blk.insert_lane(val[u], e_base + 4 * (vb + u * THREADS + tid), count0, inc);
-                            }
-                        }
+                        *inc = 0;
                     }
+                }
+                // which of the stage's survivors go in, and under which radius
+                const int planned = plan_stage<THREADS, IPT>(s, sv, nv, e_base, count0, event == EV_PLAN);
+                if (planned < 0)
+                {
+                    slow = true;
                 }
                 else
                 {
-#pragma unroll
-                    for (int u = 0; u < UNROLL; ++u)
+                    dense = s.ctrl->dense != 0;
+                    if (dense)
                     {
-                        const bool hit = mn[u] <= blk.r_d;
-                        if (__any_sync(FULL_MASK, hit))
-                        {
-                            blk.insert_fast(val[u], hit, e_base + 4 * (vb + u * THREADS + tid), count0, inc);
-                        }
+                        s.r_d = s.ctrl->r_d;
+                        s.r_x = s.ctrl->r_x;
                     }
+                    scan_stage<THREADS, UNROLL>(s, B, sv, nv, e_base, count0, inc);
+                    __syncthreads();
+                    count0 += planned;
                 }
             }
-            // ragged end of the last stage
-            for (; vb < nv; vb += THREADS)
+            if (slow)
             {
-                const int v = vb + tid;
-                const bool live = v < nv;
-                const float4 val = live ? sv[v] : make_float4(INFINITY, INFINITY, INFINITY, INFINITY);
-                const bool hit = live && fminf(fminf(val.x, val.y), fminf(val.z, val.w)) <= blk.r_d;
-                if (__any_sync(FULL_MASK, hit))
+                stage_slow<THREADS, IPT>(ld, lx, s, sv, nv, e_base, count0);
+                count0 = s.ctrl->count;
+                if (!s.keep_radius)
                 {
-                    blk.insert_fast(val, hit, e_base + 4 * v, count0, inc);
+                    s.r_d = s.ctrl->r_d;
+                    s.r_x = s.ctrl->r_x;
                 }
             }
         }
-        // one barrier per stage: every thread is done reading the stage and adding to `inc`
-        if (__syncthreads_or(timed_out ? 1 : 0) != 0)
+        state.dense_run = dense ? state.dense_run + 1 : 0;
+        if (count0 >= g.merge_at)
         {
-            timed_out = true;
-            break;
-        }
-        if (!go_slow)
-        {
-            const int added = *inc;
-            if (count0 + added > L)
+            count0 = fold_buffer<THREADS, IPT>(ld, lx, s, count0, g.merge_at);
+            if (!s.keep_radius)
             {
-                redo = true; // some survivors were dropped: forget this pass, redo the stage
-            }
-            else
-            {
-                count0 += added;
+                s.r_d = s.ctrl->r_d;
+                s.r_x = s.ctrl->r_x;
             }
         }
+        // the stage is done: its counter slot of two stages on is cleared, its memory refilled
         if (tid == 0)
         {
-            blk.ctrl->inc[i3 == 0 ? 2 : i3 - 1] = 0; // slot of stage c+2: last read before this barrier
+            s.ctrl->inc[state.i3 == 0 ? 2 : state.i3 - 1] = 0;
+            if (c + g.NST < g.nchunks)
+            {
+                issue_chunk(g, c + g.NST, state.st);
+            }
         }
-        if (redo)
+        state.c = c + 1;
+        state.i3 = state.i3 == 2 ? 0 : state.i3 + 1;
+        if (++state.st == g.NST)
         {
-            const int folds = blk.stage_slow(sv, nv, e_base, count0);
-            count0 = blk.ctrl->count;
-            go_slow = folds > 1;
+            state.st = 0;
+            state.phase ^= 1U;
         }
-        if (count0 >= p.merge_at)
-        {
-            blk.fold(count0);
-            count0 = 0;
-        }
-        // every thread has passed a barrier after its last read of this stage
-        if (tid == 0 && c + NST < nchunks)
-        {
-            issue(c + NST, st);
-        }
-        i3 = i3 == 2 ? 0 : i3 + 1;
-        if (++st == NST)
-        {
-            st = 0;
-            phase ^= 1U;
-        }
+        state.count0 = count0;
+        state.r_d = s.r_d;
+        state.r_x = s.r_x;
     }
 
-    if (timed_out)
+    if (state.count0 > 0)
     {
-        // report, let the copies still in flight land (bounded), and leave
-        for (int cc = c + 1; cc < nchunks && cc < c + NST; ++cc)
-        {
-            ptx::mbar_wait_bounded(&bars[cc % NST], static_cast<uint32_t>((cc / NST) & 1), 1U << 16);
-        }
-        if (tid == 0)
-        {
-            atomicOr(p.status, DEVICE_STATUS_TIMEOUT);
-        }
-        return;
-    }
-
-    if (count0 > 0)
-    {
-        blk.fold(count0);
+        fold_buffer<THREADS, IPT>(ld, lx, s, state.count0, 0);
     }
 
     float* od = p.out_dist + vrow * p.k;
@@ -547,12 +977,12 @@ __global__ void __launch_bounds__(THREADS) select_kernel(const select_params p)
         const int e = tid * IPT + r;
         if (e < p.k)
         {
-            int x = blk.lx[r];
+            int x = lx[r];
             if (p.raw_pad == 0 && x == PAD_IDX)
             {
                 x = e; // the reference pads short rows with (+inf, position): bits_kernel.cuh:340-358
             }
-            od[e] = blk.ld[r];
+            od[e] = ld[r];
             ox[e] = x;
         }
     }
@@ -560,7 +990,8 @@ __global__ void __launch_bounds__(THREADS) select_kernel(const select_params p)
 
 size_t select_smem_bytes(int L, int stage_floats, int stages)
 {
-    return static_cast<size_t>(stages) * stage_floats * 4 + static_cast<size_t>(L) * 8 + MAX_STAGES * 8 +
+    // stages + candidate buffer (2 L pairs) + barriers + control
+    return static_cast<size_t>(stages) * stage_floats * 4 + static_cast<size_t>(2 * L) * 8 + MAX_STAGES * 8 +
            sizeof(select_ctrl);
 }
 
@@ -603,27 +1034,23 @@ int launch_select(select_params p, int64_t vrows, cudaStream_t stream)
 int dispatch_select(const select_params& p, int64_t vrows, cudaStream_t stream)
 {
     // smallest list that holds k: the reference's dynamic_switch_le over K
-    // (src/topk/singlepass/bits_knn.cu:44), with the list never shorter than the block
+    // (src/topk/singlepass/bits_knn.cu:44), with the list never shorter than the block.
     // Long lists take larger blocks (the reference's tuned shapes use 512 threads for k = 2048,
     // scripts/optima.csv:1282): more threads fold a list of the same length with fewer pairs, and
     // registers, per thread.
-    const int wide = tuning_value("select.wide_block", 1);
     if (p.k <= 256)
     {
         return launch_select<256, 1>(p, vrows, stream);
     }
     if (p.k <= 512)
     {
-        return wide != 0 ? launch_select<512, 1>(p, vrows, stream) : launch_select<256, 2>(p, vrows, stream);
+        return launch_select<512, 1>(p, vrows, stream);
     }
     if (p.k <= 1024)
     {
-        return wide != 0 ? launch_select<512, 2>(p, vrows, stream) : launch_select<256, 4>(p, vrows, stream);
+        return launch_select<512, 2>(p, vrows, stream);
     }
-    // the longest lists: 1024 threads with two pairs each (measured against 512 x 4 at q = 1024,
-    // n = 2^20, k = 2048: 1.74 ms against 2.00 on uniform rows, 4.5 against 5.5 per 128 descending rows;
-    // at k = 1024 the 512-thread block stays ahead on uniform rows, 1.09 ms against 1.25)
-    return wide != 0 ? launch_select<1024, 2>(p, vrows, stream) : launch_select<256, 8>(p, vrows, stream);
+    return launch_select<1024, 2>(p, vrows, stream);
 }
 
 int dispatch_merge(const float* cd, const int32_t* cx, int64_t list_stride, int64_t query_stride, int64_t q, int lists,
@@ -668,17 +1095,18 @@ int check_select_args(const float* d_dist, int64_t ld, int64_t q, int64_t n, int
 void fill_stream_config(select_params& p)
 {
     // 0 = automatic: the shapes measured best on B200 -- 3 x 16 KiB for 256-thread blocks
-    // (4 blocks per SM), 3 x 32 KiB for 512-thread blocks, 2 x 64 KiB for the longest lists
+    // (4 blocks per SM), 3 x 32 KiB for 512-thread blocks, 2 x 64 KiB for 1024-thread blocks
     int stage_bytes = tuning_value("select.stage_bytes", 0);
     int stages = tuning_value("select.stages", 0);
-    const bool wide = p.k > 256 && tuning_value("select.wide_block", 1) != 0;
+    const bool wide = p.k > 256;
+    const bool widest = p.k > 1024;
     if (stage_bytes <= 0)
     {
-        stage_bytes = !wide ? 16384 : (p.k > 1024 ? 65536 : 32768);
+        stage_bytes = !wide ? 16384 : (widest ? 65536 : 32768);
     }
     if (stages <= 0)
     {
-        stages = wide && p.k > 1024 ? 2 : 3;
+        stages = widest ? 2 : 3;
     }
     stage_bytes = std::max((stage_bytes / 4096) * 4096, 4096);
     p.stage_floats = stage_bytes / 4;
@@ -696,7 +1124,7 @@ namespace bitsknn
 
 int select_rows(const float* d_dist, int64_t ld, const int32_t* d_labels, int64_t ld_labels,
                 const int32_t* d_label_offsets, int32_t label_base, int64_t q, int64_t n, int k, float* d_out_dist,
-                int32_t* d_out_idx, cudaStream_t stream)
+                int32_t* d_out_idx, cudaStream_t stream, bool no_filter)
 {
     if (const int rc = check_select_args(d_dist, ld, q, n, k, d_out_dist, d_out_idx); rc != BITSKNN_OK)
     {
@@ -729,9 +1157,9 @@ int select_rows(const float* d_dist, int64_t ld, const int32_t* d_labels, int64_
     {
         return fail(BITSKNN_ERR_CUDA, "CUDA error. cannot resolve the device status word");
     }
-    // "select.filter" = 0 turns the radius filter off: the un-buffered partial bitonic sort the
-    // reference keeps as an ablation (partial-bitonic-regs, src/topk/singlepass/partial_bitonic.cu:217-294)
-    p.no_filter = tuning_value("select.filter", 1) == 0 ? 1 : 0;
+    // without the radius filter this is the un-buffered partial bitonic sort the reference keeps as
+    // an ablation (partial-bitonic-regs, src/topk/singlepass/partial_bitonic.cu:217-294)
+    p.no_filter = no_filter ? 1 : 0;
     fill_stream_config(p);
     return dispatch_select(p, q, stream);
 }

@@ -57,20 +57,23 @@ transfer_timer::~transfer_timer()
     }
 }
 
-void transfer_timer::begin()
+void transfer_timer::begin(cudaStream_t stream)
 {
     if (begin_ == nullptr)
     {
         BITS_CUCH(cudaEventCreate(&begin_));
         BITS_CUCH(cudaEventCreate(&end_));
     }
-    BITS_CUCH(cudaEventRecord(begin_, nullptr));
+    BITS_CUCH(cudaEventRecord(begin_, stream));
 }
 
-void transfer_timer::end()
+void transfer_timer::end(cudaStream_t stream, bool wait)
 {
-    BITS_CUCH(cudaEventRecord(end_, nullptr));
-    BITS_CUCH(cudaEventSynchronize(end_));
+    BITS_CUCH(cudaEventRecord(end_, stream));
+    if (wait)
+    {
+        BITS_CUCH(cudaEventSynchronize(end_));
+    }
     measured_ = true;
 }
 
@@ -80,6 +83,7 @@ float transfer_timer::seconds() const
     {
         return 0;
     }
+    BITS_CUCH(cudaEventSynchronize(end_));
     float ms = 0;
     BITS_CUCH(cudaEventElapsedTime(&ms, begin_, end_));
     return ms / 1e3F;
@@ -109,44 +113,100 @@ inline bool pair_less(const distance_pair& a, const distance_pair& b)
 
 } // namespace
 
+cuda_distance::~cuda_distance()
+{
+    release_pieces();
+    if (copy_stream_ != nullptr)
+    {
+        cudaStreamDestroy(copy_stream_);
+    }
+}
+
+void cuda_distance::release_pieces()
+{
+    for (auto& p : pieces_)
+    {
+        cudaEventDestroy(p.arrived);
+    }
+    pieces_.clear();
+    pieces_fresh_ = false;
+}
+
 void cuda_distance::prepare(const knn_args& args)
 {
     args_ = args;
+    release_pieces();
     dist_gpu_.release();
     points_gpu_.release();
     queries_gpu_.release();
+    staging_.release();
     points_gpu_ = device_buffer<float>{args_.point_count * args_.dim};
     queries_gpu_ = device_buffer<float>{args_.query_count * args_.dim};
     if (needs_matrix_)
     {
         dist_gpu_ = device_buffer<float>{args_.query_count * args_.point_count};
     }
-    // the device always holds row-major inputs; a column-major host matrix is transposed here
-    std::vector<float> tmp_points;
-    std::vector<float> tmp_queries;
-    const float* points = args_.points;
-    const float* queries = args_.queries;
-    if (args_.points_layout == matrix_layout::column_major)
+    if (copy_stream_ == nullptr)
     {
-        tmp_points = to_row_major(points, args_.point_count, args_.dim);
-        points = tmp_points.data();
+        BITS_CUCH(cudaStreamCreateWithFlags(&copy_stream_, cudaStreamNonBlocking));
     }
-    if (args_.queries_layout == matrix_layout::column_major)
+    const std::size_t n = args_.point_count;
+    const std::size_t q = args_.query_count;
+    const std::size_t dim = args_.dim;
+    const bool points_cm = args_.points_layout == matrix_layout::column_major;
+    const bool queries_cm = args_.queries_layout == matrix_layout::column_major;
+    // the device always holds row-major inputs; a column-major host matrix is uploaded as it is
+    // and transposed by a kernel on the copy stream
+    if (points_cm || queries_cm)
     {
-        tmp_queries = to_row_major(queries, args_.query_count, args_.dim);
-        queries = tmp_queries.data();
+        staging_ = device_buffer<float>{(points_cm ? n * dim : 0) + (queries_cm ? q * dim : 0)};
     }
-    timer_.begin();
-    BITS_CUCH(cudaMemcpyAsync(points_gpu_.data(), points, points_gpu_.size() * sizeof(float), cudaMemcpyHostToDevice,
-                              nullptr));
-    BITS_CUCH(cudaMemcpyAsync(queries_gpu_.data(), queries, queries_gpu_.size() * sizeof(float),
-                              cudaMemcpyHostToDevice, nullptr));
-    timer_.end();
-    if (needs_matrix_)
+    timer_.begin(copy_stream_);
+    if (queries_cm)
     {
-        BITS_CUCH(cudaMemsetAsync(dist_gpu_.data(), 0, dist_gpu_.size() * sizeof(float), nullptr));
+        float* raw = staging_.data() + (points_cm ? n * dim : 0);
+        BITS_CUCH(cudaMemcpyAsync(raw, args_.queries, q * dim * sizeof(float), cudaMemcpyHostToDevice, copy_stream_));
+        abi_check(bitsknn_transpose(raw, static_cast<std::int64_t>(dim), static_cast<std::int64_t>(q), queries_gpu_.data(),
+                                    copy_stream_));
     }
-    BITS_CUCH(cudaStreamSynchronize(nullptr));
+    else
+    {
+        BITS_CUCH(cudaMemcpyAsync(queries_gpu_.data(), args_.queries, q * dim * sizeof(float), cudaMemcpyHostToDevice,
+                                  copy_stream_));
+    }
+    // pieces of at least 16 MiB, four at most: the distance kernel of a piece can start while
+    // the next one is still on the bus
+    const std::size_t bytes = n * dim * sizeof(float);
+    const std::size_t count = points_cm ? 1 : std::min<std::size_t>(4, std::max<std::size_t>(1, bytes >> 24));
+    for (std::size_t i = 0; i < count; ++i)
+    {
+        piece p{i * n / count, (i + 1) * n / count, nullptr};
+        if (points_cm)
+        {
+            BITS_CUCH(cudaMemcpyAsync(staging_.data(), args_.points, bytes, cudaMemcpyHostToDevice, copy_stream_));
+            abi_check(bitsknn_transpose(staging_.data(), static_cast<std::int64_t>(dim), static_cast<std::int64_t>(n),
+                                        points_gpu_.data(), copy_stream_));
+        }
+        else
+        {
+            BITS_CUCH(cudaMemcpyAsync(points_gpu_.data() + p.begin * dim, args_.points + p.begin * dim,
+                                      (p.end - p.begin) * dim * sizeof(float), cudaMemcpyHostToDevice, copy_stream_));
+        }
+        BITS_CUCH(cudaEventCreateWithFlags(&p.arrived, cudaEventDisableTiming));
+        BITS_CUCH(cudaEventRecord(p.arrived, copy_stream_));
+        pieces_.push_back(p);
+    }
+    timer_.end(copy_stream_, /*wait*/ false);
+    pieces_fresh_ = true;
+}
+
+void cuda_distance::wait_inputs()
+{
+    for (const auto& p : pieces_)
+    {
+        BITS_CUCH(cudaStreamWaitEvent(nullptr, p.arrived, 0));
+    }
+    pieces_fresh_ = false;
 }
 
 const std::vector<float>& cuda_distance::matrix_cpu()
@@ -167,6 +227,20 @@ void gemm_distance::compute()
     {
         workspace_ = device_buffer<unsigned char>{need};
     }
+    if (pieces_fresh_ && pieces_.size() > 1)
+    {
+        // first computation after the upload: the columns of every piece as soon as it has arrived
+        pieces_fresh_ = false;
+        for (const auto& p : pieces_)
+        {
+            BITS_CUCH(cudaStreamWaitEvent(nullptr, p.arrived, 0));
+            abi_check(bitsknn_l2(points_gpu_.data() + p.begin * args_.dim, queries_gpu_.data(),
+                                 static_cast<std::int64_t>(p.end - p.begin), q, dim, mode_, dist_gpu_.data() + p.begin, n,
+                                 workspace_.data(), workspace_.size(), nullptr));
+        }
+        return;
+    }
+    wait_inputs();
     abi_check(bitsknn_l2(points_gpu_.data(), queries_gpu_.data(), n, q, dim, mode_, dist_gpu_.data(), n,
                          workspace_.data(), workspace_.size(), nullptr));
 }
@@ -258,14 +332,11 @@ void bits_knn::selection()
     end_phase();
 }
 
-void partial_bitonic_regs_knn::selection()
+void ablation_knn::selection()
 {
     const auto n = static_cast<std::int64_t>(point_count());
-    abi_check(bitsknn_set_tuning("select.filter", 0));
-    const int status = bitsknn_select(in_dist_gpu(), n, nullptr, 0, nullptr, static_cast<std::int64_t>(query_count()), n,
-                                      static_cast<int>(k()), out_dist_gpu(), out_label_gpu(), nullptr);
-    bitsknn_set_tuning("select.filter", 1);
-    abi_check(status);
+    abi_check(bitsknn_select_ablation(in_dist_gpu(), n, static_cast<std::int64_t>(query_count()), n, static_cast<int>(k()),
+                                      variant_, out_dist_gpu(), out_label_gpu(), nullptr));
     end_phase();
 }
 
@@ -297,6 +368,7 @@ void fused_knn::initialize(const knn_args& args)
 
 void fused_knn::selection()
 {
+    dist_impl_->wait_inputs();
     abi_check(bitsknn_fused(dist_impl_->points_gpu(), dist_impl_->queries_gpu(), static_cast<std::int64_t>(point_count()),
                             static_cast<std::int64_t>(query_count()), static_cast<int>(dim()), static_cast<int>(k()),
                             mode_, 0, out_dist_gpu(), out_label_gpu(), workspace_.data(), workspace_.size(), nullptr));
@@ -563,7 +635,8 @@ std::vector<std::unique_ptr<knn>> make_registry()
     std::vector<std::unique_ptr<knn>> algorithms;
     algorithms.push_back(std::make_unique<serial_knn>());
     algorithms.push_back(std::make_unique<parallel_knn>());
-    algorithms.push_back(std::make_unique<partial_bitonic_regs_knn>());
+    algorithms.push_back(std::make_unique<ablation_knn>("partial-bitonic-regs", BITSKNN_ABLATION_NO_BUFFER));
+    algorithms.push_back(std::make_unique<ablation_knn>("partial-bitonic-buffered-static", BITSKNN_ABLATION_SHARED_LIST));
     algorithms.push_back(std::make_unique<bits_knn>("bits"));
     algorithms.push_back(std::make_unique<bits_knn>("bits-prefetch"));
     algorithms.push_back(std::make_unique<bits_sq_knn>());

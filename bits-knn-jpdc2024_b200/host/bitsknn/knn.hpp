@@ -119,8 +119,9 @@ public:
     transfer_timer(const transfer_timer&) = delete;
     transfer_timer& operator=(const transfer_timer&) = delete;
     ~transfer_timer();
-    void begin();
-    void end();
+    // records on `stream`; end() waits for the region unless `wait` is false (then seconds() does)
+    void begin(cudaStream_t stream = nullptr);
+    void end(cudaStream_t stream = nullptr, bool wait = true);
     float seconds() const;
 
 private:
@@ -133,13 +134,20 @@ private:
 class cuda_distance
 {
 public:
-    virtual ~cuda_distance() = default;
+    virtual ~cuda_distance();
     cuda_distance() = default;
     cuda_distance(const cuda_distance&) = delete;
     cuda_distance& operator=(const cuda_distance&) = delete;
 
-    // Allocates device memory, copies the inputs (timed) and clears the matrix.
+    // Allocates device memory and uploads the inputs (timed).  The points travel in pieces on a
+    // copy stream of their own; a column-major host matrix is uploaded as it is and transposed on
+    // the device.  With page-locked host memory prepare() returns while copies are still in
+    // flight: compute() then starts on each piece as it arrives, and every other reader calls
+    // wait_inputs() first.  (The reference transposes on the host and uploads with two blocking
+    // copies, src/distance/magma_distance.cu:32-70.)
     virtual void prepare(const knn_args& args);
+    // Makes the legacy default stream wait for the uploads of prepare().
+    void wait_inputs();
     virtual void compute() = 0;
     virtual float transfer_seconds() const { return timer_.seconds(); }
     // Row-major q x n matrix on the device / downloaded to the host.
@@ -151,6 +159,18 @@ public:
     const float* queries_gpu() const { return queries_gpu_.data(); }
 
 protected:
+    struct piece
+    {
+        std::size_t begin; // first point of the piece
+        std::size_t end;
+        cudaEvent_t arrived;
+    };
+    void release_pieces();
+
+    std::vector<piece> pieces_;   // upload pieces of the points, in order
+    bool pieces_fresh_ = false;   // prepare() ran and no compute() has consumed the pieces yet
+    cudaStream_t copy_stream_ = nullptr;
+    device_buffer<float> staging_; // column-major inputs before their device transpose
     knn_args args_{};
     device_buffer<float> points_gpu_;  // always point_count x dim row major on the device
     device_buffer<float> queries_gpu_; // always query_count x dim row major on the device
@@ -254,14 +274,20 @@ private:
     device_buffer<unsigned char> workspace_; // candidates of the slices (only when splits_ > 1)
 };
 
-// `partial-bitonic-regs`: the same kernel with the radius filter switched off -- every value is
-// buffered, sorted and merged.  Kept, like in the reference (partial_bitonic.cu:217-294), to show
-// what the buffer and the filter buy.
-class partial_bitonic_regs_knn : public cuda_knn
+// `partial-bitonic-regs` (the selection kernel without its radius filter: every value is sorted
+// and merged) and `partial-bitonic-buffered-static` (filtered buffer, but list and networks in
+// shared memory).  Kept, like in the reference (partial_bitonic.cu:217-294,
+// partial_bitonic_buffered.cu:216-337), to show what the buffer and the register list buy.
+class ablation_knn : public cuda_knn
 {
 public:
-    std::string id() const override { return "partial-bitonic-regs"; }
+    ablation_knn(std::string id, int variant) : id_(std::move(id)), variant_(variant) {}
+    std::string id() const override { return id_; }
     void selection() override;
+
+private:
+    std::string id_;
+    int variant_;
 };
 
 // `bits-sq`: rows cut into `deg` slices, then merged (reference: single_query_bits).

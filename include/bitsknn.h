@@ -72,10 +72,6 @@ int bitsknn_selftest_bounded_wait(bitsknn_stream_t stream);
  *                         0 = automatic, the default: 50 for lists of up to 256 pairs, else 75)
  *   "select.unroll"       128-bit vectors per thread examined under one warp vote (0 = automatic,
  *                         2 or 4; other values are rejected)
- *   "select.wide_block"   1 = 512-thread blocks for 256 < k <= 1024 and 1024-thread blocks beyond
- *                         (default), 0 = 256-thread blocks
- *   "select.filter"       0 = bitsknn_select buffers, sorts and merges every value (no radius
- *                         filter): the reference's un-buffered ablation `partial-bitonic-regs`
  *   "fused.variant"       FP32 fused kernel: 0 = 8 queries per block, 1 = tiled (needs the
  *                         workspace), 2 = automatic (default)
  *   "fused.parts"         blocks per query tile of the tiled fused kernels, i.e. ranges the database
@@ -116,6 +112,21 @@ int bitsknn_kernel_ms(const char* kernel, float* ms);
 int bitsknn_select(const float* d_dist, int64_t ld, const int32_t* d_labels, int64_t ld_labels,
                    const int32_t* d_label_offsets, int64_t q, int64_t n, int k, float* d_out_dist,
                    int32_t* d_out_idx, bitsknn_stream_t stream);
+
+/* Ablation variants of the selection, same arguments and result as bitsknn_select with implicit
+ * labels.  Replace the reference's registry entries `partial-bitonic-regs`
+ * (src/topk/singlepass/partial_bitonic.cu:217-294: no buffer, every value sorted and merged) and
+ * `partial-bitonic-buffered-static` (src/topk/singlepass/partial_bitonic_buffered.cu:216-337:
+ * filtered buffer, but the sorted list and every network step in shared memory), which it keeps to
+ * show what the register-resident list and the buffer buy (scripts/run-bitonic-sort.sh:33-54,
+ * scripts/run-buffer.sh:65-75). */
+enum bitsknn_ablation
+{
+    BITSKNN_ABLATION_NO_BUFFER = 0,
+    BITSKNN_ABLATION_SHARED_LIST = 1
+};
+int bitsknn_select_ablation(const float* d_dist, int64_t ld, int64_t q, int64_t n, int k, int variant,
+                            float* d_out_dist, int32_t* d_out_idx, bitsknn_stream_t stream);
 
 /* Split-row selection: every row is cut into `splits` slices scanned by separate thread
  * blocks, whose candidates (q * splits * k pairs in the caller's workspace) are merged by a
@@ -206,6 +217,13 @@ enum bitsknn_l2_mode
     BITSKNN_L2_BF16 = 3
 };
 size_t bitsknn_l2_workspace_bytes(int64_t n, int64_t q, int dim, int mode);
+
+/* d_dst[c][r] = d_src[r][c] for a row-major rows x cols float32 matrix (rows <= 2097120), on the
+ * device.  For inputs that arrive coordinate-major (dim x n: rows = dim, cols = n): every entry
+ * point above takes vectors row-major, and this replaces the host-side transposes the reference
+ * runs before its uploads (src/distance/magma_distance.cu:32-50,
+ * src/topk/singlepass/fused_cache_knn.cu:159-194, src/main.cpp:333-343). */
+int bitsknn_transpose(const float* d_src, int64_t rows, int64_t cols, float* d_dst, bitsknn_stream_t stream);
 int bitsknn_l2(const float* d_points, const float* d_queries, int64_t n, int64_t q, int dim, int mode,
                float* d_dist, int64_t ld, void* d_workspace, size_t workspace_bytes,
                bitsknn_stream_t stream);

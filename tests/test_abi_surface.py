@@ -66,3 +66,39 @@ def test_tuning_registry(bk):
         assert err.status == bk.ERR_INVALID_ARGUMENT
     else:
         raise AssertionError("unknown tuning key accepted")
+
+
+def test_every_tuning_key_is_documented_in_the_header(bk):
+    header = (ROOT / "include" / "bitsknn.h").read_text()
+    keys = bk.tuning_keys()
+    assert keys, "no tuning keys registered"
+    for key in keys:
+        assert f'"{key}"' in header, key
+
+
+def test_tuning_values_that_do_not_exist_are_rejected(bk):
+    for bad in (1, 3):
+        try:
+            bk.set_tuning("select.unroll", bad)
+        except bk.BitsKnnError as err:
+            assert err.status == bk.ERR_INVALID_ARGUMENT
+        else:
+            raise AssertionError("select.unroll accepted a value without a kernel")
+    assert bk.get_tuning("select.unroll") == 0
+
+
+def test_more_row_slices_than_a_grid_holds_are_rejected(bk):
+    lib = bk.lib()
+    fake = ctypes.c_void_p(256)
+    # q * splits = 2^31: beyond the grid limit; the workspace claim is large enough, so only the limit can refuse
+    rc = lib.bitsknn_select_split(fake, 8, None, 1 << 20, 8, 1, 2048, fake, 1 << 62, fake, fake, None)
+    assert rc == bk.ERR_INVALID_ARGUMENT and "grid limit" in bk.last_error()
+
+
+def test_sharded_entry_points_validate_before_touching_a_device(bk):
+    lib = bk.lib()
+    handle = ctypes.c_void_p()
+    assert lib.bitsknn_sharded_create(ctypes.byref(handle), None, 3, 2) == bk.ERR_INVALID_ARGUMENT
+    assert lib.bitsknn_sharded_init(ctypes.byref(handle), None, 0, 0) == bk.ERR_INVALID_ARGUMENT
+    assert lib.bitsknn_sharded_workspace_bytes(None, 10, 10) == 0
+    assert lib.bitsknn_sharded_destroy(None) == bk.OK

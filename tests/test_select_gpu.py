@@ -136,16 +136,21 @@ def test_launch_shapes_do_not_change_results(bk, oracle, cuda, stage_bytes, stag
             bk.set_tuning(key, value)
 
 
-def test_unfiltered_ablation_gives_the_same_result(bk, oracle, cuda):
-    # "select.filter" = 0: every value is buffered, sorted and merged (partial-bitonic-regs)
-    bk.set_tuning("select.filter", 0)
-    try:
-        rng = np.random.default_rng(12)
-        for k in (16, 256, 600):
-            run_select(bk, oracle, rng.random((5, 30001), dtype=np.float32), k)
-            run_select(bk, oracle, rng.integers(0, 40, size=(3, 9000)).astype(np.float32), k)
-    finally:
-        bk.set_tuning("select.filter", 1)
+@pytest.mark.parametrize("variant", ["no_buffer", "shared_list"])
+def test_ablation_variants_give_the_same_result(bk, oracle, cuda, variant):
+    # no_buffer: every value is sorted and merged (partial-bitonic-regs); shared_list: filtered
+    # buffer, list and networks in shared memory (partial-bitonic-buffered-static)
+    which = bk.ABLATION_NO_BUFFER if variant == "no_buffer" else bk.ABLATION_SHARED_LIST
+    rng = np.random.default_rng(12)
+    for k in (1, 16, 100, 256, 600, 2048):
+        for dist in (rng.random((5, 30001), dtype=np.float32), rng.integers(0, 40, size=(3, 9000)).astype(np.float32),
+                     np.sort(rng.random((2, 5000), dtype=np.float32), axis=1)[:, ::-1].copy()):
+            got_d, got_i = bk.select_ablation(torch.from_numpy(dist).cuda(), k, which)
+            torch.cuda.synchronize()
+            bk.device_status()
+            want_d, want_i = oracle.select(dist, k)
+            assert np.array_equal(got_d.cpu().numpy().view(np.uint32), want_d.view(np.uint32)), (variant, k)
+            assert np.array_equal(got_i.cpu().numpy(), want_i), (variant, k)
 
 
 def test_expired_device_wait_is_reported_and_the_context_survives(bk, oracle, cuda):
