@@ -33,6 +33,8 @@ tuning_entry g_tuning[] = {
     {"select.stages", 0, 0, 8},
     {"select.merge_at", 0, 0, 100},
     {"select.unroll", 0, 0, 4},
+    {"select.threads", 0, 0, 1024},
+    {"select.ipt", 0, 0, 4},
     {"fused.variant", 2, 0, 2},
     {"fused.tc_mma_n", 0, 0, 256},
     {"fused.parts", 0, 0, 64},

@@ -20,6 +20,7 @@
 #include <cstdint>
 
 #include "common.cuh"
+#include "tuning_table.cuh"
 #include "sortnet.cuh"
 
 namespace bitsknn
@@ -46,12 +47,16 @@ constexpr int QT = 8;                  // queries per block = warps per block
 constexpr int PPT = 4;                 // points per thread
 constexpr int PT = FUSED_THREADS * PPT; // points per tile
 constexpr int DT = 4;                  // coordinates per staged tile
-// Automatic choice between the two FP32 kernels, from a sweep at q = 2^14, n = 2^20 on B200: the
-// tiled kernel wins from dim 16 on, and below that for short lists (its folds go through L2, the
-// 8-query kernel keeps its lists in registers): dim 4: 10.1 ms against 15.4 at k = 16, 16.5 against
-// 16.5 at k = 128, 29.9 against 17.3 at k = 256.
+// Automatic choice between the two FP32 kernels: the tuning table (tuning_table.inc, from a sweep at
+// q = 2^14, n = 2^20 on B200) first.  The tiled kernel wins from dim 16 on, and below that for short
+// lists (its folds go through L2, the 8-query kernel keeps its lists in registers): dim 4: 10.1 ms
+// against 15.4 at k = 16, 16.5 against 16.5 at k = 128, 29.9 against 17.3 at k = 256.
 inline bool fused_prefers_tiled(int dim, int k)
 {
+    if (const fused_shape* row = find_fused_shape(dim, k); row != nullptr)
+    {
+        return row->tiled != 0;
+    }
     return dim >= 16 || k <= 64 || (k <= 128 && dim >= 8);
 }
 

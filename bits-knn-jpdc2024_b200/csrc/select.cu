@@ -35,6 +35,7 @@
 #include "common.cuh"
 #include "ptx.cuh"
 #include "sortnet.cuh"
+#include "tuning_table.cuh"
 
 namespace bitsknn
 {
@@ -995,27 +996,88 @@ size_t select_smem_bytes(int L, int stage_floats, int stages)
            sizeof(select_ctrl);
 }
 
+// The launch shape of one selection: block size, pairs per thread, stage ring, fold threshold.
+// Knobs set by the caller win, then the tuning table (keyed by k and the number of row slices),
+// then the built-in rule.
+struct launch_shape
+{
+    int threads;
+    int ipt;
+    int stage_bytes;
+    int stages;
+    int merge_pct;
+    int unroll;
+};
+
+launch_shape resolve_shape(int k, int64_t vrows)
+{
+    // built-in rule: the smallest list that holds k (the reference's dynamic_switch_le over K,
+    // src/topk/singlepass/bits_knn.cu:44), with the list never shorter than the block.  Long lists
+    // take larger blocks (the reference's tuned shapes use 512 threads for k = 2048,
+    // scripts/optima.csv:1282): more threads fold a list of the same length with fewer pairs, and
+    // registers, per thread.  3 x 16 KiB stages for 256-thread blocks (4 blocks per SM), 3 x 32 KiB
+    // for 512-thread blocks, 2 x 64 KiB for 1024-thread blocks; half-full buffers are folded for
+    // lists of up to 256 pairs, three-quarter-full ones for longer lists, whose folds cost more
+    // against what an earlier tightening of the radius saves.
+    launch_shape shape{};
+    if (k <= 256)
+    {
+        shape = {256, 1, 16384, 3, 50, 2};
+    }
+    else if (k <= 512)
+    {
+        shape = {512, 1, 32768, 3, 75, 2};
+    }
+    else if (k <= 1024)
+    {
+        shape = {512, 2, 32768, 3, 75, 2};
+    }
+    else
+    {
+        shape = {1024, 2, 65536, 2, 75, 2};
+    }
+    if (const select_shape* row = find_select_shape(k, vrows); row != nullptr)
+    {
+        shape = {row->threads, row->ipt, row->stage_bytes, row->stages, row->merge_pct, row->unroll};
+    }
+    const int threads = tuning_value("select.threads", 0);
+    const int ipt = tuning_value("select.ipt", 0);
+    if (threads > 0 && ipt > 0 && threads * ipt >= k)
+    {
+        shape.threads = threads;
+        shape.ipt = ipt;
+    }
+    if (const int v = tuning_value("select.stage_bytes", 0); v > 0)
+    {
+        shape.stage_bytes = v;
+    }
+    if (const int v = tuning_value("select.stages", 0); v > 0)
+    {
+        shape.stages = v;
+    }
+    if (const int v = tuning_value("select.merge_at", 0); v > 0)
+    {
+        shape.merge_pct = v;
+    }
+    if (const int v = tuning_value("select.unroll", 0); v > 0)
+    {
+        shape.unroll = v;
+    }
+    return shape;
+}
+
 template <int THREADS, int IPT>
-int launch_select(select_params p, int64_t vrows, cudaStream_t stream)
+int launch_select(select_params p, const launch_shape& shape, int64_t vrows, cudaStream_t stream)
 {
     constexpr int L = THREADS * IPT;
-    // 0 = automatic: half-full buffers for lists of up to 256 pairs, three-quarter-full ones for
-    // longer lists, whose folds cost more against what an earlier tightening of the radius saves
-    int merge_pct = tuning_value("select.merge_at", 0);
-    if (merge_pct <= 0)
-    {
-        merge_pct = L <= 256 ? 50 : 75;
-    }
-    p.merge_at = std::max(1, (L * merge_pct) / 100);
+    p.merge_at = std::min(L, std::max(1, (L * shape.merge_pct) / 100));
     // a stage is a whole number of 4-vectors per thread
-    p.stage_floats = std::max(4 * THREADS, (p.stage_floats / (4 * THREADS)) * (4 * THREADS));
+    const int stage_bytes = std::max((shape.stage_bytes / 4096) * 4096, 4096);
+    p.stage_floats = std::max(4 * THREADS, (stage_bytes / 4 / (4 * THREADS)) * (4 * THREADS));
+    p.stages = std::min(std::max(shape.stages, 2), MAX_STAGES);
     const size_t smem = select_smem_bytes(L, p.stage_floats, p.stages);
     // 128-bit vectors per thread examined under one warp vote
-    // (0 = automatic: 2, which measured a little ahead of 4 for every block size: 0.83 ms against
-    // 0.85 at k = 512, 1.70 against 1.74 at k = 2048, no register spills at 4 blocks per SM for k <= 256)
-    int unroll = tuning_value("select.unroll", 0);
-    unroll = unroll != 0 ? unroll : 2;
-    auto kernel = unroll == 2 ? select_kernel<THREADS, IPT, 2> : select_kernel<THREADS, IPT, 4>;
+    auto kernel = shape.unroll == 4 ? select_kernel<THREADS, IPT, 4> : select_kernel<THREADS, IPT, 2>;
     if (smem > 227U * 1024U)
     {
         return fail(BITSKNN_ERR_INVALID_ARGUMENT,
@@ -1033,24 +1095,29 @@ int launch_select(select_params p, int64_t vrows, cudaStream_t stream)
 
 int dispatch_select(const select_params& p, int64_t vrows, cudaStream_t stream)
 {
-    // smallest list that holds k: the reference's dynamic_switch_le over K
-    // (src/topk/singlepass/bits_knn.cu:44), with the list never shorter than the block.
-    // Long lists take larger blocks (the reference's tuned shapes use 512 threads for k = 2048,
-    // scripts/optima.csv:1282): more threads fold a list of the same length with fewer pairs, and
-    // registers, per thread.
-    if (p.k <= 256)
+    const launch_shape shape = resolve_shape(p.k, vrows);
+    switch (shape.threads * 16 + shape.ipt)
     {
-        return launch_select<256, 1>(p, vrows, stream);
+    case 256 * 16 + 1:
+        return launch_select<256, 1>(p, shape, vrows, stream);
+    case 256 * 16 + 2:
+        return launch_select<256, 2>(p, shape, vrows, stream);
+    case 256 * 16 + 4:
+        return launch_select<256, 4>(p, shape, vrows, stream);
+    case 512 * 16 + 1:
+        return launch_select<512, 1>(p, shape, vrows, stream);
+    case 512 * 16 + 2:
+        return launch_select<512, 2>(p, shape, vrows, stream);
+    case 512 * 16 + 4:
+        return launch_select<512, 4>(p, shape, vrows, stream);
+    case 1024 * 16 + 1:
+        return launch_select<1024, 1>(p, shape, vrows, stream);
+    case 1024 * 16 + 2:
+        return launch_select<1024, 2>(p, shape, vrows, stream);
+    default:
+        return fail(BITSKNN_ERR_INVALID_ARGUMENT, "no selection kernel for %d threads x %d pairs per thread",
+                    shape.threads, shape.ipt);
     }
-    if (p.k <= 512)
-    {
-        return launch_select<512, 1>(p, vrows, stream);
-    }
-    if (p.k <= 1024)
-    {
-        return launch_select<512, 2>(p, vrows, stream);
-    }
-    return launch_select<1024, 2>(p, vrows, stream);
 }
 
 int dispatch_merge(const float* cd, const int32_t* cx, int64_t list_stride, int64_t query_stride, int64_t q, int lists,
@@ -1090,27 +1157,6 @@ int check_select_args(const float* d_dist, int64_t ld, int64_t q, int64_t n, int
         return fail(BITSKNN_ERR_INVALID_ARGUMENT, "distance matrix is not 4-byte aligned");
     }
     return BITSKNN_OK;
-}
-
-void fill_stream_config(select_params& p)
-{
-    // 0 = automatic: the shapes measured best on B200 -- 3 x 16 KiB for 256-thread blocks
-    // (4 blocks per SM), 3 x 32 KiB for 512-thread blocks, 2 x 64 KiB for 1024-thread blocks
-    int stage_bytes = tuning_value("select.stage_bytes", 0);
-    int stages = tuning_value("select.stages", 0);
-    const bool wide = p.k > 256;
-    const bool widest = p.k > 1024;
-    if (stage_bytes <= 0)
-    {
-        stage_bytes = !wide ? 16384 : (widest ? 65536 : 32768);
-    }
-    if (stages <= 0)
-    {
-        stages = widest ? 2 : 3;
-    }
-    stage_bytes = std::max((stage_bytes / 4096) * 4096, 4096);
-    p.stage_floats = stage_bytes / 4;
-    p.stages = std::min(std::max(stages, 2), MAX_STAGES);
 }
 
 } // namespace
@@ -1160,7 +1206,6 @@ int select_rows(const float* d_dist, int64_t ld, const int32_t* d_labels, int64_
     // without the radius filter this is the un-buffered partial bitonic sort the reference keeps as
     // an ablation (partial-bitonic-regs, src/topk/singlepass/partial_bitonic.cu:217-294)
     p.no_filter = no_filter ? 1 : 0;
-    fill_stream_config(p);
     return dispatch_select(p, q, stream);
 }
 
@@ -1187,7 +1232,12 @@ int resolve_splits(int64_t q, int64_t n, int k, int splits)
     // run 4 blocks of 256 threads per SM, the longest one block of 512 threads; more slices than
     // that only add warm-up (every slice finds its own radius) and merge work.
     const int sms = device_sm_count();
-    const int64_t want = static_cast<int64_t>(sms) * (k <= 64 ? 600 : (k <= 256 ? 400 : (k <= 1024 ? 200 : 130))) / 148;
+    int wanted = k <= 64 ? 600 : (k <= 256 ? 400 : (k <= 1024 ? 200 : 130));
+    if (const select_shape* row = find_select_shape(k, q); row != nullptr && row->blocks_wanted > 0)
+    {
+        wanted = row->blocks_wanted;
+    }
+    const int64_t want = static_cast<int64_t>(sms) * wanted / 148;
     int64_t s = (want + q / 2) / std::max<int64_t>(q, 1);
     // a slice should be long against the list it has to fill
     const int64_t list = k <= 256 ? 256 : (k <= 512 ? 512 : (k <= 1024 ? 1024 : 2048));
@@ -1270,7 +1320,6 @@ extern "C" int bitsknn_select_split(const float* d_dist, int64_t ld, const int32
     {
         return fail(BITSKNN_ERR_CUDA, "CUDA error. cannot resolve the device status word");
     }
-    fill_stream_config(p);
     auto cs = static_cast<cudaStream_t>(stream);
     if (const int rc = dispatch_select(p, q * s, cs); rc != BITSKNN_OK)
     {
@@ -1383,7 +1432,6 @@ extern "C" int bitsknn_select_split_static(const float* d_dist, int64_t ld, cons
     {
         return fail(BITSKNN_ERR_CUDA, "CUDA error. cannot resolve the device status word");
     }
-    fill_stream_config(p);
     auto cs = static_cast<cudaStream_t>(stream);
     if (const int rc = dispatch_select(p, q * splits, cs); rc != BITSKNN_OK)
     {

@@ -62,7 +62,11 @@ int bitsknn_device_status(bitsknn_stream_t stream);
  * waits and no such check (its only failure path is the CUCH macro, include/bits/cuch.hpp:9-19). */
 int bitsknn_selftest_bounded_wait(bitsknn_stream_t stream);
 
-/* Tuning knobs (launch shapes).  Unknown keys return BITSKNN_ERR_INVALID_ARGUMENT.
+/* Tuning knobs (launch shapes).  Unknown keys return BITSKNN_ERR_INVALID_ARGUMENT.  With a knob at
+ * its default the library takes the shape from its tuning table (csrc/tuning_table.inc, keyed by
+ * k, the number of row slices and, for the fused kernels, the dimension; regenerated on a GPU by
+ * bits-knn-jpdc2024_b200/tune.py), the role of the reference's scripts/optima.csv and its lookup
+ * config_algorithm (scripts/config.sh:98-214).
  *   "select.stage_bytes"  bytes per shared-memory stage of the row stream (multiple of 4096;
  *                         0 = automatic, the default); stages x stage_bytes beyond the 227 KiB a
  *                         block may use makes the next selection return INVALID_ARGUMENT
@@ -72,6 +76,8 @@ int bitsknn_selftest_bounded_wait(bitsknn_stream_t stream);
  *                         0 = automatic, the default: 50 for lists of up to 256 pairs, else 75)
  *   "select.unroll"       128-bit vectors per thread examined under one warp vote (0 = automatic,
  *                         2 or 4; other values are rejected)
+ *   "select.threads" / "select.ipt"  block size (256, 512, 1024) and list pairs per thread (1, 2, 4)
+ *                         of the selection kernel; both non-zero and threads x ipt >= k to apply
  *   "fused.variant"       FP32 fused kernel: 0 = 8 queries per block, 1 = tiled (needs the
  *                         workspace), 2 = automatic (default)
  *   "fused.parts"         blocks per query tile of the tiled fused kernels, i.e. ranges the database

@@ -136,6 +136,24 @@ def test_launch_shapes_do_not_change_results(bk, oracle, cuda, stage_bytes, stag
             bk.set_tuning(key, value)
 
 
+@pytest.mark.parametrize("threads,ipt", [(256, 1), (256, 2), (256, 4), (512, 1), (512, 2), (512, 4), (1024, 1), (1024, 2)])
+def test_block_shapes_do_not_change_results(bk, oracle, cuda, threads, ipt):
+    # every (block size, pairs per thread) the tuning table may pick, on random, tie-heavy and
+    # descending rows (the last keep every stage dense)
+    old = {key: bk.get_tuning(key) for key in ("select.threads", "select.ipt")}
+    try:
+        bk.set_tuning("select.threads", threads)
+        bk.set_tuning("select.ipt", ipt)
+        rng = np.random.default_rng(threads + ipt)
+        for k in {min(threads * ipt, 2048), max(1, threads * ipt // 2 - 3), 17}:
+            run_select(bk, oracle, rng.random((5, 200001), dtype=np.float32), k)
+            run_select(bk, oracle, rng.integers(0, 9, size=(3, 70000)).astype(np.float32), k)
+            run_select(bk, oracle, np.sort(rng.random((3, 150000), dtype=np.float32), axis=1)[:, ::-1].copy(), k)
+    finally:
+        for key, value in old.items():
+            bk.set_tuning(key, value)
+
+
 @pytest.mark.parametrize("variant", ["no_buffer", "shared_list"])
 def test_ablation_variants_give_the_same_result(bk, oracle, cuda, variant):
     # no_buffer: every value is sorted and merged (partial-bitonic-regs); shared_list: filtered
