@@ -38,6 +38,7 @@ tuning_entry g_tuning[] = {
     {"fused.variant", 2, 0, 2},
     {"fused.tc_mma_n", 0, 0, 256},
     {"fused.parts", 0, 0, 64},
+    {"fused.tc_cap", 0, 0, 32},
     {"profile.kernel_events", 0, 0, 1},
 };
 

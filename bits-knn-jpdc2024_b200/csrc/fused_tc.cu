@@ -52,7 +52,7 @@ constexpr int FT_THREADS = 352;
 constexpr int FT_PRODUCER_WARP = 8;
 constexpr int FT_MMA_WARP = 9;
 constexpr int FT_ACCS = tcpipe::ACCS; // four 128-column accumulators: each consumer group owns two
-constexpr int CAP = 32; // candidate slots per (group, query)
+constexpr int CAP = 32; // candidate slots per (group, query); 16 when the operand ring needs the room
 
 struct ftc_params
 {
@@ -66,6 +66,7 @@ struct ftc_params
     int stages;
     int parts;
     int64_t tiles;
+    int cap;          // candidate slots per (group, query): 32 or 16
     int k;            // list entry k - 1 is a list's radius (the reported k plus a margin)
     int32_t index_base;
     const float* qnorm;    // [q] squared norms of the queries
@@ -109,8 +110,9 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pipe.acc_empty + FT_ACCS);
     float* rad = reinterpret_cast<float*>(bars + 64);     // [2][128] radius distance per group and query
     float* hlf = rad + 2 * TILE_M;                        // [2][128] distance of list entry ceil(k / 2) - 1
-    float* buf_d = hlf + 2 * TILE_M;                      // [8 warps][CAP][32 lanes]
-    int* buf_x = reinterpret_cast<int*>(buf_d + 8 * CAP * 32);
+    const int cap = p.cap;
+    float* buf_d = hlf + 2 * TILE_M;                      // [8 warps][cap][32 lanes]
+    int* buf_x = reinterpret_cast<int*>(buf_d + 8 * cap * 32);
     const tcpipe::shape shape{p.nkb, p.nsteps, p.hs, p.stages};
 
     const int tid = threadIdx.x;
@@ -165,8 +167,8 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
         const int qrow = w4 * 32 + lane;              // query of this thread inside the tile
         const int64_t gq = qb * TILE_M + qrow;        // global query
         const bool live = gq < p.q;
-        float* my_buf_d = buf_d + warp * (CAP * 32);  // slot s of lane l at [s * 32 + (l + s) % 32]
-        int* my_buf_x = buf_x + warp * (CAP * 32);
+        float* my_buf_d = buf_d + warp * (cap * 32);  // slot s of lane l at [s * 32 + (l + s) % 32]
+        int* my_buf_x = buf_x + warp * (cap * 32);
         const int64_t list_id = static_cast<int64_t>(part) * 2 + group;
         const uint32_t lane_base = static_cast<uint32_t>(w4 * 32) << 16;
 
@@ -232,9 +234,23 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
             }
         };
 
+        // Folds every buffer that is more than half full and tightens the bound.
+        auto fold_full = [&]() {
+            const unsigned need = __ballot_sync(FULL_MASK, cnt > cap / 2);
+            if (need != 0)
+            {
+                __syncwarp();
+                fold_queries(need);
+                if (live)
+                {
+                    thr = fmaxf(thr, -0.5F * bound());
+                }
+            }
+        };
+
         // The candidates of one half chunk (16 columns) of this thread's row go to its buffer; full
-        // buffers are folded.  A buffer holds at most 16 pairs when a half starts, so its at most
-        // 16 pushes always fit.
+        // buffers are folded.  A buffer is at most half full when a run of cap / 2 columns starts
+        // (16 columns with 32 slots, 8 with 16), so the pushes of the run always fit.
         auto push_half = [&](const uint32_t(&v)[16], const float(&g)[4], int64_t col0) {
             const int ncols = p.n - col0 < 16 ? static_cast<int>(p.n - col0) : 16; // valid columns
             const float r_part = -2.0F * thr; // the bound as a distance
@@ -261,17 +277,12 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
                         }
                     }
                 }
-            }
-            const unsigned need = __ballot_sync(FULL_MASK, cnt > CAP / 2);
-            if (need != 0)
-            {
-                __syncwarp();
-                fold_queries(need);
-                if (live)
+                if (i == 1 && cap < 32)
                 {
-                    thr = fmaxf(thr, -0.5F * bound());
+                    fold_full();
                 }
             }
+            fold_full();
         };
 
         // this group's tiles are the local tiles lt = group, group + 2, ...; tile lt sits in
@@ -453,8 +464,24 @@ int run_ftc(const float* points, const float* queries, int64_t n, int64_t q, int
     // shared memory: query image + ring + barriers + radii + candidate buffers.  The MMA covers 256
     // points (two tiles, one per consumer group) when at least two of its 32 KiB stages fit beside
     // the query image, else 128 points.
-    const size_t fixed = 1024 + 64 * 8 + 4 * TILE_M * 4 + 2 * (8 * CAP * 32 * 4);
-    const int room128 = static_cast<int>((227 * 1024 - fixed) / STAGE_BYTES) - p.nkb;
+    // 32 candidate slots per (group, query); 16 for long image rows (five or more 128-byte K blocks:
+    // TF32 from dim 57, BF16 from dim 121), where the 32 KiB that frees -- two more 16 KiB stages --
+    // buy more than the extra folds cost (q = 2^14, n = 2^20: TF32 dim 64 k = 16 14.6 -> 11.7 ms,
+    // BF16 dim 128 k = 64 15.2 -> 13.0 ms; for shorter rows the ring is deep enough and the smaller
+    // buffers only add folds: BF16 dim 64 k = 128 11.4 -> 13.1 ms)
+    auto fixed_bytes = [](int cap) { return static_cast<size_t>(1024 + 64 * 8 + 4 * TILE_M * 4) + 2U * (8U * cap * 32U * 4U); };
+    auto room_for = [&](int cap) { return static_cast<int>((227 * 1024 - fixed_bytes(cap)) / STAGE_BYTES) - p.nkb; };
+    p.cap = CAP;
+    if (const int forced = tuning_value("fused.tc_cap", 0); forced == 16 || forced == 32)
+    {
+        p.cap = forced;
+    }
+    else if (p.nkb >= 5)
+    {
+        p.cap = 16;
+    }
+    const size_t fixed = fixed_bytes(p.cap);
+    const int room128 = room_for(p.cap);
     if (room128 < 2)
     {
         return fail(BITSKNN_ERR_UNSUPPORTED_DIM, "Unsupported dimension: %d (query image does not fit shared memory)", dim);

@@ -82,6 +82,8 @@ int bitsknn_selftest_bounded_wait(bitsknn_stream_t stream);
  *                         workspace), 2 = automatic (default)
  *   "fused.parts"         blocks per query tile of the tiled fused kernels, i.e. ranges the database
  *                         is cut into (0 = automatic, the default)
+ *   "fused.tc_cap"        candidate slots per query and consumer group of the fused TF32/BF16 kernels:
+ *                         0 = automatic (32, or 16 when the operand ring needs the shared memory), 16, 32
  *   "profile.kernel_events"  1 = record CUDA events around the main kernels (bitsknn_kernel_ms)
  *   "fused.tc_mma_n"      points per tensor-core MMA of the fused TF32/BF16 kernels: 0 = 256
  *                         whenever the operand ring fits shared memory (default), 128 = always 128
