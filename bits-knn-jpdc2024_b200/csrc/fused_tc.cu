@@ -67,6 +67,7 @@ struct ftc_params
     int parts;
     int64_t tiles;
     int cap;          // candidate slots per (group, query): 32 or 16
+    int fold_above;   // a buffer is folded when it holds more than this many candidates (cap - 16 or cap - 8)
     int k;            // list entry k - 1 is a list's radius (the reported k plus a margin)
     int32_t index_base;
     const float* qnorm;    // [q] squared norms of the queries
@@ -236,7 +237,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
 
         // Folds every buffer that is more than half full and tightens the bound.
         auto fold_full = [&]() {
-            const unsigned need = __ballot_sync(FULL_MASK, cnt > cap / 2);
+            const unsigned need = __ballot_sync(FULL_MASK, cnt > p.fold_above);
             if (need != 0)
             {
                 __syncwarp();
@@ -249,8 +250,8 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
         };
 
         // The candidates of one half chunk (16 columns) of this thread's row go to its buffer; full
-        // buffers are folded.  A buffer is at most half full when a run of cap / 2 columns starts
-        // (16 columns with 32 slots, 8 with 16), so the pushes of the run always fit.
+        // buffers are folded.  A buffer holds at most fold_above candidates when a run of
+        // cap - fold_above columns (16 or 8) starts, so the pushes of the run always fit.
         auto push_half = [&](const uint32_t(&v)[16], const float(&g)[4], int64_t col0) {
             const int ncols = p.n - col0 < 16 ? static_cast<int>(p.n - col0) : 16; // valid columns
             const float r_part = -2.0F * thr; // the bound as a distance
@@ -277,7 +278,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
                         }
                     }
                 }
-                if (i == 1 && cap < 32)
+                if (i == 1 && cap - p.fold_above < 16)
                 {
                     fold_full();
                 }
@@ -479,6 +480,14 @@ int run_ftc(const float* points, const float* queries, int64_t n, int64_t q, int
     else if (p.nkb >= 5)
     {
         p.cap = 16;
+    }
+    // folding fuller buffers means fewer folds (each sorts 32 slots whatever they hold) but a check of
+    // the fill every 8 columns instead of every 16: worth it for the longer lists only (k = 128:
+    // 11.5 -> 11.3 ms at dim 64, q = 2^14, n = 2^20; k = 16: 7.9 -> 8.0)
+    p.fold_above = p.cap == 32 ? (k > 32 ? 24 : 16) : 8;
+    if (const int forced = tuning_value("fused.tc_fold_above", 0); forced > 0 && (p.cap - forced == 8 || p.cap - forced == 16))
+    {
+        p.fold_above = forced;
     }
     const size_t fixed = fixed_bytes(p.cap);
     const int room128 = room_for(p.cap);
