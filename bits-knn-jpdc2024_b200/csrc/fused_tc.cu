@@ -94,7 +94,6 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     __shared__ uint2 a_tab_both[2][MAX_KB * 4]; // one descriptor table per MMA-issuing thread
-    __shared__ volatile int fills_seen[2];      // ring fills each issuing thread has seen complete
     tcpipe::state pipe;
     pipe.a_tiles = smem;
     pipe.b_ring = pipe.a_tiles + static_cast<size_t>(p.nkb) * STAGE_BYTES;
@@ -105,7 +104,6 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
     pipe.acc_full = pipe.empty_b + 16;
     pipe.acc_empty = pipe.acc_full + FT_ACCS;
     pipe.a_tab = &a_tab_both[0][0];
-    pipe.fills_seen = fills_seen;
     uint64_t* acc_full = pipe.acc_full;
     uint64_t* acc_empty = pipe.acc_empty;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pipe.acc_empty + FT_ACCS);
@@ -297,7 +295,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
             }
             const int a = static_cast<int>(lt & (FT_ACCS - 1));
             // (made warp-uniform: the lanes poll independently)
-            if (!__all_sync(FULL_MASK, ptx::mbar_wait_bounded_spin(&acc_full[a], static_cast<uint32_t>((lt >> 2) & 1))))
+            if (!__all_sync(FULL_MASK, ptx::mbar_wait_bounded_spin(&acc_full[tcpipe::acc_full_index<NMMA>(a)], static_cast<uint32_t>((lt >> 2) & 1))))
             {
                 ok = false;
                 break;

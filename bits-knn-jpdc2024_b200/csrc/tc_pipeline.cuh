@@ -5,12 +5,20 @@
 //   * four 128-column accumulators in tensor memory.  Tile lt (128 points) of the block's range
 //     goes to accumulator lt % 4, used for the (lt / 4)-th time; the readers of the accumulators
 //     arrive on acc_empty (128 arrivals) when they have taken a tile out.
-// One MMA covers NMMA = 128 or 256 points; a 256-point MMA fills two neighbouring accumulators.
-// The tensor pipe needs about 64 clocks for a 128 x 128 x 16 MMA and 128 for 128 x 256 x 16, but
-// the issuing thread is held for about that long per instruction and spends more on its barrier
-// traffic, so (a) 256-point MMAs halve the instruction count, (b) the descriptor words come from
-// a table built once, and (c) two threads issue in turn, so that one's waits and commits are
-// covered by the other's MMAs.
+// One MMA covers NMMA = 128 or 256 points; a 256-point MMA fills two neighbouring accumulators
+// and reports both on the barrier of the first (acc_full_index).
+//
+// The tensor pipe runs a 128 x 256 x 16 MMA in 128 clocks (128 x 128 x 16: 73), and it holds the
+// issuing thread for that long: whatever the thread does between two MMAs -- barrier waits,
+// commits (about 95 clocks each), descriptor arithmetic -- is added to the MMA time instead of
+// being covered by it (4096 back-to-back MMAs: 128 clocks each; with a commit after every fourth:
+// 258; the same from two threads that issue side by side: 129).  So two threads issue, and
+// nothing makes one wait for the other: unit u (one MMA's worth of points) belongs to thread
+// u % 2, which has its own accumulators ((2 u) % 4 and the next for 256-point MMAs, u % 4 for
+// 128-point ones) and its own "stage full" barriers.  The ring itself is shared and filled in
+// unit order; a stage has one full barrier per issuing thread (the producer signals the one of
+// the unit's thread), so that each thread sees every phase of the barriers it waits on -- a
+// parity wait on a barrier whose earlier phases the thread has not watched could pass early.
 //
 // Images (tc_host.cuh): plain (hs == 0: step st of the points meets step st of the queries) or
 // compact split ([hi (hs steps) | lo (hs steps) | optional norm step]: a hi step of the points
@@ -31,13 +39,14 @@ namespace bitsknn::tcpipe
 constexpr int ACCS = 4;           // 128-column accumulators in tensor memory
 constexpr int TMEM_COLS = 512;
 constexpr int K_STEP_BYTES = 32;  // one MMA consumes 32 bytes of K (8 TF32 / 16 BF16)
+constexpr int MAX_STAGES = 8;
 
 struct shape
 {
     int nkb;    // 128-byte K blocks per row of the images
     int nsteps; // MMA K steps (32 bytes) per row that hold data
     int hs;     // steps of the hi part of a compact split image (0: plain image)
-    int stages; // ring stages
+    int stages; // ring stages (at most MAX_STAGES)
 };
 
 // Barriers and buffers of one block, all in shared memory.
@@ -46,13 +55,20 @@ struct state
     unsigned char* a_tiles; // nkb x 16 KiB, 1024-byte aligned
     unsigned char* b_ring;  // stages x (NMMA / 128) x 16 KiB
     uint64_t* a_full;
-    uint64_t* full_b;       // [stages]
+    uint64_t* full_b;       // [2][MAX_STAGES]: per issuing thread
     uint64_t* empty_b;      // [stages]
     uint64_t* acc_full;     // [ACCS]
     uint64_t* acc_empty;    // [ACCS]
     uint2* a_tab;           // [2][MAX_KB * 4]: descriptor table of each issuing thread
-    volatile int* fills_seen; // [2]: ring fills each issuing thread has seen complete
 };
+
+// Barrier that reports tile accumulator `a` full: a 256-point MMA reports its two accumulators on
+// the barrier of the first.
+template <int NMMA>
+__device__ __forceinline__ int acc_full_index(int a)
+{
+    return NMMA == 2 * TILE_N ? (a & ~1) : a;
+}
 
 // Number of 64-bit barrier words `carve` lays out (a_full, 16 full, 16 empty, 2 x ACCS).
 constexpr int BARRIER_WORDS = 1 + 16 + 16 + 2 * ACCS;
@@ -63,6 +79,7 @@ __device__ __forceinline__ void init_barriers(const state& st, int stages)
     for (int s = 0; s < stages; ++s)
     {
         ptx::mbar_init(&st.full_b[s], 1);
+        ptx::mbar_init(&st.full_b[MAX_STAGES + s], 1);
         ptx::mbar_init(&st.empty_b[s], 1);
     }
     for (int a = 0; a < ACCS; ++a)
@@ -70,8 +87,6 @@ __device__ __forceinline__ void init_barriers(const state& st, int stages)
         ptx::mbar_init(&st.acc_full[a], 1);
         ptx::mbar_init(&st.acc_empty[a], 128);
     }
-    st.fills_seen[0] = 0;
-    st.fills_seen[1] = 0;
     ptx::mbar_init_fence();
 }
 
@@ -92,7 +107,8 @@ __device__ __forceinline__ bool producer(const state& st, const shape& sh, const
     }
     int s = 0;
     uint32_t ph = 0;
-    for (int64_t t = t_begin; t < t_end; t += NT)
+    int issuer = 0;
+    for (int64_t t = t_begin; t < t_end; t += NT, issuer ^= 1)
     {
         for (int kb = 0; kb < sh.nkb; ++kb)
         {
@@ -101,9 +117,10 @@ __device__ __forceinline__ bool producer(const state& st, const shape& sh, const
             {
                 return false;
             }
-            ptx::mbar_expect_tx(&st.full_b[s], STAGE_B);
-            tc::tma_load_2d(st.b_ring + static_cast<size_t>(s) * STAGE_B, map_p, kb * KB_ELEMS,
-                            static_cast<int>(t * TILE_N), &st.full_b[s]);
+            uint64_t* full = &st.full_b[issuer * MAX_STAGES + s];
+            ptx::mbar_expect_tx(full, STAGE_B);
+            tc::tma_load_2d(st.b_ring + static_cast<size_t>(s) * STAGE_B, map_p, kb * KB_ELEMS, static_cast<int>(t * TILE_N),
+                            full);
             if (++s == sh.stages)
             {
                 s = 0;
@@ -114,7 +131,7 @@ __device__ __forceinline__ bool producer(const state& st, const shape& sh, const
     return true;
 }
 
-// One of the two MMA-issuing threads (issuer = 0 or 1): takes every other MMA of the block's
+// One of the two MMA-issuing threads (issuer = 0 or 1): takes every other unit of the block's
 // range, waits for its accumulators and its stages, issues, commits.
 template <bool BF16, int NMMA>
 __device__ __forceinline__ bool mma_issuer(const state& st, const shape& sh, uint32_t tmem_base, int issuer,
@@ -127,7 +144,6 @@ __device__ __forceinline__ bool mma_issuer(const state& st, const shape& sh, uin
     // Low descriptor words of the query steps that meet step s of the point image (0: none).
     const uint64_t a_desc0 = tc::smem_desc_sw128(st.a_tiles);
     const uint32_t desc_hi = static_cast<uint32_t>(a_desc0 >> 32);
-    const uint32_t b_lo0 = static_cast<uint32_t>(tc::smem_desc_sw128(st.b_ring));
     auto a_step = [&](int s) {
         return static_cast<uint32_t>(a_desc0) + static_cast<uint32_t>(s >> 2) * (STAGE_BYTES >> 4) +
                static_cast<uint32_t>((s & 3) * (K_STEP_BYTES >> 4));
@@ -157,42 +173,15 @@ __device__ __forceinline__ bool mma_issuer(const state& st, const shape& sh, uin
     {
         return false;
     }
-    int s = 0;
-    uint32_t ph = 0;
-    int64_t lt = 0;
-    int turn = 0;
-    int fills_before = 0; // ring fills that belong to earlier MMAs
-    for (int64_t t = t_begin; t < t_end; t += NT, lt += NT, turn ^= 1, fills_before += sh.nkb)
+    const uint32_t b_lo0 = static_cast<uint32_t>(tc::smem_desc_sw128(st.b_ring));
+    uint64_t* full_b = st.full_b + issuer * MAX_STAGES;
+    // ring position of this thread's first unit; `seen` holds, per stage, the parity of the next
+    // phase of this thread's full barrier
+    int s = (issuer * sh.nkb) % sh.stages;
+    uint32_t seen = 0;
+    int64_t lt = static_cast<int64_t>(issuer) * NT;
+    for (int64_t t = t_begin + issuer * NT; t < t_end; t += 2 * NT, lt += 2 * NT)
     {
-        if (turn != issuer)
-        {
-            // the other thread's MMA: step over its stages of the ring
-            for (int kb = 0; kb < sh.nkb; ++kb)
-            {
-                if (++s == sh.stages)
-                {
-                    s = 0;
-                    ph ^= 1U;
-                }
-            }
-            continue;
-        }
-        // A parity wait on a ring stage is only meaningful once the stage's previous fill has
-        // completed.  This thread has not watched the fills of the other thread's MMAs, so it
-        // first lets the other thread report them (they were requested before this MMA's fills,
-        // so this hardly ever spins).
-        if (fills_before > 0)
-        {
-            uint32_t polls = 0;
-            const long long deadline = clock64() + ptx::WAIT_CLOCK_LIMIT;
-            while (st.fills_seen[issuer ^ 1] < fills_before)
-            {
-                if ((++polls & 1023U) == 0 && clock64() > deadline)
-                {
-                    return false;
-                }
-            }
-        }
         const int a = static_cast<int>(lt & (ACCS - 1));
         const uint32_t aph = static_cast<uint32_t>((lt >> 2) & 1);
         if (!ptx::mbar_wait_bounded_spin(&st.acc_empty[a], aph ^ 1U) ||
@@ -212,10 +201,11 @@ __device__ __forceinline__ bool mma_issuer(const state& st, const shape& sh, uin
             {
                 a_words[ks] = a_tab[kb * 4 + ks];
             }
-            if (!ptx::mbar_wait_bounded_spin(&st.full_b[s], ph))
+            if (!ptx::mbar_wait_bounded_spin(&full_b[s], (seen >> s) & 1U))
             {
                 return false;
             }
+            seen ^= 1U << s;
             tc::fence_after_sync();
             const uint32_t b_lo = b_lo0 + static_cast<uint32_t>(s) * (STAGE_B >> 4);
 #pragma unroll
@@ -230,18 +220,11 @@ __device__ __forceinline__ bool mma_issuer(const state& st, const shape& sh, uin
             if (++s == sh.stages)
             {
                 s = 0;
-                ph ^= 1U;
-            }
-            if (kb == sh.nkb - 1)
-            {
-                st.fills_seen[issuer] = fills_before + sh.nkb;
             }
         }
         tc::mma_commit(&st.acc_full[a]);
-        if constexpr (NT == 2)
-        {
-            tc::mma_commit(&st.acc_full[a + 1]);
-        }
+        // step over the other thread's unit
+        s = (s + sh.nkb) % sh.stages;
     }
     return true;
 }
