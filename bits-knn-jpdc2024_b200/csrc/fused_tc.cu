@@ -6,18 +6,26 @@
 // queries.hi, norm step with norm step), so an accumulator holds  s = x.y - |x|^2 / 2  and the
 // partial distance is d = -2 s (= |x|^2 - 2 x.y, the quantity the reference's fused kernel ranks by,
 // include/bits/topk/singlepass/fused_cache_kernel_structs.cuh:622-630).  The consumer compares
-// raw accumulators against  -bound / 2: one max-tree and one vote per 16 columns.
+// raw accumulators against  -bound / 2: one max-tree and one vote per 32 columns.
 //
-// Block = 352 threads on one SM, 128 queries (the TMEM lanes):
-//   warp 8   TMA producer (query image once, point image K blocks through a ring of stages)
-//   warps 9, 10  tcgen05.mma issue, the two taking MMAs in turn (tc_pipeline.cuh; warp 9 also
+// Block = 608 threads on one SM, 128 queries (the TMEM lanes):
+//   warp 16  TMA producer (query image once, point image K blocks through a ring of stages)
+//   warps 17, 18  tcgen05.mma issue, each with its own accumulators (tc_pipeline.cuh; warp 17 also
 //            allocates the tensor memory: 4 accumulators of 128 columns).  Whenever the ring fits,
 //            an MMA covers 256 points and fills two neighbouring accumulators, one per consumer
 //            group (NMMA = 256); long vectors fall back to 128 points per MMA.
-//   warps 0-7  consumers, two groups of four.  Group g takes every other 128-point tile (each
-//            group alternates between two accumulators, so the MMAs run ahead of it);
-//            thread t of a group is query 32 * (warp % 4) + t and reads its row with
-//            tcgen05.ld.  Each (group, query) has a private 32-slot candidate buffer in shared
+//   warps 0-7  scanners, two groups of four.  Group g takes every other 128-point tile (each
+//            group alternates between two accumulators, so the MMAs run ahead of it); thread t of
+//            a group is query 32 * (warp % 4) + t and reads its row with tcgen05.ld, 64 columns
+//            per step.  A scanner only compares: a tree of maxima and one vote per 32 columns
+//            against the query's threshold (-bound / 2).  It releases the accumulator when it has
+//            looked at it and mails the chunks (32 columns) in which some lane saw something to
+//            its helper, one message per tile (a ring of mailbox slots guarded by mbarriers).
+//   warps 8-15  helpers, one per scanner, on the same tensor-memory lanes (same queries).  A
+//            helper takes the flagged chunks out of tensor memory again, releases the accumulator
+//            as soon as the last of them is in its registers, pushes every accumulator that passes
+//            the current bound into the query's candidate buffer and folds full buffers into the
+//            query's list.  Each (group, query) has a private 32-slot candidate buffer in shared
 //            memory (no atomics: one writer) and a sorted list of KL = 32 * IPT pairs in the
 //            workspace (HBM/L2), touched only when the buffer is folded: the warp sorts the 32
 //            candidates with shuffles, takes the element-wise minimum against the list's last 32
@@ -25,6 +33,11 @@
 //            e % 32).  The acceptance bound of a query is the smallest of: its group's radius,
 //            the partner group's radius, and the larger of the two lists' entries
 //            ceil(k / 2) - 1 (the lists cover different points, so k pairs lie at or below it).
+//            The helper publishes the threshold in shared memory; a scanner reads it once per
+//            tile, and a stale value only costs a needless message.
+//   Why two kinds of warps: with the pushes and folds inside the scanning warps, every tile waited
+//   for the slowest of the eight warps (a push costs about a thousand clocks, a fold two to
+//   three thousand, and nine tiles in ten had at least one), and the MMAs waited with it.
 // After the scan the 2 * parts lists of every query hold its candidates by tensor-core distance;
 // rerank_lists() recomputes every candidate's distance as the exact FP32 chain of (y - x)^2 and
 // reports the k smallest pairs by that, so the rounding of the tensor-core inputs only decides
@@ -48,9 +61,13 @@ namespace bitsknn
 namespace
 {
 
-constexpr int FT_THREADS = 352;
-constexpr int FT_PRODUCER_WARP = 8;
-constexpr int FT_MMA_WARP = 9;
+constexpr int FT_THREADS = 608;
+constexpr int FT_HELPER_WARP = 8;    // warps 8-15: helper of scanner warp (warp - 8)
+constexpr int FT_PRODUCER_WARP = 16;
+constexpr int FT_MMA_WARP = 17;
+constexpr int FT_MAIL_SLOTS = 16;    // chunks a scanner may be ahead of its helper
+// mail from a scanner to its helper: (local tile << 4) | mask of the tile's four chunks to look at
+constexpr uint32_t FT_MAIL_SCAN_DONE = 0xFFFFFFFFU;
 constexpr int FT_ACCS = tcpipe::ACCS; // four 128-column accumulators: each consumer group owns two
 constexpr int CAP = 32; // candidate slots per (group, query); 16 when the operand ring needs the room
 
@@ -94,6 +111,10 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     __shared__ uint2 a_tab_both[2][MAX_KB * 4]; // one descriptor table per MMA-issuing thread
+    __shared__ uint64_t mail_full[8][FT_MAIL_SLOTS];  // scanner -> helper: slot holds a message
+    __shared__ uint64_t mail_empty[8][FT_MAIL_SLOTS]; // helper -> scanner: slot may be reused
+    __shared__ uint32_t mail_code[8][FT_MAIL_SLOTS];
+    __shared__ float thr_s[2 * TILE_M];               // acceptance threshold per (group, query), kept by the helpers
     tcpipe::state pipe;
     pipe.a_tiles = smem;
     pipe.b_ring = pipe.a_tiles + static_cast<size_t>(p.nkb) * STAGE_BYTES;
@@ -128,13 +149,21 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
 
     if (tid == 0)
     {
-        tcpipe::init_barriers(pipe, p.stages);
+        tcpipe::init_barriers(pipe, p.stages, 2 * TILE_M); // scanners and helpers both release an accumulator
+    }
+    if (tid < 8 * FT_MAIL_SLOTS)
+    {
+        ptx::mbar_init(&mail_full[0][0] + tid, 1);
+        ptx::mbar_init(&mail_empty[0][0] + tid, 1);
     }
     if (tid < 2 * TILE_M)
     {
         rad[tid] = INFINITY;
         hlf[tid] = INFINITY;
+        // a dead row (query beyond q) never accepts anything
+        thr_s[tid] = qb * TILE_M + (tid & (TILE_M - 1)) < p.q ? -INFINITY : INFINITY;
     }
+    ptx::mbar_init_fence();
     if (warp == FT_MMA_WARP)
     {
         tc::tmem_alloc(tmem_slot, tcpipe::TMEM_COLS);
@@ -159,17 +188,137 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
             ok = tcpipe::mma_issuer<BF16, NMMA>(pipe, shape, tmem_base, warp - FT_MMA_WARP, t_begin, t_end);
         }
     }
-    else
+    else if (warp < FT_HELPER_WARP)
     {
+        // ---- scanner: looks at every accumulator once and tells its helper which chunks (32
+        // columns) hold something at or above some lane's threshold.  It touches neither the
+        // candidate buffers nor the lists, so its loop is short and its pace even.
         const int group = warp >> 2;
         const int w4 = warp & 3;
+        const int qrow = w4 * 32 + lane; // query of this thread inside the tile
+        const uint32_t lane_base = static_cast<uint32_t>(w4 * 32) << 16;
+        uint64_t* my_full = mail_full[warp];
+        uint64_t* my_empty = mail_empty[warp];
+        uint32_t* my_code = mail_code[warp];
+        int slot = 0;
+        uint32_t mph = 0;
+        // (lane 0 alone posts; a fresh barrier passes a wait on the opposite parity at once)
+        auto post = [&](uint32_t code) {
+            bool sent = true;
+            if (lane == 0)
+            {
+                sent = ptx::mbar_wait_bounded_spin(&my_empty[slot], mph ^ 1U);
+                my_code[slot] = code;
+                tc::mbar_arrive(&my_full[slot]);
+            }
+            if (++slot == FT_MAIL_SLOTS)
+            {
+                slot = 0;
+                mph ^= 1U;
+            }
+            return sent;
+        };
+
+        auto group_maxima = [](const uint32_t(&v)[16], float(&g)[4]) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+            {
+                g[i] = fmaxf(max3(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]), __uint_as_float(v[4 * i + 2])),
+                             __uint_as_float(v[4 * i + 3]));
+            }
+        };
+
+        // this group's tiles are the local tiles lt = group, group + 2, ...; tile lt sits in
+        // accumulator lt % 4, so the group alternates between its two accumulators
+        int64_t lt = group;
+        for (int64_t t = t_begin + group; t < t_end && ok; t += 2, lt += 2)
+        {
+            // the helper tightens the threshold as the lists fill; a stale one only sends it a
+            // chunk it would not have needed
+            const float thr = *reinterpret_cast<volatile float*>(&thr_s[group * TILE_M + qrow]);
+            const int a = static_cast<int>(lt & (FT_ACCS - 1));
+            // (made warp-uniform: the lanes poll independently)
+            if (!__all_sync(FULL_MASK, ptx::mbar_wait_bounded_spin(&acc_full[tcpipe::acc_full_index<NMMA>(a)],
+                                                                   static_cast<uint32_t>((lt >> 2) & 1))))
+            {
+                ok = false;
+                break;
+            }
+            tc::fence_after_sync();
+            const uint32_t acc_addr = tmem_base + lane_base + static_cast<uint32_t>(a * TILE_N);
+            // 64 columns per step (two loads in flight, two independent trees of maxima, one vote per
+            // 32 columns); the next step's loads are issued as soon as the maxima are taken
+            uint32_t lo0[16];
+            uint32_t hi0[16];
+            uint32_t lo1[16];
+            uint32_t hi1[16];
+            uint32_t flagged = 0; // chunks of this tile that hold something for some lane
+            tc::tmem_ld_32x32_halves(acc_addr, lo0, hi0);
+            tc::tmem_ld_32x32_halves(acc_addr + 32U, lo1, hi1);
+#pragma unroll 1
+            for (int c = 0; c < TILE_N / 32; c += 2)
+            {
+                float g0_lo[4];
+                float g0_hi[4];
+                float g1_lo[4];
+                float g1_hi[4];
+                tc::tmem_ld_wait();
+                group_maxima(lo0, g0_lo);
+                group_maxima(hi0, g0_hi);
+                group_maxima(lo1, g1_lo);
+                group_maxima(hi1, g1_hi);
+                const float mx0 = max3(max3(g0_lo[0], g0_lo[1], g0_lo[2]), max3(g0_hi[0], g0_hi[1], g0_hi[2]),
+                                       fmaxf(g0_lo[3], g0_hi[3]));
+                const float mx1 = max3(max3(g1_lo[0], g1_lo[1], g1_lo[2]), max3(g1_hi[0], g1_hi[1], g1_hi[2]),
+                                       fmaxf(g1_lo[3], g1_hi[3]));
+                if (c + 2 < TILE_N / 32)
+                {
+                    tc::tmem_ld_32x32_halves(acc_addr + static_cast<uint32_t>(c * 32 + 64), lo0, hi0);
+                    tc::tmem_ld_32x32_halves(acc_addr + static_cast<uint32_t>(c * 32 + 96), lo1, hi1);
+                }
+                const bool any0 = __any_sync(FULL_MASK, mx0 >= thr);
+                const bool any1 = __any_sync(FULL_MASK, mx1 >= thr);
+                flagged |= (any0 ? 1U : 0U) << c;
+                flagged |= (any1 ? 2U : 0U) << c;
+            }
+            // This thread's reads of the accumulator are over.  The helper releases it too, once it
+            // has the last flagged chunk in registers; with nothing flagged it is not told about the
+            // tile at all and the scanner arrives in its place.
+            tc::fence_before_sync();
+            if (flagged == 0)
+            {
+                tc::mbar_arrive(&acc_empty[a], 2U);
+            }
+            else
+            {
+                tc::mbar_arrive(&acc_empty[a]);
+                const bool sent = post((static_cast<uint32_t>(lt) << 4) | flagged);
+                if (!__shfl_sync(FULL_MASK, sent ? 1 : 0, 0))
+                {
+                    ok = false;
+                }
+            }
+        }
+        post(FT_MAIL_SCAN_DONE);
+    }
+    else if (warp < FT_PRODUCER_WARP)
+    {
+        // ---- helper of scanner warp (warp - 8): same queries (tensor-memory lanes), owns their
+        // candidate buffers and lists.  Takes the chunks its scanner points at out of tensor memory
+        // again, pushes what passes the current bound, folds full buffers, publishes the threshold.
+        const int hw = warp - FT_HELPER_WARP;
+        const int group = hw >> 2;
+        const int w4 = hw & 3;
         const int qrow = w4 * 32 + lane;              // query of this thread inside the tile
         const int64_t gq = qb * TILE_M + qrow;        // global query
         const bool live = gq < p.q;
-        float* my_buf_d = buf_d + warp * (cap * 32);  // slot s of lane l at [s * 32 + (l + s) % 32]
-        int* my_buf_x = buf_x + warp * (cap * 32);
+        float* my_buf_d = buf_d + hw * (cap * 32);    // slot s of lane l at [s * 32 + (l + s) % 32]
+        int* my_buf_x = buf_x + hw * (cap * 32);
         const int64_t list_id = static_cast<int64_t>(part) * 2 + group;
         const uint32_t lane_base = static_cast<uint32_t>(w4 * 32) << 16;
+        uint64_t* my_full = mail_full[hw];
+        uint64_t* my_empty = mail_empty[hw];
+        const uint32_t* my_code = mail_code[hw];
 
         // radius pair of this (group, query); a dead row (query beyond q) never accepts anything
         float r_d = live ? INFINITY : -INFINITY;
@@ -223,118 +372,125 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
             }
         };
 
-        // Maxima of the four groups of four columns of a half chunk.
-        auto group_maxima = [](const uint32_t(&v)[16], float(&g)[4]) {
+        // Column j (0..31) of the chunk held in lo / hi: a tree of bitwise selects on the bits of j
+        // (registers cannot be indexed, and a copy of the chunk in local memory would cost more).
+        auto column = [](const uint32_t(&lo)[16], const uint32_t(&hi)[16], int j) {
+            auto pick = [](uint32_t a, uint32_t b, uint32_t mk) { return (a & mk) | (b & ~mk); };
+            const uint32_t m4 = 0U - ((static_cast<uint32_t>(j) >> 4) & 1U);
+            const uint32_t m3 = 0U - ((static_cast<uint32_t>(j) >> 3) & 1U);
+            const uint32_t m2 = 0U - ((static_cast<uint32_t>(j) >> 2) & 1U);
+            const uint32_t m1 = 0U - ((static_cast<uint32_t>(j) >> 1) & 1U);
+            const uint32_t m0 = 0U - (static_cast<uint32_t>(j) & 1U);
+            uint32_t v8[8];
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
+            for (int i = 0; i < 8; ++i)
             {
-                g[i] = fmaxf(max3(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]), __uint_as_float(v[4 * i + 2])),
-                             __uint_as_float(v[4 * i + 3]));
+                v8[i] = pick(pick(hi[i + 8], lo[i + 8], m4), pick(hi[i], lo[i], m4), m3);
             }
+            uint32_t v2[2];
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+            {
+                v2[i] = pick(pick(v8[i + 6], v8[i + 2], m2), pick(v8[i + 4], v8[i], m2), m1);
+            }
+            return __uint_as_float(pick(v2[1], v2[0], m0));
         };
 
-        // Folds every buffer that is more than half full and tightens the bound.
-        auto fold_full = [&]() {
-            const unsigned need = __ballot_sync(FULL_MASK, cnt > p.fold_above);
-            if (need != 0)
+        // One chunk: 32 columns of this thread's row, starting at point col0.  Every lane marks its
+        // columns at or above the threshold in a bit mask and pushes them one by one (the lanes
+        // diverge).  A lane whose buffer is full waits for the fold that follows and goes on under
+        // the tightened bound.
+        auto take_chunk = [&](const uint32_t(&lo)[16], const uint32_t(&hi)[16], int64_t col0) {
+            unsigned m = 0;
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
             {
-                __syncwarp();
-                fold_queries(need);
-                if (live)
-                {
-                    thr = fmaxf(thr, -0.5F * bound());
-                }
+                m |= (__uint_as_float(lo[j]) >= thr ? 1U : 0U) << j;
+                m |= (__uint_as_float(hi[j]) >= thr ? 1U : 0U) << (16 + j);
             }
-        };
-
-        // The candidates of one half chunk (16 columns) of this thread's row go to its buffer; full
-        // buffers are folded.  A buffer holds at most fold_above candidates when a run of
-        // cap - fold_above columns (16 or 8) starts, so the pushes of the run always fit.
-        auto push_half = [&](const uint32_t(&v)[16], const float(&g)[4], int64_t col0) {
-            const int ncols = p.n - col0 < 16 ? static_cast<int>(p.n - col0) : 16; // valid columns
-            const float r_part = -2.0F * thr; // the bound as a distance
-            // warp votes per group of four, then per column
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
+            if (p.n - col0 < 32)
             {
-                if (__any_sync(FULL_MASK, g[i] >= thr))
+                // ragged end: the columns from n on hold no point
+                m &= p.n <= col0 ? 0U : (1U << static_cast<int>(p.n - col0)) - 1U;
+            }
+            while (__any_sync(FULL_MASK, m != 0))
+            {
+                while (m != 0 && cnt < cap)
                 {
-#pragma unroll
-                    for (int j = 4 * i; j < 4 * i + 4; ++j)
+                    const int j = __ffs(static_cast<int>(m)) - 1;
+                    m &= m - 1;
+                    const float s = column(lo, hi, j);
+                    const float d = -2.0F * s;
+                    const int idx = p.index_base + static_cast<int>(col0 + j);
+                    if (s >= thr && pair_lt(d, idx, r_d, r_x))
                     {
-                        const float s = __uint_as_float(v[j]);
-                        if (s >= thr && j < ncols)
-                        {
-                            const float d = -2.0F * s;
-                            const int idx = p.index_base + static_cast<int>(col0 + j);
-                            if (d <= r_part && pair_lt(d, idx, r_d, r_x))
-                            {
-                                my_buf_d[cnt * 32 + ((lane + cnt) & 31)] = d;
-                                my_buf_x[cnt * 32 + ((lane + cnt) & 31)] = idx;
-                                ++cnt;
-                            }
-                        }
+                        my_buf_d[cnt * 32 + ((lane + cnt) & 31)] = d;
+                        my_buf_x[cnt * 32 + ((lane + cnt) & 31)] = idx;
+                        ++cnt;
                     }
                 }
-                if (i == 1 && cap - p.fold_above < 16)
+                const unsigned need = __ballot_sync(FULL_MASK, cnt > p.fold_above);
+                if (need != 0)
                 {
-                    fold_full();
+                    __syncwarp();
+                    fold_queries(need);
+                    if (live)
+                    {
+                        thr = fmaxf(thr, -0.5F * bound());
+                    }
                 }
             }
-            fold_full();
         };
 
-        // this group's tiles are the local tiles lt = group, group + 2, ...; tile lt sits in
-        // accumulator lt % 4, so the group alternates between its two accumulators
-        int64_t lt = group;
-        for (int64_t t = t_begin + group; t < t_end && ok; t += 2, lt += 2)
+        int slot = 0;
+        uint32_t mph = 0;
+        while (ok)
         {
-            if (live)
-            {
-                thr = -0.5F * bound();
-            }
-            const int a = static_cast<int>(lt & (FT_ACCS - 1));
-            // (made warp-uniform: the lanes poll independently)
-            if (!__all_sync(FULL_MASK, ptx::mbar_wait_bounded_spin(&acc_full[tcpipe::acc_full_index<NMMA>(a)], static_cast<uint32_t>((lt >> 2) & 1))))
+            if (!__all_sync(FULL_MASK, ptx::mbar_wait_bounded_spin(&my_full[slot], mph)))
             {
                 ok = false;
                 break;
             }
-            tc::fence_after_sync();
-            const uint32_t acc_addr = tmem_base + lane_base + static_cast<uint32_t>(a * TILE_N);
-            // 32 columns per step: both halves' max-trees run side by side and one vote rejects the
-            // step; the registers are free for the next load as soon as the step is decided (the
-            // other warp of this scheduler covers the load's latency)
-            uint32_t lo[16];
-            uint32_t hi[16];
-            tc::tmem_ld_32x32_halves(acc_addr, lo, hi);
-#pragma unroll 1
-            for (int c = 0; c < TILE_N / 32; ++c)
+            const uint32_t code = my_code[slot];
+            __syncwarp();
+            if (lane == 0)
             {
-                float g_lo[4];
-                float g_hi[4];
+                tc::mbar_arrive(&my_empty[slot]);
+            }
+            if (++slot == FT_MAIL_SLOTS)
+            {
+                slot = 0;
+                mph ^= 1U;
+            }
+            if (code == FT_MAIL_SCAN_DONE)
+            {
+                break;
+            }
+            const int64_t lt = code >> 4;
+            const int a = static_cast<int>(lt & (FT_ACCS - 1));
+            uint32_t todo = code & 15U;
+            tc::fence_after_sync();
+            while (todo != 0)
+            {
+                const int c = __ffs(static_cast<int>(todo)) - 1;
+                todo &= todo - 1;
+                uint32_t lo[16];
+                uint32_t hi[16];
+                tc::tmem_ld_32x32_halves(tmem_base + lane_base + static_cast<uint32_t>(a * TILE_N + c * 32), lo, hi);
+                if (live)
+                {
+                    thr = fmaxf(thr, -0.5F * bound()); // the partner group may have tightened it
+                }
                 tc::tmem_ld_wait();
-                group_maxima(lo, g_lo);
-                group_maxima(hi, g_hi);
-                const float mx = max3(max3(g_lo[0], g_lo[1], g_lo[2]), max3(g_hi[0], g_hi[1], g_hi[2]),
-                                      fmaxf(g_lo[3], g_hi[3]));
-                if (__any_sync(FULL_MASK, mx >= thr))
+                if (todo == 0)
                 {
-                    const int64_t col0 = t * TILE_N + c * 32;
-                    push_half(lo, g_lo, col0);
-                    push_half(hi, g_hi, col0 + 16);
-                }
-                if (c + 1 < TILE_N / 32)
-                {
-                    tc::tmem_ld_32x32_halves(acc_addr + static_cast<uint32_t>(c * 32 + 32), lo, hi);
-                }
-                else
-                {
-                    // every accumulator of this thread has been looked at: the buffer may be reused
+                    // the last chunk wanted from this accumulator is in registers
                     tc::fence_before_sync();
                     tc::mbar_arrive(&acc_empty[a]);
                 }
+                take_chunk(lo, hi, (t_begin + lt) * TILE_N + c * 32);
             }
+            thr_s[group * TILE_M + qrow] = thr;
         }
         // flush: every live (group, query) leaves a complete list behind, padding included
         __syncwarp();
@@ -383,12 +539,31 @@ ftc_layout ftc_layout_of(int64_t n, int64_t q, int dim, int k, bool bf16)
     l.k_scan = std::min(l.kl, k + std::max(4, k / 4));
     const int64_t nqb = (q + TILE_M - 1) / TILE_M;
     const int64_t tiles = (n + TILE_N - 1) / TILE_N;
-    // every extra part is one more pair of lists per query that has to find its own radius, so
-    // the database is only split when the query tiles alone cannot occupy the SMs (parts of at
-    // least 64 tiles)
+    // The database is split into parts when the query tiles alone cannot occupy the SMs.  A block's
+    // time is its share of the scan plus the work of bringing its lists' radii down, which hardly
+    // shrinks with the part (measured at q = 2^16, n = 2^20 with one and two parts: that work is
+    // about 0.3 of a full scan for k <= 32 and 0.45 above), and the blocks run in waves of one per
+    // SM: the number of parts (of at least 64 tiles) with the smallest waves x block time wins
+    // (q = 8192: two parts, one wave of 128 blocks, 5.3 ms at dim 32, k = 64; three parts: 7.8 ms).
     const int sms = device_sm_count();
-    const int64_t want = 4 * nqb >= 3 * sms ? 1 : (sms + nqb - 1) / nqb;
-    l.parts = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(want, std::max<int64_t>(1, tiles / 64))));
+    const double fixed_work = k > 32 ? 0.45 : 0.3;
+    const int64_t max_parts = std::max<int64_t>(1, std::min<int64_t>(tiles / 64, 4 * sms));
+    double best = 0.0;
+    l.parts = 1;
+    for (int64_t parts = 1; parts <= max_parts; ++parts)
+    {
+        const double waves = static_cast<double>((nqb * parts + sms - 1) / sms);
+        const double cost = waves * (1.0 / static_cast<double>(parts) + fixed_work);
+        if (parts == 1 || cost < best * 0.98)
+        {
+            best = cost;
+            l.parts = static_cast<int>(parts);
+        }
+        if (nqb * parts >= 4 * static_cast<int64_t>(sms))
+        {
+            break;
+        }
+    }
     if (const int forced = tuning_value("fused.parts", 0); forced > 0)
     {
         l.parts = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(forced, std::max<int64_t>(1, tiles / 64))));
@@ -469,7 +644,8 @@ int run_ftc(const float* points, const float* queries, int64_t n, int64_t q, int
     // BF16 dim 128 k = 64 15.2 -> 13.0 ms; for shorter rows the ring is deep enough and the smaller
     // buffers only add folds: BF16 dim 64 k = 128 11.4 -> 13.1 ms)
     auto fixed_bytes = [](int cap) { return static_cast<size_t>(1024 + 64 * 8 + 4 * TILE_M * 4) + 2U * (8U * cap * 32U * 4U); };
-    auto room_for = [&](int cap) { return static_cast<int>((227 * 1024 - fixed_bytes(cap)) / STAGE_BYTES) - p.nkb; };
+    // (the kernel's static shared memory -- descriptor tables, mailboxes, thresholds -- is 4.5 KiB)
+    auto room_for = [&](int cap) { return static_cast<int>((227 * 1024 - 4608 - fixed_bytes(cap)) / STAGE_BYTES) - p.nkb; };
     p.cap = CAP;
     if (const int forced = tuning_value("fused.tc_cap", 0); forced == 16 || forced == 32)
     {

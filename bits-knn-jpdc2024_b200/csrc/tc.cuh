@@ -29,6 +29,12 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar)
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(ptx::smem_addr(bar)) : "memory");
 }
 
+// The same, counted as `count` arrivals.
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar, uint32_t count)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0], %1;" ::"r"(ptx::smem_addr(bar)), "r"(count) : "memory");
+}
+
 // ---- tensor memory ------------------------------------------------------------------------
 // Allocates `cols` (power of two >= 32) TMEM columns; the base address lands in *slot (shared
 // memory).  Executed by one whole warp; the same warp frees the columns before the kernel ends.

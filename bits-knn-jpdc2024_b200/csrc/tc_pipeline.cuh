@@ -4,7 +4,7 @@
 //   * a ring of stages, each one K block of NMMA points (128-byte rows, 128-byte swizzle),
 //   * four 128-column accumulators in tensor memory.  Tile lt (128 points) of the block's range
 //     goes to accumulator lt % 4, used for the (lt / 4)-th time; the readers of the accumulators
-//     arrive on acc_empty (128 arrivals) when they have taken a tile out.
+//     arrive on acc_empty (128 arrivals, or as many as the kernel says) when they have taken a tile out.
 // One MMA covers NMMA = 128 or 256 points; a 256-point MMA fills two neighbouring accumulators
 // and reports both on the barrier of the first (acc_full_index).
 //
@@ -73,7 +73,7 @@ __device__ __forceinline__ int acc_full_index(int a)
 // Number of 64-bit barrier words `carve` lays out (a_full, 16 full, 16 empty, 2 x ACCS).
 constexpr int BARRIER_WORDS = 1 + 16 + 16 + 2 * ACCS;
 
-__device__ __forceinline__ void init_barriers(const state& st, int stages)
+__device__ __forceinline__ void init_barriers(const state& st, int stages, int acc_readers = 128)
 {
     ptx::mbar_init(st.a_full, 1);
     for (int s = 0; s < stages; ++s)
@@ -85,7 +85,7 @@ __device__ __forceinline__ void init_barriers(const state& st, int stages)
     for (int a = 0; a < ACCS; ++a)
     {
         ptx::mbar_init(&st.acc_full[a], 1);
-        ptx::mbar_init(&st.acc_empty[a], 128);
+        ptx::mbar_init(&st.acc_empty[a], acc_readers);
     }
     ptx::mbar_init_fence();
 }
