@@ -39,7 +39,7 @@ tuning_entry g_tuning[] = {
     {"fused.tc_mma_n", 0, 0, 256},
     {"fused.parts", 0, 0, 64},
     {"fused.tc_cap", 0, 0, 32},
-    {"fused.tc_fold_above", 0, 0, 24},
+    {"fused.tc_fold_above", 0, 0, 31},
     {"profile.kernel_events", 0, 0, 1},
 };
 

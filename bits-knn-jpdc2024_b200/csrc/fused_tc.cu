@@ -655,11 +655,11 @@ int run_ftc(const float* points, const float* queries, int64_t n, int64_t q, int
     {
         p.cap = 16;
     }
-    // folding fuller buffers means fewer folds (each sorts 32 slots whatever they hold) but a check of
-    // the fill every 8 columns instead of every 16: worth it for the longer lists only (k = 128:
-    // 11.5 -> 11.3 ms at dim 64, q = 2^14, n = 2^20; k = 16: 7.9 -> 8.0)
-    p.fold_above = p.cap == 32 ? (k > 32 ? 24 : 16) : 8;
-    if (const int forced = tuning_value("fused.tc_fold_above", 0); forced > 0 && (p.cap - forced == 8 || p.cap - forced == 16))
+    // folding fuller buffers means fewer folds (each sorts 32 slots whatever they hold) but a later
+    // radius: worth it for the longer lists only (q = 2^14, n = 2^20, dim 64: k = 128 folds above
+    // 16 / 24 / 28: 11.96 / 11.52 / 11.40 ms; k = 16: 7.66 / 7.71 / 7.74)
+    p.fold_above = p.cap == 32 ? (k > 64 ? 28 : (k > 32 ? 24 : 16)) : 8;
+    if (const int forced = tuning_value("fused.tc_fold_above", 0); forced > 0 && forced < p.cap)
     {
         p.fold_above = forced;
     }

@@ -85,7 +85,7 @@ int bitsknn_selftest_bounded_wait(bitsknn_stream_t stream);
  *   "fused.tc_cap"        candidate slots per query and consumer group of the fused TF32/BF16 kernels:
  *                         0 = automatic (32, or 16 when the operand ring needs the shared memory), 16, 32
  *   "fused.tc_fold_above" fold a candidate buffer of those kernels above this many candidates
- *                         (slots - 8 or slots - 16; 0 = automatic)
+ *                         (1 .. slots - 1; 0 = automatic)
  *   "profile.kernel_events"  1 = record CUDA events around the main kernels (bitsknn_kernel_ms)
  *   "fused.tc_mma_n"      points per tensor-core MMA of the fused TF32/BF16 kernels: 0 = 256
  *                         whenever the operand ring fits shared memory (default), 128 = always 128
