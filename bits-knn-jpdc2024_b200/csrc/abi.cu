@@ -31,7 +31,7 @@ std::mutex g_tuning_mutex;
 tuning_entry g_tuning[] = {
     {"select.stage_bytes", 0, 0, 65536},
     {"select.stages", 0, 0, 8},
-    {"select.merge_at", 0, 0, 100},
+    {"select.merge_at", 0, 0, 190},
     {"select.unroll", 0, 0, 4},
     {"select.threads", 0, 0, 1024},
     {"select.ipt", 0, 0, 4},

@@ -63,7 +63,7 @@ struct select_params
     int no_filter;    // 1: never tighten the radius: every value is buffered, sorted and merged (ablation)
     int stage_floats; // floats per stage, a multiple of 4 * THREADS
     int stages;
-    int merge_at;     // fold the buffer as soon as it holds this many candidates (<= L)
+    int merge_at;     // fold the buffer as soon as it holds this many candidates (<= L; < 2 L for folds by selection)
     int* status;
 };
 
@@ -75,6 +75,15 @@ struct select_ctrl
     float r_d;         // radius pair, written by the owner of list element k-1 (fold) or the pivot (plan)
     int r_x;
     int dense;         // plan: the stage was dense
+    // fold by selection (long lists): range of keys that holds the k-th, counters
+    unsigned long long key_lo;
+    unsigned long long key_hi;
+    int sel_bin;       // bucket that holds the wanted rank
+    int sel_before;    // keys in the buckets before it
+    int sel_count;     // keys in it
+    int sel_real;      // real (non-padding) keys
+    int sel_kept;      // survivors written so far
+    int sel_ties;      // keys equal to the pivot taken so far
 };
 
 // What a block knows about its row besides the list: passed by value to the out-of-line parts.
@@ -269,6 +278,277 @@ __device__ __forceinline__ void scan_stage(const row_ctx& s, int cap, const floa
 
 // ---- the parts that run a few times per row ---------------------------------------------------
 
+// The pair order as one unsigned 64-bit key: distance (sign-magnitude floats made monotone; the
+// two zeros coincide, as they do under <) above the label (signed order).
+__device__ __forceinline__ unsigned long long pair_key(float d, int x)
+{
+    uint32_t u = __float_as_uint(d + 0.0F);
+    u = (u & 0x80000000U) != 0 ? ~u : (u | 0x80000000U);
+    return (static_cast<unsigned long long>(u) << 32) | (static_cast<uint32_t>(x) ^ 0x80000000U);
+}
+
+constexpr unsigned long long PAD_KEY = 0xFF800000FFFFFFFFULL; // key of the padding pair (+inf, PAD_IDX)
+
+// Fold for long lists (L >= 1024): the list is kept as an UNSORTED set of the k smallest pairs and a
+// fold is a selection, not a sort -- the k-th smallest key of list + buffer is found by bucketing
+// (256 buckets over the range that still holds it, narrowed level by level, then a ranking of the
+// last 32 or fewer keys inside one warp), everything below it is compacted into the list and the
+// pivot is the new radius.  A fold of a 2048-pair list is about a tenth of the instructions of the
+// sorting networks (77 compare-exchange steps, 20 of them through shared memory); the list is
+// sorted once, when the row ends.  Takes the whole buffer; returns 0 (nothing stays buffered).
+template <int THREADS, int IPT>
+__device__ __forceinline__ int fold_select(float (&ld)[IPT], int (&lx)[IPT], row_ctx s, int valid)
+{
+    constexpr int E = 3 * IPT; // pairs a thread holds: its share of the list and of the 2 L buffer slots
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    select_ctrl* ctrl = s.ctrl;
+    float pd[E];
+    int px[E];
+#pragma unroll
+    for (int r = 0; r < IPT; ++r)
+    {
+        pd[r] = ld[r];
+        px[r] = lx[r];
+    }
+#pragma unroll
+    for (int r = 0; r < 2 * IPT; ++r)
+    {
+        const int e = r * THREADS + tid;
+        const bool in = e < valid;
+        pd[IPT + r] = in ? s.buf_d[e] : INFINITY;
+        px[IPT + r] = in ? s.buf_x[e] : PAD_IDX;
+    }
+    // range and number of the real keys
+    unsigned long long kmin = PAD_KEY;
+    unsigned long long kmax = 0;
+    int real = 0;
+#pragma unroll
+    for (int i = 0; i < E; ++i)
+    {
+        const unsigned long long key = pair_key(pd[i], px[i]);
+        if (key != PAD_KEY)
+        {
+            kmin = key < kmin ? key : kmin;
+            kmax = key > kmax ? key : kmax;
+            ++real;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1)
+    {
+        const unsigned long long a = __shfl_xor_sync(FULL_MASK, kmin, o);
+        const unsigned long long b = __shfl_xor_sync(FULL_MASK, kmax, o);
+        kmin = a < kmin ? a : kmin;
+        kmax = b > kmax ? b : kmax;
+        real += __shfl_xor_sync(FULL_MASK, real, o);
+    }
+    if (tid == 0)
+    {
+        ctrl->key_lo = PAD_KEY;
+        ctrl->key_hi = 0;
+        ctrl->sel_real = 0;
+        ctrl->sel_kept = 0;
+        ctrl->sel_ties = 0;
+    }
+    __syncthreads(); // every thread holds its buffer entries: the buffer is scratch from here on
+    uint32_t* hist = reinterpret_cast<uint32_t*>(s.buf_d);                           // 256 buckets
+    unsigned long long* last = reinterpret_cast<unsigned long long*>(s.buf_d + 256); // the last <= 32 keys
+    if (lane == 0 && real > 0)
+    {
+        atomicMin(&ctrl->key_lo, kmin);
+        atomicMax(&ctrl->key_hi, kmax);
+        atomicAdd(&ctrl->sel_real, real);
+    }
+    __syncthreads();
+    const int total_real = ctrl->sel_real;
+    const int k = s.k;
+    unsigned long long pivot = PAD_KEY; // keys below the pivot stay, and `ties` keys equal to it
+    int ties = 0;
+    if (total_real >= k)
+    {
+        unsigned long long lo = ctrl->key_lo;
+        unsigned long long hi = ctrl->key_hi;
+        int want = k; // rank (1-based) of the pivot among the keys in [lo, hi]
+        while (true)
+        {
+            const unsigned long long range = hi - lo;
+            const int shift = range < 256ULL ? 0 : (64 - __clzll(static_cast<long long>(range))) - 8;
+            if (tid < 256)
+            {
+                hist[tid] = 0;
+            }
+            __syncthreads();
+#pragma unroll
+            for (int i = 0; i < E; ++i)
+            {
+                const unsigned long long key = pair_key(pd[i], px[i]);
+                if (key >= lo && key <= hi)
+                {
+                    atomicAdd(&hist[static_cast<uint32_t>((key - lo) >> shift)], 1U);
+                }
+            }
+            __syncthreads();
+            if (tid < 32)
+            {
+                // lane l sums buckets 8 l .. 8 l + 7; the bucket in which the running count reaches `want`
+                uint32_t h[8];
+                uint32_t sum = 0;
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                {
+                    h[j] = hist[lane * 8 + j];
+                    sum += h[j];
+                }
+                uint32_t incl = sum;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1)
+                {
+                    const uint32_t t = __shfl_up_sync(FULL_MASK, incl, o);
+                    incl += lane >= o ? t : 0U;
+                }
+                uint32_t before = incl - sum;
+                if (before < static_cast<uint32_t>(want) && static_cast<uint32_t>(want) <= incl)
+                {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                    {
+                        if (before < static_cast<uint32_t>(want) && static_cast<uint32_t>(want) <= before + h[j])
+                        {
+                            ctrl->sel_bin = lane * 8 + j;
+                            ctrl->sel_before = static_cast<int>(before);
+                            ctrl->sel_count = static_cast<int>(h[j]);
+                        }
+                        before += h[j];
+                    }
+                }
+            }
+            __syncthreads();
+            const int bin = ctrl->sel_bin;
+            const int count = ctrl->sel_count;
+            want -= ctrl->sel_before;
+            lo += static_cast<unsigned long long>(bin) << shift;
+            const unsigned long long top = lo + ((1ULL << shift) - 1ULL); // (wraps when the bucket reaches the top)
+            hi = top >= lo && top < hi ? top : hi;
+            if (shift == 0)
+            {
+                // one key value per bucket: it is the pivot, `want` of its copies stay
+                pivot = lo;
+                ties = want;
+                break;
+            }
+            if (count <= 32)
+            {
+                // rank the bucket's keys inside one warp
+                if (tid == 0)
+                {
+                    ctrl->sel_count = 0;
+                }
+                __syncthreads();
+#pragma unroll
+                for (int i = 0; i < E; ++i)
+                {
+                    const unsigned long long key = pair_key(pd[i], px[i]);
+                    if (key >= lo && key <= hi)
+                    {
+                        last[atomicAdd(&ctrl->sel_count, 1)] = key;
+                    }
+                }
+                __syncthreads();
+                if (tid < 32)
+                {
+                    const unsigned long long mine = lane < count ? last[lane] : PAD_KEY;
+                    int less = 0;
+                    int same = 0;
+                    for (int j = 0; j < count; ++j)
+                    {
+                        const unsigned long long other = __shfl_sync(FULL_MASK, mine, j);
+                        less += other < mine ? 1 : 0;
+                        same += other == mine ? 1 : 0;
+                    }
+                    if (lane < count && less < want && want <= less + same)
+                    {
+                        // (copies of one key all get here and write the same words)
+                        ctrl->key_lo = mine;
+                        ctrl->sel_before = want - less;
+                    }
+                }
+                __syncthreads();
+                pivot = ctrl->key_lo;
+                ties = ctrl->sel_before;
+                break;
+            }
+            // (the barrier after the scan also keeps the next level's clearing of the buckets behind
+            // every thread's read of the scan's result)
+            __syncthreads();
+        }
+    }
+    else
+    {
+        __syncthreads();
+    }
+    // compaction: survivors into the front of the buffer area, any order
+    float* out_d = s.buf_d;
+    int* out_x = s.buf_x;
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < E; ++i)
+    {
+        const unsigned long long key = pair_key(pd[i], px[i]);
+        bool keep = key < pivot;
+        if (key == pivot && key != PAD_KEY)
+        {
+            keep = atomicAdd(&ctrl->sel_ties, 1) < ties;
+        }
+        const unsigned b = __ballot_sync(FULL_MASK, keep);
+        if (b != 0)
+        {
+            int base = 0;
+            if (lane == 0)
+            {
+                base = atomicAdd(&ctrl->sel_kept, __popc(b));
+            }
+            base = __shfl_sync(FULL_MASK, base, 0);
+            if (keep)
+            {
+                const int pos = base + __popc(b & ((1U << lane) - 1U));
+                out_d[pos] = pd[i];
+                out_x[pos] = px[i];
+            }
+        }
+    }
+    __syncthreads();
+    const int kept = ctrl->sel_kept;
+#pragma unroll
+    for (int r = 0; r < IPT; ++r)
+    {
+        const int e = tid * IPT + r;
+        ld[r] = e < kept ? out_d[e] : INFINITY;
+        lx[r] = e < kept ? out_x[e] : PAD_IDX;
+    }
+    if (tid == 0)
+    {
+        // the pivot is the k-th smallest pair seen so far
+        float rd = INFINITY;
+        int rx = PAD_IDX;
+        if (pivot != PAD_KEY)
+        {
+            uint32_t u = static_cast<uint32_t>(pivot >> 32);
+            u = (u & 0x80000000U) != 0 ? (u ^ 0x80000000U) : ~u;
+            rd = __uint_as_float(u);
+            rx = static_cast<int>(static_cast<uint32_t>(pivot) ^ 0x80000000U);
+        }
+        ctrl->r_d = rd;
+        ctrl->r_x = rx;
+        ctrl->count = 0;
+    }
+    __syncthreads();
+    return 0;
+}
+
+// Lists of this many pairs and more are folded by selection.
+constexpr int SELECT_FOLD_FROM = 1024;
+
 // Folds buffer entries into the list, L at a time, and publishes the new radius in ctrl->r_d/r_x.
 // Whole chunks of L are always folded; a remainder is folded too (padded) when it holds at least
 // `keep_below` entries, else it is moved to the front of the buffer and stays a candidate.
@@ -277,6 +557,10 @@ template <int THREADS, int IPT>
 __device__ __forceinline__ int fold_buffer(float (&ld)[IPT], int (&lx)[IPT], row_ctx s, int valid, int keep_below)
 {
     constexpr int L = THREADS * IPT;
+    if constexpr (L >= SELECT_FOLD_FROM)
+    {
+        return fold_select<THREADS, IPT>(ld, lx, s, valid);
+    }
     const int tid = threadIdx.x;
     int base = 0;
     for (; base < valid; base += L)
@@ -348,12 +632,13 @@ __device__ __forceinline__ int fold_buffer(float (&ld)[IPT], int (&lx)[IPT], row
 // the full buffer and retry the rest.  Leaves the number of buffered entries in ctrl->count and
 // the radius in ctrl->r_d/r_x.
 template <int THREADS, int IPT>
-__device__ __forceinline__ void stage_slow(float (&ld)[IPT], int (&lx)[IPT], row_ctx s, const float4* sv, int nv, int e_base,
+__device__ __forceinline__ bool stage_slow(float (&ld)[IPT], int (&lx)[IPT], row_ctx s, const float4* sv, int nv, int e_base,
                                         int count0)
 {
     constexpr int B = 2 * THREADS * IPT;
     const int tid = threadIdx.x;
     const int lane = tid & 31;
+    bool folded = false; // the stage's survivors did not fit beside what the buffer held
     if (tid == 0)
     {
         s.ctrl->count = count0;
@@ -406,6 +691,7 @@ __device__ __forceinline__ void stage_slow(float (&ld)[IPT], int (&lx)[IPT], row
             }
             // the buffer is full: fold it, then offer the rest again under the tighter radius
             // (unlike the reference, which carries every allocated slot over)
+            folded = true;
             fold_buffer<THREADS, IPT>(ld, lx, s, B, 0);
             if (!s.keep_radius)
             {
@@ -419,6 +705,7 @@ __device__ __forceinline__ void stage_slow(float (&ld)[IPT], int (&lx)[IPT], row
             }
         }
     }
+    return folded;
 }
 
 // Number of values of the stage that pass the radius filter and are not above the pivot pair
@@ -891,7 +1178,20 @@ __global__ void __launch_bounds__(THREADS, BITSKNN_SELECT_MINBLOCKS) select_kern
         bool dense = false;
         if (event == EV_PLAN || event == EV_OVERFLOW)
         {
-            bool slow = s.keep_radius; // the un-buffered ablation sorts and merges every value
+            // the un-buffered ablation sorts and merges every value; with folds by selection a dense
+            // stage is cheapest taken as it is (a fold costs less than the plan's sorted sample)
+            bool slow = s.keep_radius || L >= SELECT_FOLD_FROM;
+            if (L >= SELECT_FOLD_FROM)
+            {
+                if (event == EV_OVERFLOW)
+                {
+                    __syncthreads();
+                    if (tid == 0)
+                    {
+                        *inc = 0;
+                    }
+                }
+            }
             if (!slow)
             {
                 if (event == EV_OVERFLOW)
@@ -925,7 +1225,11 @@ __global__ void __launch_bounds__(THREADS, BITSKNN_SELECT_MINBLOCKS) select_kern
             }
             if (slow)
             {
-                stage_slow<THREADS, IPT>(ld, lx, s, sv, nv, e_base, count0);
+                const bool folded = stage_slow<THREADS, IPT>(ld, lx, s, sv, nv, e_base, count0);
+                if (L >= SELECT_FOLD_FROM)
+                {
+                    dense = folded || event == EV_OVERFLOW;
+                }
                 count0 = s.ctrl->count;
                 if (!s.keep_radius)
                 {
@@ -968,6 +1272,12 @@ __global__ void __launch_bounds__(THREADS, BITSKNN_SELECT_MINBLOCKS) select_kern
     if (state.count0 > 0)
     {
         fold_buffer<THREADS, IPT>(ld, lx, s, state.count0, 0);
+    }
+    if constexpr (L >= SELECT_FOLD_FROM)
+    {
+        // the list was kept as a set: sorted once, here
+        __syncthreads();
+        block_sort<THREADS, IPT>(ld, lx, false, s.buf_d, s.buf_x, tid);
     }
 
     float* od = p.out_dist + vrow * p.k;
@@ -1070,7 +1380,8 @@ template <int THREADS, int IPT>
 int launch_select(select_params p, const launch_shape& shape, int64_t vrows, cudaStream_t stream)
 {
     constexpr int L = THREADS * IPT;
-    p.merge_at = std::min(L, std::max(1, (L * shape.merge_pct) / 100));
+    // (folds by selection take the whole buffer of 2 L slots whatever it holds, so they may wait longer)
+    p.merge_at = std::min(L >= SELECT_FOLD_FROM ? 2 * L - L / 8 : L, std::max(1, (L * shape.merge_pct) / 100));
     // a stage is a whole number of 4-vectors per thread
     const int stage_bytes = std::max((shape.stage_bytes / 4096) * 4096, 4096);
     p.stage_floats = std::max(4 * THREADS, (stage_bytes / 4 / (4 * THREADS)) * (4 * THREADS));

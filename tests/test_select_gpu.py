@@ -90,6 +90,28 @@ def test_special_values(bk, oracle, cuda):
     run_select(bk, oracle, dist, 2048)
 
 
+@pytest.mark.parametrize("k", [1024, 2048])
+def test_long_lists_with_runs_of_equal_distances(bk, oracle, cuda, k):
+    # lists of 1024 pairs and more are folded by selection on (distance, label) keys: rows in which
+    # the k-th pair sits inside a long run of equal distances, at the top of the key range (+inf),
+    # at its bottom (-inf) and in the middle, and repeated (distance, label) pairs
+    rng = np.random.default_rng(k)
+    n = 20000
+    dist = np.full((6, n), np.inf, dtype=np.float32)
+    dist[0, 17] = 1.0
+    dist[1, :] = -np.inf
+    dist[1, 5::7] = rng.random(len(dist[1, 5::7]), dtype=np.float32)
+    dist[2, :] = 0.5
+    dist[2, ::50] = rng.random(len(dist[2, ::50]), dtype=np.float32)
+    dist[3, :] = rng.integers(0, 3, size=n).astype(np.float32)
+    dist[4, :] = np.float32(3.0e38)
+    dist[4, 1::2] = -np.float32(3.0e38)
+    dist[5, :] = rng.random(n, dtype=np.float32)
+    run_select(bk, oracle, dist, k)
+    labels = rng.integers(0, 40, size=(6, n)).astype(np.int32)   # many identical pairs
+    run_select(bk, oracle, dist, k, labels=labels)
+
+
 @pytest.mark.parametrize("n,k", [(3, 16), (100, 256), (1, 1), (255, 2048)])
 def test_rows_shorter_than_k_are_padded(bk, oracle, cuda, n, k):
     rng = np.random.default_rng(n)
