@@ -59,7 +59,8 @@ def select_candidates(k):
             blocks = max(1, 1024 // t)
             if smem * blocks > 226 * 1024:      # keep the block count the register budget allows
                 continue
-            for merge_pct in ((50, 75) if t * i <= 256 else (75, 100)):
+            # (lists of 1024 pairs and more are folded by selection, which takes the whole buffer: later folds)
+            for merge_pct in ((50, 75) if t * i <= 256 else ((75, 100) if t * i < 1024 else (100, 140))):
                 out.append((t, i, stage_bytes, stages, merge_pct, 2))
     return out
 

@@ -72,8 +72,10 @@ int bitsknn_selftest_bounded_wait(bitsknn_stream_t stream);
  *                         block may use makes the next selection return INVALID_ARGUMENT
  *   "select.stages"       stages in the ring (2..8; 0 = automatic, the default)
  *   "select.merge_at"     merge the candidate buffer when it holds at least this percentage
- *                         of its capacity (1..100; 100 = only when full, like the reference;
- *                         0 = automatic, the default: 50 for lists of up to 256 pairs, else 75)
+ *                         of the list length (1..100; 100 = like the reference; lists of 1024
+ *                         pairs and more, which are folded by selection over a buffer of twice
+ *                         the list length, take up to 187; 0 = automatic, the default: 50 for
+ *                         lists of up to 256 pairs, 75 for longer ones, 140 from 1024 pairs)
  *   "select.unroll"       128-bit vectors per thread examined under one warp vote (0 = automatic,
  *                         2 or 4; other values are rejected)
  *   "select.threads" / "select.ipt"  block size (256, 512, 1024) and list pairs per thread (1, 2, 4)
