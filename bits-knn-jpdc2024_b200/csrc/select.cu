@@ -1178,19 +1178,18 @@ __global__ void __launch_bounds__(THREADS, BITSKNN_SELECT_MINBLOCKS) select_kern
         bool dense = false;
         if (event == EV_PLAN || event == EV_OVERFLOW)
         {
-            // the un-buffered ablation sorts and merges every value; with folds by selection a dense
-            // stage is cheapest taken as it is (a fold costs less than the plan's sorted sample)
-            bool slow = s.keep_radius || L >= SELECT_FOLD_FROM;
-            if (L >= SELECT_FOLD_FROM)
+            // the un-buffered ablation sorts and merges every value; with folds by selection the first
+            // stage (radius +inf: everything goes in) is cheaper taken as it is than planned: its three
+            // or four folds cost less than the plan's sorted sample and counting passes
+            const bool first_unplanned = L >= SELECT_FOLD_FROM && event == EV_PLAN && c == 0;
+            bool slow = s.keep_radius || first_unplanned;
+            if (L >= SELECT_FOLD_FROM && count0 >= L && !slow)
             {
-                if (event == EV_OVERFLOW)
-                {
-                    __syncthreads();
-                    if (tid == 0)
-                    {
-                        *inc = 0;
-                    }
-                }
+                // the plan sorts its sample in the upper half of the buffer; with folds by selection
+                // the buffer may hold more than a list's worth by now: those go into the list first
+                count0 = fold_buffer<THREADS, IPT>(ld, lx, s, count0, 0);
+                s.r_d = s.ctrl->r_d;
+                s.r_x = s.ctrl->r_x;
             }
             if (!slow)
             {
@@ -1226,10 +1225,7 @@ __global__ void __launch_bounds__(THREADS, BITSKNN_SELECT_MINBLOCKS) select_kern
             if (slow)
             {
                 const bool folded = stage_slow<THREADS, IPT>(ld, lx, s, sv, nv, e_base, count0);
-                if (L >= SELECT_FOLD_FROM)
-                {
-                    dense = folded || event == EV_OVERFLOW;
-                }
+                dense = first_unplanned && folded;
                 count0 = s.ctrl->count;
                 if (!s.keep_radius)
                 {
