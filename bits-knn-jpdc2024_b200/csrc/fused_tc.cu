@@ -38,7 +38,8 @@
 //   Why two kinds of warps: with the pushes and folds inside the scanning warps, every tile waited
 //   for the slowest of the eight warps (a push costs about a thousand clocks, a fold two to
 //   three thousand, and nine tiles in ten had at least one), and the MMAs waited with it.
-// After the scan the 2 * parts lists of every query hold its candidates by tensor-core distance;
+// After the scan the lists of every query (two, or 2 * parts where the database was cut into
+// ranges) hold its candidates by tensor-core distance;
 // rerank_lists() recomputes every candidate's distance as the exact FP32 chain of (y - x)^2 and
 // reports the k smallest pairs by that, so the rounding of the tensor-core inputs only decides
 // which pairs are looked at (with an allowance in the acceptance bound), not what is reported.
@@ -81,7 +82,8 @@ struct ftc_params
     int nsteps; // MMA K steps (32 bytes) per row that hold data
     int hs;     // steps of the hi part of a compact split image (0: plain image)
     int stages;
-    int parts;
+    int parts;       // database ranges of the query tiles from full_blocks on
+    int full_blocks; // leading query tiles that are scanned whole, one block each
     int64_t tiles;
     int cap;          // candidate slots per (group, query): 32 or 16
     int fold_above;   // a buffer is folded when it holds more than this many candidates (cap - 16 or cap - 8)
@@ -139,10 +141,15 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
     const int warp = tid >> 5;
     const int lane = tid & 31;
 
-    const int64_t qb = blockIdx.x / p.parts;
-    const int part = static_cast<int>(blockIdx.x - qb * p.parts);
+    // the first full_blocks blocks scan the whole database for one query tile each; the others
+    // share the remaining query tiles, `parts` database ranges per tile
+    const bool whole = static_cast<int64_t>(blockIdx.x) < p.full_blocks;
+    const int64_t tail_block = static_cast<int64_t>(blockIdx.x) - p.full_blocks;
+    const int nparts = whole ? 1 : p.parts;
+    const int64_t qb = whole ? static_cast<int64_t>(blockIdx.x) : p.full_blocks + tail_block / p.parts;
+    const int part = whole ? 0 : static_cast<int>(tail_block % p.parts);
     // tiles of 128 points; a part is a whole number of MMAs (a tile beyond n holds no valid column)
-    const int64_t per = ((p.tiles + p.parts - 1) / p.parts + NT - 1) / NT * NT;
+    const int64_t per = ((p.tiles + nparts - 1) / nparts + NT - 1) / NT * NT;
     const int64_t tiles_up = (p.tiles + NT - 1) / NT * NT;
     const int64_t t_begin = part * per;
     const int64_t t_end = t_begin + per < tiles_up ? t_begin + per : tiles_up;
@@ -518,7 +525,8 @@ struct ftc_layout
     int nsteps;  // K steps that hold data
     int nkb;     // 128-byte K blocks per row
     int kl;
-    int parts;
+    int parts;       // database ranges per query tile from full_blocks on
+    int full_blocks; // leading query tiles scanned whole
     int k_scan;  // list position of the radius during the scan: k plus a margin, at most kl
     size_t off_pn, off_qn, off_max, off_p, off_q, off_ld, off_lx, total;
 };
@@ -539,33 +547,43 @@ ftc_layout ftc_layout_of(int64_t n, int64_t q, int dim, int k, bool bf16)
     l.k_scan = std::min(l.kl, k + std::max(4, k / 4));
     const int64_t nqb = (q + TILE_M - 1) / TILE_M;
     const int64_t tiles = (n + TILE_N - 1) / TILE_N;
-    // The database is split into parts when the query tiles alone cannot occupy the SMs.  A block's
-    // time is its share of the scan plus the work of bringing its lists' radii down, which hardly
-    // shrinks with the part (measured at q = 2^16, n = 2^20 with one and two parts: that work is
-    // about 0.3 of a full scan for k <= 32 and 0.45 above), and the blocks run in waves of one per
-    // SM: the number of parts (of at least 64 tiles) with the smallest waves x block time wins
-    // (q = 8192: two parts, one wave of 128 blocks, 5.3 ms at dim 32, k = 64; three parts: 7.8 ms).
+    // Blocks run in waves of one per SM.  A block's time is its share of the scan plus the work of
+    // bringing its lists' radii down, which hardly shrinks with the range it scans (measured at
+    // q = 2^16, n = 2^20 with one and two ranges: that work is about 0.3 of a full scan for k <= 32
+    // and 0.45 above).  So: as many whole waves of query tiles as there are scan the database whole,
+    // one block per tile, and the query tiles that are left over -- all of them when there are fewer
+    // tiles than SMs -- are cut into database ranges (of at least 64 tiles), as many as make
+    // waves x block time smallest (q = 8192: 64 tiles, two ranges, one wave of 128 blocks: 5.3 ms at
+    // dim 32, k = 64, against 7.8 ms with three ranges; q = 2^16: 444 tiles whole in three waves and
+    // 68 tiles in two ranges in a fourth, shorter one).
     const int sms = device_sm_count();
     const double fixed_work = k > 32 ? 0.45 : 0.3;
     const int64_t max_parts = std::max<int64_t>(1, std::min<int64_t>(tiles / 64, 4 * sms));
-    double best = 0.0;
+    l.full_blocks = static_cast<int>(nqb / sms * sms);
+    const int64_t rest = nqb - l.full_blocks;
     l.parts = 1;
-    for (int64_t parts = 1; parts <= max_parts; ++parts)
+    if (rest > 0)
     {
-        const double waves = static_cast<double>((nqb * parts + sms - 1) / sms);
-        const double cost = waves * (1.0 / static_cast<double>(parts) + fixed_work);
-        if (parts == 1 || cost < best * 0.98)
+        double best = 0.0;
+        for (int64_t parts = 1; parts <= max_parts; ++parts)
         {
-            best = cost;
-            l.parts = static_cast<int>(parts);
-        }
-        if (nqb * parts >= 4 * static_cast<int64_t>(sms))
-        {
-            break;
+            const double waves = static_cast<double>((rest * parts + sms - 1) / sms);
+            const double cost = waves * (1.0 / static_cast<double>(parts) + fixed_work);
+            if (parts == 1 || cost < best * 0.98)
+            {
+                best = cost;
+                l.parts = static_cast<int>(parts);
+            }
+            if (rest * parts >= 4 * static_cast<int64_t>(sms))
+            {
+                break;
+            }
         }
     }
     if (const int forced = tuning_value("fused.parts", 0); forced > 0)
     {
+        // a forced count applies to every query tile
+        l.full_blocks = 0;
         l.parts = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(forced, std::max<int64_t>(1, tiles / 64))));
     }
     const size_t esz = bf16 ? 2 : 4;
@@ -621,6 +639,7 @@ int run_ftc(const float* points, const float* queries, int64_t n, int64_t q, int
     p.nsteps = l.nsteps;
     p.hs = l.hs;
     p.parts = l.parts;
+    p.full_blocks = l.full_blocks;
     p.tiles = (n + TILE_N - 1) / TILE_N;
     p.k = l.k_scan;
     p.index_base = index_base;
@@ -687,7 +706,7 @@ int run_ftc(const float* points, const float* queries, int64_t n, int64_t q, int
     }
 
     const int64_t nqb = (q + TILE_M - 1) / TILE_M;
-    const int64_t grid = nqb * p.parts;
+    const int64_t grid = l.full_blocks + (nqb - l.full_blocks) * p.parts;
     int rc;
     switch (l.kl * nt)
     {
@@ -717,8 +736,24 @@ int run_ftc(const float* points, const float* queries, int64_t n, int64_t q, int
     // The 2 * parts lists of every query hold its candidates ranked by tensor-core distances.  The
     // result is decided by the exact FP32 distance of every candidate (one FMA chain of (y - x)^2
     // per pair, as the FP32 path computes it), which is also the distance reported.
-    return rerank_lists(p.list_x, static_cast<int64_t>(q) * l.kl, l.kl, q, 2 * l.parts, l.kl, k, points, queries, n, dim,
-                        index_base, out_dist, out_idx, stream);
+    // (the queries of the tiles scanned whole have two lists each, the others 2 * parts)
+    const int64_t q_whole = std::min<int64_t>(q, static_cast<int64_t>(l.full_blocks) * TILE_M);
+    const int64_t list_stride = static_cast<int64_t>(q) * l.kl;
+    if (q_whole > 0)
+    {
+        if (const int rc2 = rerank_lists(p.list_x, list_stride, l.kl, q_whole, 2, l.kl, k, points, queries, n, dim, index_base,
+                                         out_dist, out_idx, stream);
+            rc2 != BITSKNN_OK)
+        {
+            return rc2;
+        }
+    }
+    if (q_whole < q)
+    {
+        return rerank_lists(p.list_x + q_whole * l.kl, list_stride, l.kl, q - q_whole, 2 * l.parts, l.kl, k, points,
+                            queries + q_whole * dim, n, dim, index_base, out_dist + q_whole * k, out_idx + q_whole * k, stream);
+    }
+    return BITSKNN_OK;
 }
 
 } // namespace

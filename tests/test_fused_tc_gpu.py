@@ -97,6 +97,25 @@ def test_few_queries_long_database_is_cut_into_parts(bk, cuda):
     check_against_fp32(bk, points, queries, 200, bk.L2_TF32)
 
 
+@pytest.mark.parametrize("mode_name", ["tf32", "bf16"])
+def test_more_query_tiles_than_sms(bk, cuda, mode_name):
+    # whole waves of query tiles scan the database whole, the tiles left over are cut into database
+    # ranges: both kinds of blocks in one launch (a few more tiles than SMs), indices against FP32
+    mode = bk.L2_TF32 if mode_name == "tf32" else bk.L2_BF16
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    q, n, dim, k = (sms + 2) * 128 - 37, 20000, 8, 16
+    g = torch.Generator(device="cuda").manual_seed(5)
+    points = torch.rand(n, dim, device="cuda", generator=g)
+    queries = torch.rand(q, dim, device="cuda", generator=g)
+    d_tc, i_tc = bk.fused(points, queries, k, mode=mode)
+    d_ex, i_ex = bk.fused(points, queries, k, mode=bk.L2_EXACT)
+    torch.cuda.synchronize()
+    bk.device_status()
+    same = (i_tc == i_ex).all(dim=1).float().mean().item()
+    assert same >= 0.999, same
+    assert bool((d_tc[:, 1:] >= d_tc[:, :-1]).all())
+
+
 def test_many_parts_and_clustered_data(bk, cuda):
     # 2^18 points: several blocks per query tile; clustered data (256 centres, sigma 0.05)
     gen = torch.Generator(device="cuda").manual_seed(5)
