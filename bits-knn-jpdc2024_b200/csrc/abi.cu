@@ -40,6 +40,7 @@ tuning_entry g_tuning[] = {
     {"fused.parts", 0, 0, 64},
     {"fused.tc_cap", 0, 0, 32},
     {"fused.tc_fold_above", 0, 0, 31},
+    {"fused.tc_tf32_plain", 0, 0, 2},
     {"profile.kernel_events", 0, 0, 1},
 };
 

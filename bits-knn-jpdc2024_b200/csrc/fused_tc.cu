@@ -534,7 +534,18 @@ struct ftc_layout
 ftc_layout ftc_layout_of(int64_t n, int64_t q, int dim, int k, bool bf16)
 {
     ftc_layout l{};
-    const tcpipe::image_shape img = tcpipe::image_shape_of(dim, bf16, true);
+    // TF32 from 32 dimensions on: the plainly rounded image (one product per K step instead of the
+    // split image's three).  Its distances are off by up to 2^-11 of |x|^2 + |y|^2; the acceptance
+    // bound allows for that, the lists keep a margin and the exact re-ranking decides, and at these
+    // dimensions few enough points lie that close to the k-th distance: recall 1.0 and no error of
+    // the k-th distance in the quality tests at dim 32 and 64, uniform and clustered (q = 2^14,
+    // n = 2^20: dim 64, k = 16 11.3 -> 7.7 ms; dim 32 7.7 -> 6.5 ms).  At lower dimensions too many
+    // points lie within the allowance (dim 16, tight clusters: the stated bounds are missed; dim 4:
+    // k-th distance off by 4 %), and a BF16 image rounded plainly (2^-8) is too coarse at every
+    // dimension: both keep the split.
+    const int want_plain = tuning_value("fused.tc_tf32_plain", 0);
+    const bool plain = !bf16 && (want_plain == 1 || (want_plain == 0 && dim >= 32));
+    const tcpipe::image_shape img = tcpipe::image_shape_of(dim, bf16, true, plain);
     l.dim_pad = img.dim_pad;
     l.split = img.split;
     l.hs = img.hs;

@@ -240,14 +240,14 @@ struct image_shape
     int nkb;
 };
 
-inline image_shape image_shape_of(int dim, bool bf16, bool norm_cols)
+inline image_shape image_shape_of(int dim, bool bf16, bool norm_cols, bool plain = false)
 {
     image_shape l{};
     const int unit = bf16 ? 64 : 32; // elements per 128-byte K block
     const int step = unit / 4;       // elements per MMA K step
     const int dp = (dim + step - 1) / step * step;
     const int extra = norm_cols ? 1 : 0;
-    if (2 * (dp / step) + extra <= MAX_KB * 4)
+    if (!plain && 2 * (dp / step) + extra <= MAX_KB * 4)
     {
         // compact split image: [hi (dp) | lo (dp) | norm columns, padded to one step]
         l.split = 2;

@@ -88,6 +88,8 @@ int bitsknn_selftest_bounded_wait(bitsknn_stream_t stream);
  *                         0 = automatic (32, or 16 when the operand ring needs the shared memory), 16, 32
  *   "fused.tc_fold_above" fold a candidate buffer of those kernels above this many candidates
  *                         (1 .. slots - 1; 0 = automatic)
+ *   "fused.tc_tf32_plain" image of the fused TF32 kernel: 0 = automatic (plainly rounded from 32
+ *                         dimensions on, hi/lo split below), 1 = always plain, 2 = always split
  *   "profile.kernel_events"  1 = record CUDA events around the main kernels (bitsknn_kernel_ms)
  *   "fused.tc_mma_n"      points per tensor-core MMA of the fused TF32/BF16 kernels: 0 = 256
  *                         whenever the operand ring fits shared memory (default), 128 = always 128
