@@ -69,7 +69,7 @@ constexpr int FT_MMA_WARP = 17;
 constexpr int FT_MAIL_SLOTS = 16;    // chunks a scanner may be ahead of its helper
 // mail from a scanner to its helper: (local tile << 4) | mask of the tile's four chunks to look at
 constexpr uint32_t FT_MAIL_SCAN_DONE = 0xFFFFFFFFU;
-constexpr int FT_ACCS = tcpipe::ACCS; // four 128-column accumulators: each consumer group owns two
+constexpr int FT_ACCS = tcpipe::ACCS; // four 128-column accumulators: each scanner group owns two
 constexpr int CAP = 32; // candidate slots per (group, query); 16 when the operand ring needs the room
 
 struct ftc_params
@@ -666,7 +666,7 @@ int run_ftc(const float* points, const float* queries, int64_t n, int64_t q, int
         return fail(BITSKNN_ERR_CUDA, "CUDA error. cannot resolve the device status word");
     }
     // shared memory: query image + ring + barriers + radii + candidate buffers.  The MMA covers 256
-    // points (two tiles, one per consumer group) when at least two of its 32 KiB stages fit beside
+    // points (two tiles, one per scanner group) when at least two of its 32 KiB stages fit beside
     // the query image, else 128 points.
     // 32 candidate slots per (group, query); 16 for long image rows (five or more 128-byte K blocks:
     // TF32 from dim 57, BF16 from dim 121), where the 32 KiB that frees -- two more 16 KiB stages --

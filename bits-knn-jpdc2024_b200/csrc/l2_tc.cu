@@ -13,7 +13,7 @@
 //              recall@k >= 0.999 against the FP32 path
 //   main       352 threads per block, one block per SM:
 //              warp 8      TMA producer: query tile once, then point tiles through a ring
-//              warps 9, 10 tcgen05.mma issue in turn (tc_pipeline.cuh), M = 128 queries,
+//              warps 9, 10 tcgen05.mma issue, each with its own accumulators (tc_pipeline.cuh), M = 128 queries,
 //                          N = 256 points (two accumulators at once) or 128, K = 8 TF32 / 16 BF16
 //                          per instruction; warp 9 allocates the 512 TMEM columns
 //              warps 0-7   epilogue, two groups of four: group g drains every other 128-point
