@@ -257,11 +257,12 @@ inline image_shape image_shape_of(int dim, bool bf16, bool norm_cols, bool plain
     }
     else
     {
-        // plain image: [row | norm columns], padded to whole K blocks
+        // plain image: [row | norm columns], padded to whole K steps (the part of the last K block
+        // beyond the row is filled with zeros by the TMA unit and costs neither traffic nor MMAs)
         l.split = 0;
         l.hs = 0;
-        l.dim_pad = ((dim + 3 * extra + unit - 1) / unit) * unit;
-        l.nsteps = l.dim_pad / step;
+        l.nsteps = (dim + 3 * extra + step - 1) / step;
+        l.dim_pad = l.nsteps * step;
     }
     l.nkb = (l.nsteps + 3) / 4;
     return l;
