@@ -51,7 +51,8 @@ struct tiled_params
     int dp; // coordinates padded to a multiple of 4
     int k;
     int32_t index_base;
-    int parts;
+    int parts;       // database ranges per query tile from full_blocks on
+    int full_blocks; // leading query tiles scanned whole, one block each
     int64_t tiles; // point tiles of 128
     float* list_d; // [parts][q][KL]
     int32_t* list_x;
@@ -99,11 +100,16 @@ __global__ void __launch_bounds__(FT_THREADS, 2) fused_tiled_kernel(const tiled_
     const int tx = tid & 15;
     const int ty = tid >> 4;
     // (32-bit tile and slab counters: fewer registers; the host checks that they fit)
-    const int qb = static_cast<int>(blockIdx.x) / p.parts;
-    const int part = static_cast<int>(blockIdx.x) - qb * p.parts;
+    // the first full_blocks blocks scan the whole database for one query tile each; the others
+    // share the remaining query tiles, `parts` database ranges per tile
+    const bool whole = static_cast<int>(blockIdx.x) < p.full_blocks;
+    const int tail_block = static_cast<int>(blockIdx.x) - p.full_blocks;
+    const int nparts = whole ? 1 : p.parts;
+    const int qb = whole ? static_cast<int>(blockIdx.x) : p.full_blocks + tail_block / p.parts;
+    const int part = whole ? 0 : tail_block % p.parts;
     const int64_t m0 = static_cast<int64_t>(qb) * FT_BM;
     const int tiles = static_cast<int>(p.tiles);
-    const int per = (tiles + p.parts - 1) / p.parts;
+    const int per = (tiles + nparts - 1) / nparts;
     const int t_begin = part * per;
     const int t_end = t_begin + per < tiles ? t_begin + per : tiles;
     const int nslab = (p.dp + FT_BK - 1) / FT_BK;
@@ -400,7 +406,8 @@ __global__ void __launch_bounds__(FT_THREADS, 2) fused_tiled_kernel(const tiled_
 struct tiled_layout
 {
     int kl;
-    int parts;
+    int parts;       // database ranges per query tile from full_blocks on
+    int full_blocks; // leading query tiles scanned whole
     int dp;
     size_t off_pimg, off_qimg, off_ld, off_lx, total;
 };
@@ -412,13 +419,19 @@ tiled_layout tiled_layout_of(int64_t n, int64_t q, int dim, int k)
     l.dp = (dim + 3) / 4 * 4;
     const int64_t nqb = (q + FT_BM - 1) / FT_BM;
     const int64_t tiles = (n + FT_BN - 1) / FT_BN;
-    // two blocks fit an SM; the database is split as far as all blocks still run at once
-    // (measured: q = 2^14 on 148 SMs takes 19.3 ms with 2 ranges, 21.8 with 3, 20.5 with 4)
+    // two blocks fit an SM.  As many whole waves of query tiles as there are scan the database whole;
+    // for the tiles left over (all of them when there are fewer than block slots) the database is
+    // split as far as those blocks still run at once (measured: q = 2^14 on 148 SMs takes 19.3 ms
+    // with 2 ranges, 21.8 with 3, 20.5 with 4)
     const int slots = 2 * device_sm_count();
-    const int64_t want = std::max<int64_t>(1, slots / nqb);
+    l.full_blocks = static_cast<int>(nqb / slots * slots);
+    const int64_t rest = nqb - l.full_blocks;
+    const int64_t want = rest > 0 ? std::max<int64_t>(1, slots / rest) : 1;
     l.parts = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(want, std::max<int64_t>(1, tiles / 32))));
     if (const int forced = tuning_value("fused.parts", 0); forced > 0)
     {
+        // a forced count applies to every query tile
+        l.full_blocks = 0;
         l.parts = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(forced, std::max<int64_t>(1, tiles / 32))));
     }
     const size_t lists = static_cast<size_t>(l.parts) * static_cast<size_t>(q) * l.kl;
@@ -508,6 +521,7 @@ int fused_tiled_launch(const float* points, const float* queries, int64_t n, int
     p.k = k;
     p.index_base = index_base;
     p.parts = l.parts;
+    p.full_blocks = l.full_blocks;
     p.tiles = tiles;
     p.list_d = reinterpret_cast<float*>(ws + l.off_ld);
     p.list_x = reinterpret_cast<int32_t*>(ws + l.off_lx);
@@ -516,7 +530,7 @@ int fused_tiled_launch(const float* points, const float* queries, int64_t n, int
     {
         return fail(BITSKNN_ERR_CUDA, "CUDA error. cannot resolve the device status word");
     }
-    const int64_t grid = nqb * l.parts;
+    const int64_t grid = l.full_blocks + (nqb - l.full_blocks) * l.parts;
     int rc;
     switch (l.kl)
     {
@@ -537,8 +551,24 @@ int fused_tiled_launch(const float* points, const float* queries, int64_t n, int
     {
         return rc;
     }
-    return merge_lists(p.list_d, p.list_x, static_cast<int64_t>(q) * l.kl, l.kl, q, l.parts, l.kl, k, nullptr, out_dist,
-                       out_idx, merge_input::sorted, stream);
+    // (the queries of the tiles scanned whole have one list, the others one per range)
+    const int64_t q_whole = std::min<int64_t>(q, static_cast<int64_t>(l.full_blocks) * FT_BM);
+    const int64_t list_stride = static_cast<int64_t>(q) * l.kl;
+    if (q_whole > 0)
+    {
+        if (const int rc2 = merge_lists(p.list_d, p.list_x, list_stride, l.kl, q_whole, 1, l.kl, k, nullptr, out_dist, out_idx,
+                                        merge_input::sorted, stream);
+            rc2 != BITSKNN_OK)
+        {
+            return rc2;
+        }
+    }
+    if (q_whole < q)
+    {
+        return merge_lists(p.list_d + q_whole * l.kl, p.list_x + q_whole * l.kl, list_stride, l.kl, q - q_whole, l.parts, l.kl, k,
+                           nullptr, out_dist + q_whole * k, out_idx + q_whole * k, merge_input::sorted, stream);
+    }
+    return BITSKNN_OK;
 }
 
 } // namespace bitsknn
