@@ -1235,6 +1235,12 @@ __global__ void __launch_bounds__(THREADS, BITSKNN_SELECT_MINBLOCKS) select_kern
             }
         }
         state.dense_run = dense ? state.dense_run + 1 : 0;
+        // The stage is done (every thread has passed a barrier after its last read of it): its memory
+        // is refilled now, before the fold, so that the copy runs while the block folds.
+        if (tid == 0 && c + g.NST < g.nchunks)
+        {
+            issue_chunk(g, c + g.NST, state.st);
+        }
         if (count0 >= g.merge_at)
         {
             count0 = fold_buffer<THREADS, IPT>(ld, lx, s, count0, g.merge_at);
@@ -1244,14 +1250,10 @@ __global__ void __launch_bounds__(THREADS, BITSKNN_SELECT_MINBLOCKS) select_kern
                 s.r_x = s.ctrl->r_x;
             }
         }
-        // the stage is done: its counter slot of two stages on is cleared, its memory refilled
+        // its counter slot of two stages on is cleared
         if (tid == 0)
         {
             s.ctrl->inc[state.i3 == 0 ? 2 : state.i3 - 1] = 0;
-            if (c + g.NST < g.nchunks)
-            {
-                issue_chunk(g, c + g.NST, state.st);
-            }
         }
         state.c = c + 1;
         state.i3 = state.i3 == 2 ? 0 : state.i3 + 1;
