@@ -699,8 +699,12 @@ int run_ftc(const float* points, const float* queries, int64_t n, int64_t q, int
     {
         return fail(BITSKNN_ERR_UNSUPPORTED_DIM, "Unsupported dimension: %d (query image does not fit shared memory)", dim);
     }
+    // One-K-block rows (BF16 up to dim 16, TF32 up to dim 8) are bound by the round trip of an
+    // accumulator, not by the MMAs: there 128-point MMAs, which hand every accumulator over by
+    // itself and sooner, are 2-4 % faster (q = 2^14, n = 2^20, dim 16: k = 16 5.39 -> 5.18 ms, k = 128
+    // 9.17 -> 8.77 ms); from two K blocks on the 256-point MMAs win (dim 32: 6.50 against 6.79 ms).
     const int want_n = tuning_value("fused.tc_mma_n", 0);
-    const bool wide = want_n == 128 ? false : room128 >= 4;
+    const bool wide = want_n == 128 ? false : (want_n == 256 || p.nkb >= 2) && room128 >= 4;
     const int nt = wide ? 2 : 1;
     p.stages = std::min(wide ? 4 : 8, room128 / nt);
     const size_t smem = fixed + (static_cast<size_t>(p.nkb) + static_cast<size_t>(p.stages) * nt) * STAGE_BYTES;

@@ -91,8 +91,10 @@ int bitsknn_selftest_bounded_wait(bitsknn_stream_t stream);
  *   "fused.tc_tf32_plain" image of the fused TF32 kernel: 0 = automatic (plainly rounded from 32
  *                         dimensions on, hi/lo split below), 1 = always plain, 2 = always split
  *   "profile.kernel_events"  1 = record CUDA events around the main kernels (bitsknn_kernel_ms)
- *   "fused.tc_mma_n"      points per tensor-core MMA of the fused TF32/BF16 kernels: 0 = 256
- *                         whenever the operand ring fits shared memory (default), 128 = always 128
+ *   "fused.tc_mma_n"      points per tensor-core MMA of the fused TF32/BF16 kernels: 0 = automatic
+ *                         (256 for image rows of two or more 128-byte K blocks when the operand
+ *                         ring fits shared memory, else 128), 128 = always 128, 256 = 256 whenever
+ *                         the ring fits
  * The reference's `--block-size` / `--items-per-thread` flags tune the same things for its
  * kernels (src/topk/singlepass/bits_knn.cu:98-114); here they are hints. */
 int bitsknn_set_tuning(const char* key, int value);
