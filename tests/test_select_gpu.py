@@ -112,6 +112,37 @@ def test_long_lists_with_runs_of_equal_distances(bk, oracle, cuda, k):
     run_select(bk, oracle, dist, k, labels=labels)
 
 
+@pytest.mark.parametrize("seed", range(24))
+def test_long_lists_random_shapes(bk, oracle, cuda, seed):
+    # k above 512 (lists folded by selection), row lengths around the stage and buffer sizes, value
+    # patterns that make stages sparse, dense, tied or partly infinite; whole rows and split rows
+    rng = np.random.default_rng(1000 + seed)
+    k = int(rng.choice([513, 777, 1000, 1024, 1025, 1500, 2000, 2048]))
+    n = int(rng.choice([k, k + 1, 3000, 4097, 16384, 16385, 50000, 131072 + 5, 300001]))
+    q = int(rng.integers(1, 5))
+    kind = seed % 5
+    if kind == 0:
+        dist = rng.random((q, n), dtype=np.float32)
+    elif kind == 1:
+        dist = np.sort(rng.random((q, n), dtype=np.float32), axis=1)[:, ::-1].copy()
+    elif kind == 2:
+        dist = rng.integers(0, 7, size=(q, n)).astype(np.float32)
+    elif kind == 3:
+        dist = np.sort(rng.random((q, n), dtype=np.float32), axis=1)
+    else:
+        dist = (rng.standard_normal((q, n)) * 1e3).astype(np.float32)
+        dist[:, ::11] = np.inf
+    run_select(bk, oracle, dist, k)
+    if n > 20000:
+        d = torch.from_numpy(dist).cuda()
+        got_d, got_i = bk.select_split(d, k, splits=int(rng.choice([2, 5])))
+        torch.cuda.synchronize()
+        bk.device_status()
+        want_d, want_i = oracle.select(dist, k)
+        assert np.array_equal(got_d.cpu().numpy().view(np.uint32), want_d.view(np.uint32)), "distances differ (split rows)"
+        assert np.array_equal(got_i.cpu().numpy(), want_i), "indices differ (split rows)"
+
+
 @pytest.mark.parametrize("n,k", [(3, 16), (100, 256), (1, 1), (255, 2048)])
 def test_rows_shorter_than_k_are_padded(bk, oracle, cuda, n, k):
     rng = np.random.default_rng(n)
