@@ -11,9 +11,10 @@
 // Block = 608 threads on one SM, 128 queries (the TMEM lanes):
 //   warp 16  TMA producer (query image once, point image K blocks through a ring of stages)
 //   warps 17, 18  tcgen05.mma issue, each with its own accumulators (tc_pipeline.cuh; warp 17 also
-//            allocates the tensor memory: 4 accumulators of 128 columns).  Whenever the ring fits,
-//            an MMA covers 256 points and fills two neighbouring accumulators, one per consumer
-//            group (NMMA = 256); long vectors fall back to 128 points per MMA.
+//            allocates the tensor memory: 4 accumulators of 128 columns).  For image rows of two
+//            or more K blocks an MMA covers 256 points and fills two neighbouring accumulators, one
+//            per scanner group (NMMA = 256), whenever the ring fits; one-K-block rows and long
+//            vectors take 128 points per MMA.
 //   warps 0-7  scanners, two groups of four.  Group g takes every other 128-point tile (each
 //            group alternates between two accumulators, so the MMAs run ahead of it); thread t of
 //            a group is query 32 * (warp % 4) + t and reads its row with tcgen05.ld, 64 columns
