@@ -739,9 +739,18 @@ def main():
     barrier()
     clocks = sampler.stop() if rank == 0 else None
     bk.device_status()
-    total_ms = max_over_ranks(ev[-2].elapsed_time(ev[-1]))
+    own_total_ms = ev[-2].elapsed_time(ev[-1])
+    total_ms = max_over_ranks(own_total_ms)
     kernel_ms = statistics.mean(ev[2 * s].elapsed_time(ev[2 * s + 1]) for s in range(args.steps))
     ms_per_step = total_ms / args.steps
+    per_rank = None
+    if world > 1:
+        # every rank's own clock: the timed region and the mean duration of its selection kernel
+        mine = torch.tensor([own_total_ms / args.steps, kernel_ms], dtype=torch.float64, device=dev)
+        everyone = [torch.empty_like(mine) for _ in range(world)]
+        dist_pg.all_gather(everyone, mine)
+        per_rank = {"ms_per_step": [round(float(t[0]), 4) for t in everyone],
+                    "select_kernel_ms": [round(float(t[1]), 4) for t in everyone]}
     value = q * n * world / (ms_per_step * 1e-3)
 
     algo_bytes = 4.0 * q * n + 8.0 * q * k
@@ -969,7 +978,7 @@ def main():
                            "l2_policy": "input (4 GiB per GPU) is larger than L2; no flush needed"},
                 "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "e2e_knn": e2e_knn,
                 "gpu_launches": launches_per_step * args.steps, "clocks": clocks}
-        for key, val in (("sharded_check", sharded_check), ("sweep", sweep), ("reference_gpu", reference_gpu),
+        for key, val in (("sharded_check", sharded_check), ("per_rank", per_rank), ("sweep", sweep), ("reference_gpu", reference_gpu),
                          ("kernels", kernels), ("c3", c3), ("c4", c4), ("knn_cpu_baseline", knn_cpu),
                          ("knn_sharded", knn_sharded), ("knn_sharded_strong", knn_sharded_strong)):
             if val is not None:
