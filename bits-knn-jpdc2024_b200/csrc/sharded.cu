@@ -144,7 +144,15 @@ int make_handle(bitsknn_sharded** out, void* comm, bool own, int rank, int world
     cudaError_t err = cudaGetDevice(&h->device);
     if (err == cudaSuccess)
     {
-        err = cudaStreamCreateWithFlags(&h->side, cudaStreamNonBlocking);
+        // lowest priority: the exchange and merge of one search run beside the next search's kernels
+        // and should only take the SMs those leave free
+        int least = 0;
+        int greatest = 0;
+        err = cudaDeviceGetStreamPriorityRange(&least, &greatest);
+        if (err == cudaSuccess)
+        {
+            err = cudaStreamCreateWithPriority(&h->side, cudaStreamNonBlocking, least);
+        }
     }
     for (int s = 0; s < SLOTS && err == cudaSuccess; ++s)
     {
