@@ -51,8 +51,7 @@ struct tiled_params
     int dp; // coordinates padded to a multiple of 4
     int k;
     int32_t index_base;
-    int parts;       // database ranges per query tile from full_blocks on
-    int full_blocks; // leading query tiles scanned whole, one block each
+    int parts;
     int64_t tiles; // point tiles of 128
     float* list_d; // [parts][q][KL]
     int32_t* list_x;
@@ -100,16 +99,11 @@ __global__ void __launch_bounds__(FT_THREADS, 2) fused_tiled_kernel(const tiled_
     const int tx = tid & 15;
     const int ty = tid >> 4;
     // (32-bit tile and slab counters: fewer registers; the host checks that they fit)
-    // the first full_blocks blocks scan the whole database for one query tile each; the others
-    // share the remaining query tiles, `parts` database ranges per tile
-    const bool whole = static_cast<int>(blockIdx.x) < p.full_blocks;
-    const int tail_block = static_cast<int>(blockIdx.x) - p.full_blocks;
-    const int nparts = whole ? 1 : p.parts;
-    const int qb = whole ? static_cast<int>(blockIdx.x) : p.full_blocks + tail_block / p.parts;
-    const int part = whole ? 0 : tail_block % p.parts;
+    const int qb = static_cast<int>(blockIdx.x) / p.parts;
+    const int part = static_cast<int>(blockIdx.x) - qb * p.parts;
     const int64_t m0 = static_cast<int64_t>(qb) * FT_BM;
     const int tiles = static_cast<int>(p.tiles);
-    const int per = (tiles + nparts - 1) / nparts;
+    const int per = (tiles + p.parts - 1) / p.parts;
     const int t_begin = part * per;
     const int t_end = t_begin + per < tiles ? t_begin + per : tiles;
     const int nslab = (p.dp + FT_BK - 1) / FT_BK;
@@ -520,53 +514,61 @@ int fused_tiled_launch(const float* points, const float* queries, int64_t n, int
     p.dp = l.dp;
     p.k = k;
     p.index_base = index_base;
-    p.parts = l.parts;
-    p.full_blocks = l.full_blocks;
     p.tiles = tiles;
-    p.list_d = reinterpret_cast<float*>(ws + l.off_ld);
-    p.list_x = reinterpret_cast<int32_t*>(ws + l.off_lx);
     p.status = device_status_word();
     if (p.status == nullptr)
     {
         return fail(BITSKNN_ERR_CUDA, "CUDA error. cannot resolve the device status word");
     }
-    const int64_t grid = l.full_blocks + (nqb - l.full_blocks) * l.parts;
-    int rc;
-    switch (l.kl)
-    {
-    case 32:
-        rc = launch_tiled<1>(p, mode, grid, stream);
-        break;
-    case 64:
-        rc = launch_tiled<2>(p, mode, grid, stream);
-        break;
-    case 128:
-        rc = launch_tiled<4>(p, mode, grid, stream);
-        break;
-    default:
-        rc = launch_tiled<8>(p, mode, grid, stream);
-        break;
-    }
-    if (rc != BITSKNN_OK)
-    {
-        return rc;
-    }
-    // (the queries of the tiles scanned whole have one list, the others one per range)
-    const int64_t q_whole = std::min<int64_t>(q, static_cast<int64_t>(l.full_blocks) * FT_BM);
-    const int64_t list_stride = static_cast<int64_t>(q) * l.kl;
+    // Two launches of the same kernel: the query tiles that scan the database whole (one block each,
+    // whole waves of them), then the tiles left over with `parts` database ranges each.  Each has its
+    // own region of lists: [q_whole][KL], then [parts][q - q_whole][KL].
+    float* list_d = reinterpret_cast<float*>(ws + l.off_ld);
+    int32_t* list_x = reinterpret_cast<int32_t*>(ws + l.off_lx);
+    // (tiles left over that are not cut: everything is one launch)
+    const int64_t q_whole = l.parts == 1 ? 0 : std::min<int64_t>(q, static_cast<int64_t>(l.full_blocks) * FT_BM);
+    const int64_t whole_blocks = l.parts == 1 ? 0 : l.full_blocks;
+    auto launch = [&](int64_t q0, int64_t rows, int parts, int64_t grid) {
+        tiled_params r = p;
+        r.q = rows;
+        r.parts = parts;
+        r.qimg = qimg + (q0 / FT_BM) * static_cast<int64_t>(l.dp + 1) * FT_BM;
+        r.list_d = list_d + q0 * l.kl;
+        r.list_x = list_x + q0 * l.kl;
+        switch (l.kl)
+        {
+        case 32:
+            return launch_tiled<1>(r, mode, grid, stream);
+        case 64:
+            return launch_tiled<2>(r, mode, grid, stream);
+        case 128:
+            return launch_tiled<4>(r, mode, grid, stream);
+        default:
+            return launch_tiled<8>(r, mode, grid, stream);
+        }
+    };
     if (q_whole > 0)
     {
-        if (const int rc2 = merge_lists(p.list_d, p.list_x, list_stride, l.kl, q_whole, 1, l.kl, k, nullptr, out_dist, out_idx,
-                                        merge_input::sorted, stream);
-            rc2 != BITSKNN_OK)
+        if (const int rc = launch(0, q_whole, 1, whole_blocks); rc != BITSKNN_OK)
         {
-            return rc2;
+            return rc;
+        }
+        if (const int rc = merge_lists(list_d, list_x, q_whole * l.kl, l.kl, q_whole, 1, l.kl, k, nullptr, out_dist, out_idx,
+                                       merge_input::sorted, stream);
+            rc != BITSKNN_OK)
+        {
+            return rc;
         }
     }
     if (q_whole < q)
     {
-        return merge_lists(p.list_d + q_whole * l.kl, p.list_x + q_whole * l.kl, list_stride, l.kl, q - q_whole, l.parts, l.kl, k,
-                           nullptr, out_dist + q_whole * k, out_idx + q_whole * k, merge_input::sorted, stream);
+        const int64_t rows = q - q_whole;
+        if (const int rc = launch(q_whole, rows, l.parts, (nqb - whole_blocks) * l.parts); rc != BITSKNN_OK)
+        {
+            return rc;
+        }
+        return merge_lists(list_d + q_whole * l.kl, list_x + q_whole * l.kl, rows * l.kl, l.kl, rows, l.parts, l.kl, k, nullptr,
+                           out_dist + q_whole * k, out_idx + q_whole * k, merge_input::sorted, stream);
     }
     return BITSKNN_OK;
 }
