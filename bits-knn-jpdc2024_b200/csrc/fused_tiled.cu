@@ -7,7 +7,7 @@
 // [coordinate][row] (coordinates zero padded to a multiple of four, which changes no FP32 sum),
 // followed by one row of squared norms (accumulated in coordinate order like the reference does).
 // The block keeps its query image resident in shared memory and streams the point image through a
-// ring of 16-coordinate slabs with 1-D bulk copies (cp.async.bulk + mbarrier): the compute warps
+// ring of 32-coordinate slabs with 1-D bulk copies (cp.async.bulk + mbarrier): the compute warps
 // issue no global loads at all, their inner loop is four 128-bit shared-memory loads per 64 FMAs.
 //
 // Per query the block keeps a 32-slot candidate buffer in shared memory (slots handed out by
@@ -35,11 +35,14 @@ namespace
 
 constexpr int FT_BM = 128;
 constexpr int FT_BN = 128;
-constexpr int FT_BK = 16;      // coordinates per slab
-constexpr int FT_STAGES = 4;   // slabs in flight
+// (measured at q = 2^14, n = 2^20: slabs of 32 coordinates with two in flight take one block barrier per
+// 32 coordinates and the same shared memory as four slabs of 16: dim 64 60.9 -> 58.7 ms, dim 32 33.1 -> 32.0;
+// three slabs of 32 no longer leave room for two blocks per SM at dim 64: 70.9 ms)
+constexpr int FT_BK = 32;      // coordinates per slab
+constexpr int FT_STAGES = 2;   // slabs in flight
 constexpr int FT_THREADS = 256;
 constexpr int FT_CAP = 32;
-constexpr int FT_SLAB_FLOATS = (FT_BK + 1) * FT_BN; // 16 coordinate rows + room for the norm row
+constexpr int FT_SLAB_FLOATS = (FT_BK + 1) * FT_BN; // the coordinate rows + room for the norm row
 constexpr int FT_MAX_DIM = 320;                     // query image + ring + buffers within 227 KiB
 
 struct tiled_params
@@ -80,7 +83,7 @@ template <int IPT, bool PARTIAL>
 __global__ void __launch_bounds__(FT_THREADS, 2) fused_tiled_kernel(const tiled_params p)
 {
     constexpr int KL = 32 * IPT;
-    // ring [FT_STAGES][17][128] | query image [dp][128] | candidate buffers [128][32] x 2
+    // ring [FT_STAGES][FT_BK + 1][128] | query image [dp][128] | candidate buffers [128][32] x 2
     extern __shared__ __align__(128) unsigned char ft_smem[];
     float* Bs = reinterpret_cast<float*>(ft_smem);
     float* As = Bs + FT_STAGES * FT_SLAB_FLOATS;
@@ -489,7 +492,7 @@ int fused_tiled_launch(const float* points, const float* queries, int64_t n, int
     }
     if (n / FT_BN * ((dim + FT_BK - 1) / FT_BK) >= (int64_t{1} << 31) - FT_BN)
     {
-        return fail(BITSKNN_ERR_INVALID_ARGUMENT, "the tiled fused kernel counts up to 2^31 slabs of 16 coordinates x 128 points");
+        return fail(BITSKNN_ERR_INVALID_ARGUMENT, "the tiled fused kernel counts up to 2^31 slabs of coordinates x 128 points");
     }
     const tiled_layout l = tiled_layout_of(n, q, dim, k);
     if (workspace == nullptr || workspace_bytes < l.total || (reinterpret_cast<uintptr_t>(workspace) & 255U) != 0)
