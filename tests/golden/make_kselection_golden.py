@@ -48,7 +48,7 @@ def invocations(lines):
 
 
 def main():
-    ref = pathlib.Path(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("BITSKNN_REFERENCE_DIR", "/root/reference"))
+    ref = pathlib.Path(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("BITSKNN_REFERENCE_DIR", str(pathlib.Path(__file__).resolve().parents[3] / "reference")))
     src = ref / "data" / "kselection-hopper01-108424.err"
     runs = list(invocations(src.read_text().splitlines()))
     configs = [(2 ** qp, 2 ** (30 - qp), 2 ** kp) for qp in (6, 8, 10, 12) for kp in range(5, 12)]
