@@ -45,7 +45,7 @@ Q = 1024
 N_COLS = 1 << 20
 METRIC = "bits top-k selection throughput"
 UNIT = "distances/s"
-# ncu: (2.4831 GB read + 5.6 MB written) / 592 rows, k = 256
+# ncu: (2.4845 GB read + 6.9 MB written) / 592 rows, k = 256
 NCU_DRAM_BYTES_PER_ROW = (2.4845e9 + 6.9e6) / 592
 # the reference's published H100-PCIe numbers for this shape (q=1024, n=2^20), by k:
 # plots/kselection-hopper01-108424.csv lines 13, 45, 61, 106
